@@ -1,0 +1,178 @@
+/* C ABI of libb2g: hand-written sm_100a kernels for the GGUF-quantized LoRA path.
+ *
+ * Conventions
+ *   - every function returns 0 on success or a negative B2G_E_* code; the message is available
+ *     from b2g_last_error() on the calling thread.  Nothing throws, aborts or synchronises the
+ *     device.
+ *   - all tensor pointers are borrowed DEVICE pointers on the current device, row-major and
+ *     contiguous; `stream` is a cudaStream_t passed as void*.  Unless a function says otherwise it
+ *     allocates nothing: outputs and workspaces come from the caller.
+ *   - bf16 activations / outputs, uint8 GGUF payloads in their on-disk block layout
+ *     ([rows, K / block * block_bytes]); quant types use the GGML ids (8 = Q8_0, 12 = Q4_K,
+ *     16 = IQ2_XXS).
+ *   - `status` (nullable) is a device int32 the kernels write a non-zero code into when a bounded
+ *     device-side wait runs out; it is never written on a healthy run.
+ *
+ * Each entry names the reference interface it stands in for (file:line in
+ * woct0rdho/transformers5-qwen3.5-recipe).  The reference reaches these through the third-party
+ * torch_ggml_ops / AITER ops; the mapping to those ops is in INTEGRATION.md.
+ */
+#ifndef B2G_H_
+#define B2G_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define B2G_API __attribute__((visibility("default")))
+#else
+#define B2G_API
+#endif
+
+#define B2G_E_ARG (-1)     /* bad argument: shape, alignment, unsupported type */
+#define B2G_E_CUDA (-2)    /* a CUDA runtime / driver call failed */
+#define B2G_E_STATE (-3)   /* library state missing (e.g. IQ2_XXS grid not uploaded) */
+
+#define B2G_Q8_0 8
+#define B2G_Q4_K 12
+#define B2G_IQ2_XXS 16
+
+#define B2G_LORA_PAD 16    /* LoRA rank operands are zero-padded to 16 columns / rows */
+
+B2G_API const char* b2g_last_error(void);
+B2G_API int b2g_abi_version(void);
+
+/* Upload the IQ2_XXS magnitude table (256 rows x 8 bytes, HOST pointer) to the current device.
+ * The table is third-party data owned by the gguf package; the caller reads it from there
+ * (gguf.quants.IQ2_XXS.grid) and hands it in once per device before any IQ2_XXS call. */
+B2G_API int b2g_set_iq2xxs_grid(const uint8_t* host_grid_256x8);
+
+/* Logical bf16 weight from a packed payload, bit-exact with float32 decode + round-to-nearest-even.
+ * Replaces transformers.integrations.gguf_dequant.dequantize_gguf_tensor as used at
+ * fast_moe_lora.py:163,235,264 and as the oracle of test_fast_lora.py:110-115. */
+B2G_API int b2g_dequant(int qtype, const void* payload, int64_t rows, int64_t cols, void* out_bf16, void* stream);
+
+/* ---- dense path ------------------------------------------------------------------------------ */
+
+/* Y[M,N] = X[M,K] . deq(W[N,K])^T (+ bias[N]) (+ XAs[M,16] . Bp[N,16]^T).
+ * Replaces torch_ggml_ops.mmq (fast_lora.py:155-160) and, with the two LoRA operands, the addmm of
+ * _fused_lora_add (fast_lora.py:55-61): XAs is the already scaled s*(X.A^T) from b2g_lora_down and
+ * Bp is lora_B zero-padded to 16 columns.  bias, xas/lora_b16 are nullable (xas and lora_b16 together). */
+B2G_API int b2g_qlinear_fwd(int qtype, const void* x, const void* payload, const void* bias, const void* xas,
+                    const void* lora_b16, void* y, int64_t M, int64_t N, int64_t K, int* status, void* stream);
+
+/* dX[M,K] = dY[M,N] . deq(W[N,K]) (+ dYBs[M,16] . Ap[16,K]).
+ * Replaces torch_ggml_ops.mmq_grad_input (registered autograd of mmq, test_fast_lora.py:104-105;
+ * direct call at gguf_liger_loss.py:172) plus the LoRA input-gradient term of fast_lora.py:50-61's
+ * autograd: dYBs = s*(dY.B) from b2g_lora_down, Ap = lora_A zero-padded to 16 rows. */
+B2G_API int b2g_qlinear_dgrad(int qtype, const void* dy, const void* payload, const void* dybs, const void* lora_a16,
+                      void* dx, int64_t M, int64_t N, int64_t K, int* status, void* stream);
+
+/* Skinny projection onto the LoRA rank: P[M,r] = X[M,C] . W^T with W given as [r,C] (w_is_cr = 0,
+ * lora_A for X.A^T) or as [C,r] (w_is_cr = 1, lora_B for dY.B); r <= 16.
+ * Writes out_plain[M,16] = bf16(P) and out_scaled[M,16] = bf16(scale*P), zero in columns >= r
+ * (either may be null).  Replaces the torch.matmul of fast_lora.py:50-53 and its autograd twin. */
+B2G_API int b2g_lora_down(const void* x, const void* w, int w_is_cr, float scale, void* out_plain, void* out_scaled,
+                  int64_t M, int64_t C, int r, void* stream);
+
+/* LoRA factor gradient, a contraction over the M rows:
+ *   G[r,C] = scale * S[M,16]^T . T[M,C]   (only the first r rows of S^T are used)
+ * stored as [r,C] (transpose_out = 0: dA = s*(dY.B)^T.X) or as [C,r] (transpose_out = 1:
+ * dB = s*dY^T.(X.A^T)).  Replaces the addmm/matmul autograd of fast_lora.py:50-61.
+ * `workspace` is fp32 scratch of at least b2g_lora_wgrad_workspace_bytes(M, C) bytes. */
+B2G_API int64_t b2g_lora_wgrad_workspace_bytes(int64_t M, int64_t C);
+B2G_API int b2g_lora_wgrad(const void* s, const void* t, float scale, void* out, int transpose_out, void* workspace,
+                   int64_t workspace_bytes, int64_t M, int64_t C, int r, void* stream);
+
+/* ---- router / routing ------------------------------------------------------------------------ */
+
+/* Top-k expert ids per token, best first, ties to the smaller id.  logits_dtype: 0 = bf16, 1 = fp32;
+ * score_fn: 0 = identity, 1 = sqrt(softplus(x)) (+ bias[E], nullable, fp32).  E must be 256.
+ * Replaces router_topk_indices / _router_topk_kernel (fast_moe_ranking.py:166-270). */
+B2G_API int b2g_router_topk(const void* logits, int logits_dtype, const float* bias, int score_fn, int64_t* indices,
+                    int64_t T, int E, int top_k, void* stream);
+
+/* Stable counting sort of the flat [T*top_k] expert ids.  idx_dtype: 0 = int32, 1 = int64.
+ * Outputs: sorted_expert[R], perm[R], inv_perm[R] (int64), group_sizes[E], offsets[E] (int32,
+ * cumulative ends).  `workspace` is int32 scratch of b2g_route_plan_workspace_bytes(T*top_k, E).
+ * Replaces torch.sort + _inverse_permutation_kernel (fast_moe_routing.py:400-410) and the expert
+ * histogram of GGUFExperts._prepare_expert_execution (called at fast_moe_lora.py:709). */
+B2G_API int64_t b2g_route_plan_workspace_bytes(int64_t R, int E);
+B2G_API int b2g_route_plan(const void* topk_idx, int idx_dtype, int64_t T, int top_k, int E, int64_t* sorted_expert,
+                   int64_t* perm, int64_t* inv_perm, int32_t* group_sizes, int32_t* offsets, void* workspace,
+                   int64_t workspace_bytes, void* stream);
+
+/* sel[s,:] = hidden[perm[s] / top_k, :]            (_route_gather_forward_kernel, fast_moe_routing.py:101-123) */
+B2G_API int b2g_route_gather(const void* hidden, const int64_t* perm, void* selected, int64_t T, int top_k, int H, void* stream);
+/* dHidden[t,:] = sum over the token's k routes in ascending sorted position, bf16 rounding after
+ * every add                                        (_route_gather_backward_kernel, :126-159) */
+B2G_API int b2g_route_gather_bwd(const void* grad_selected, const int64_t* inv_perm, void* grad_hidden, int64_t T,
+                         int top_k, int H, void* stream);
+/* out[t,:] = sum_j expert_out[inv[t*k+j],:] * bf16(w[t,j]); w_dtype 0 = bf16, 1 = fp32
+ *                                                  (_route_combine_forward_kernel, :162-194) */
+B2G_API int b2g_route_combine(const void* expert_out, const void* weights, int w_dtype, const int64_t* inv_perm, void* out,
+                      int64_t T, int top_k, int H, void* stream);
+/* dExpertOut[s,:] = bf16(dFinal[t,:]*bf16(w)); dW[route] = sum_h dFinal*expert_out (in w's dtype)
+ *                                                  (_route_combine_backward_kernel, :197-226) */
+B2G_API int b2g_route_combine_bwd(const void* expert_out, const void* weights, int w_dtype, const int64_t* perm,
+                          const void* grad_final, void* grad_expert_out, void* grad_weights, int64_t T, int top_k,
+                          int H, void* stream);
+
+/* ---- grouped (MoE) path ---------------------------------------------------------------------- */
+
+/* Tile table for the persistent grouped kernels: one entry per (active expert, block of rows).
+ * expert_indices[G] int64, offsets[G] int32 cumulative ends (the pair produced by
+ * GGUFExperts._prepare_expert_execution, fast_moe_lora.py:709-719).  `tiles` is int32 scratch of
+ * b2g_grouped_tiles_bytes(R, G) bytes that the grouped calls below consume. */
+B2G_API int64_t b2g_grouped_tiles_bytes(int64_t R, int G);
+B2G_API int b2g_grouped_schedule(const int64_t* expert_indices, const int32_t* offsets, int G, int64_t R, int32_t* tiles,
+                         void* stream);
+
+/* One persistent launch over the ragged expert segments:
+ *   Y0[rows_g, N] = X[rows_g, K] . deq(W0[e_g])^T   and, when payload1 != NULL, Y1 likewise from W1.
+ * Optional fused LoRA: + XAs[R,16] . Bp[e_g][n,16]^T where lora_b16 is [E, lora_rows, 16] and the
+ * rows used for output j are lora_rows_offset_j + n (Y0: 0, Y1: N).
+ * Replaces torch_ggml_ops.grouped_mmq (fast_moe_lora.py:221-228) and grouped_mmq_pair (:339-347),
+ * and with the LoRA operands the second AITER gmm + torch.add of :737-745 / :756-763. */
+B2G_API int b2g_grouped_fwd(int qtype, const void* x, const void* payload0, const void* payload1, const int32_t* tiles,
+                    const void* xas, const void* lora_b16, int64_t lora_rows, void* y0, void* y1, int64_t R,
+                    int64_t N, int64_t K, int num_experts, int* status, void* stream);
+
+/* dX[rows_g, K] = dY0[rows_g, N] . deq(W0[e_g]) (+ dY1 . deq(W1[e_g]) in the same fp32 accumulator)
+ * (+ dYBs[R,16] . Ap[e_g][16,K]).  Replaces grouped_mmq_grad_input (fast_moe_lora.py:255-262) and
+ * grouped_mmq_pair_grad_input (:364-375) plus the gmm input-gradient of :126-131. */
+B2G_API int b2g_grouped_dgrad(int qtype, const void* dy0, const void* dy1, const void* payload0, const void* payload1,
+                      const int32_t* tiles, const void* dybs, const void* lora_a16, void* dx, int64_t R, int64_t N,
+                      int64_t K, int num_experts, int* status, void* stream);
+
+/* Per-expert skinny projection P[rows_g, r] = X[rows_g, C] . W[e_g]^T, W given per expert as [r,C]
+ * (w_is_cr = 0) or [C,r] (w_is_cr = 1); with x1 != NULL the reduction runs over [x | x1] (two
+ * [R,C] halves against a [2C,r] factor: dGate|dUp against gate_up_b).  Outputs as b2g_lora_down.
+ * Replaces the first AITER gmm of _lora_grouped_linear (fast_moe_lora.py:675-682) and gmm's use in
+ * _AiterGroupedMM.backward (:126-131). */
+B2G_API int b2g_grouped_lora_down(const void* x, const void* x1, const void* w, int w_is_cr, float scale, const int32_t* tiles,
+                          void* out_plain, void* out_scaled, int64_t R, int64_t C, int r, int num_experts,
+                          void* stream);
+
+/* Per-expert LoRA factor gradients over all E experts (zero rows -> exactly zero output):
+ *   G[e][r,C] = scale * S[rows_e,16]^T . T[rows_e, C], stored [E,r,C] or (transpose_out) [E,C,r].
+ * `offsets_full` is the cumulative-end array over ALL E experts (fast_moe_lora.py:663-672).
+ * Replaces AITER ptgmm via _aiter_weight_grad (fast_moe_lora.py:76-87,132-139). */
+B2G_API int b2g_grouped_lora_wgrad(const void* s, const void* t, float scale, const int32_t* offsets_full, void* out,
+                           int transpose_out, int64_t R, int64_t C, int r, int num_experts, int64_t out_col_offset,
+                           int64_t out_cols_total, void* stream);
+
+/* SwiGLU between the two grouped products: z = silu(g) * u (optionally clamped as the DeepSeek
+ * experts do: g <= limit, |u| <= limit; limit <= 0 disables).  Replaces GGUFExperts._apply_split_gate
+ * (called at fast_moe_lora.py:747; clamp semantics at test_deepseek_v4_moe_lora.py:194-196). */
+B2G_API int b2g_swiglu_fwd(const void* gate, const void* up, void* z, int64_t n, float limit, void* stream);
+B2G_API int b2g_swiglu_bwd(const void* gate, const void* up, const void* dz, void* dgate, void* dup, int64_t n, float limit,
+                   void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B2G_H_ */

@@ -1,0 +1,81 @@
+"""ctypes binding of libb2g.so (the C ABI declared in include/b2g.h)."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+from pathlib import Path
+
+_HERE = Path(__file__).resolve().parent
+LIB_PATH = _HERE.parent / "csrc" / "libb2g.so"
+
+_vp, _i32, _i64, _f32 = C.c_void_p, C.c_int, C.c_int64, C.c_float
+
+# name -> (restype, argtypes); mirrors include/b2g.h one to one
+SIGNATURES = {
+    "b2g_last_error": (C.c_char_p, []),
+    "b2g_abi_version": (_i32, []),
+    "b2g_set_iq2xxs_grid": (_i32, [_vp]),
+    "b2g_dequant": (_i32, [_i32, _vp, _i64, _i64, _vp, _vp]),
+    "b2g_qlinear_fwd": (_i32, [_i32, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp]),
+    "b2g_qlinear_dgrad": (_i32, [_i32, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp]),
+    "b2g_lora_down": (_i32, [_vp, _vp, _i32, _f32, _vp, _vp, _i64, _i64, _i32, _vp]),
+    "b2g_lora_wgrad_workspace_bytes": (_i64, [_i64, _i64]),
+    "b2g_lora_wgrad": (_i32, [_vp, _vp, _f32, _vp, _i32, _vp, _i64, _i64, _i64, _i32, _vp]),
+    "b2g_router_topk": (_i32, [_vp, _i32, _vp, _i32, _vp, _i64, _i32, _i32, _vp]),
+    "b2g_route_plan_workspace_bytes": (_i64, [_i64, _i32]),
+    "b2g_route_plan": (_i32, [_vp, _i32, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp]),
+    "b2g_route_gather": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _vp]),
+    "b2g_route_gather_bwd": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _vp]),
+    "b2g_route_combine": (_i32, [_vp, _vp, _i32, _vp, _vp, _i64, _i32, _i32, _vp]),
+    "b2g_route_combine_bwd": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp]),
+    "b2g_grouped_tiles_bytes": (_i64, [_i64, _i32]),
+    "b2g_grouped_schedule": (_i32, [_vp, _vp, _i32, _i64, _vp, _vp]),
+    "b2g_grouped_fwd": (_i32, [_i32, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i32, _vp, _vp]),
+    "b2g_grouped_dgrad": (_i32, [_i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp, _vp]),
+    "b2g_grouped_lora_down": (_i32, [_vp, _vp, _vp, _i32, _f32, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp]),
+    "b2g_grouped_lora_wgrad": (_i32, [_vp, _vp, _f32, _vp, _vp, _i32, _i64, _i64, _i32, _i32, _i64, _i64, _vp]),
+    "b2g_swiglu_fwd": (_i32, [_vp, _vp, _vp, _i64, _f32, _vp]),
+    "b2g_swiglu_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _f32, _vp]),
+}
+
+_lib = None
+_lock = threading.Lock()
+
+
+class B2GError(RuntimeError):
+    """A libb2g call returned an error code."""
+
+
+def load() -> C.CDLL:
+    """Load the library once.  Raises (never falls back) when it has not been built."""
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                path = Path(os.environ.get("B2G_LIB", LIB_PATH))
+                if not path.exists():
+                    raise B2GError(
+                        f"{path} is missing: build it with `python {LIB_PATH.parent / 'build.py'}`. "
+                        "This package has no CPU or PyTorch fallback."
+                    )
+                lib = C.CDLL(str(path))
+                for name, (res, args) in SIGNATURES.items():
+                    fn = getattr(lib, name)
+                    fn.restype, fn.argtypes = res, args
+                _lib = lib
+    return _lib
+
+
+def call(name: str, *args):
+    """Invoke an int-returning entry point; raise B2GError with the library's message on failure."""
+    lib = load()
+    rc = getattr(lib, name)(*args)
+    if rc != 0:
+        msg = lib.b2g_last_error().decode("utf-8", "replace")
+        kind = ValueError if rc == -1 else B2GError
+        raise kind(f"{name}: {msg} (code {rc})")
+
+
+def query(name: str, *args) -> int:
+    return int(getattr(load(), name)(*args))

@@ -1,0 +1,127 @@
+// Device-side decoders for the GGUF block formats on the path: Q8_0, Q4_K, IQ2_XXS.
+//
+// The arithmetic reproduces the float32 decode of the public format definition bit for bit
+// after the final bf16 round-to-nearest-even:
+//   Q8_0    q * d                                 (19 significant bits: exact in fp32)
+//   Q4_K    (d*sc)*q - (dmin*m)                   (both products exact; the subtraction rounds once,
+//                                                  so a single fused multiply-add gives the same bits)
+//   IQ2_XXS d*(0.5+s4)*0.25 * grid * sign         (22 significant bits: exact in fp32)
+// Block layouts (bytes): Q8_0 34 = fp16 d | 32 x int8; Q4_K 144 = fp16 d | fp16 dmin | 12 scale bytes
+// | 128 nibble bytes; IQ2_XXS 66 = fp16 d | 8 x (4 grid indices | u32: 4 x 7-bit signs + 4-bit scale).
+#pragma once
+
+#include "b2g_common.cuh"
+
+namespace b2g {
+namespace fmt {
+
+template <int QT> struct Block;
+template <> struct Block<B2G_Q8_0> { static constexpr int kValues = 32, kBytes = 34; };
+template <> struct Block<B2G_Q4_K> { static constexpr int kValues = 256, kBytes = 144; };
+template <> struct Block<B2G_IQ2_XXS> { static constexpr int kValues = 256, kBytes = 66; };
+
+__host__ __device__ inline int64_t row_bytes(int qtype, int64_t k) {
+  switch (qtype) {
+    case B2G_Q8_0: return k / 32 * 34;
+    case B2G_Q4_K: return k / 256 * 144;
+    case B2G_IQ2_XXS: return k / 256 * 66;
+    default: return -1;
+  }
+}
+__host__ __device__ inline int block_values(int qtype) { return qtype == B2G_Q8_0 ? 32 : 256; }
+
+// Exact small-integer -> float: place the byte in the mantissa of 2^23 and subtract 2^23.
+__device__ __forceinline__ float byte_to_float(uint32_t word, int byte_index) {
+  // selector nibbles (lsb first): result byte0 = word.byte[i], byte1 = 0x00, byte2 = 0x00, byte3 = 0x4B
+  const uint32_t magic = __byte_perm(word, 0x4B000000u, 0x7540u + byte_index);
+  return __uint_as_float(magic) - 8388608.0f;
+}
+
+// Q4_K: 6-bit (scale, min) of sub-block `i` (0..7) from the 12 scale bytes held as three words.
+__device__ __forceinline__ void q4k_scale_min(uint32_t s0, uint32_t s1, uint32_t s2, int i, uint32_t& sc, uint32_t& mn) {
+  const int sh = (i & 3) * 8;
+  const uint32_t a = (s0 >> sh) & 0xFFu, m = (s1 >> sh) & 0xFFu, lo = (s2 >> sh) & 0xFFu;
+  if (i < 4) {
+    sc = a & 63u;
+    mn = m & 63u;
+  } else {
+    sc = (lo & 15u) | ((a >> 6) << 4);
+    mn = (lo >> 4) | ((m >> 6) << 4);
+  }
+}
+
+// IQ2_XXS: sign byte of a 7-bit index (bit 7 = parity of the low seven bits).
+__device__ __forceinline__ uint32_t iq2_sign_byte(uint32_t idx7) { return idx7 | ((__popc(idx7) & 1u) << 7); }
+
+// ---- decode 8 consecutive values k0..k0+7 (k0 % 8 == 0) of one packed row in GLOBAL memory ----
+// Used by the stand-alone dequantiser; the GEMM kernels decode from shared memory instead.
+template <int QT>
+struct Decode8;
+
+template <>
+struct Decode8<B2G_Q8_0> {
+  __device__ static __forceinline__ void run(const uint8_t* __restrict__ row, int k0, const uint2*, float (&v)[8]) {
+    const uint8_t* b = row + (k0 >> 5) * 34;  // 34-byte blocks are only 2-byte aligned
+    const float d = dev::half_bits_to_float(*reinterpret_cast<const unsigned short*>(b));
+    const unsigned short* q = reinterpret_cast<const unsigned short*>(b + 2 + (k0 & 31));
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t two = q[i];
+      const float lo = static_cast<float>(static_cast<int>(static_cast<signed char>(two & 0xFF)));
+      const float hi = static_cast<float>(static_cast<int>(static_cast<signed char>(two >> 8)));
+      v[2 * i] = __fmul_rn(lo, d);
+      v[2 * i + 1] = __fmul_rn(hi, d);
+    }
+  }
+};
+
+template <>
+struct Decode8<B2G_Q4_K> {
+  __device__ static __forceinline__ void run(const uint8_t* __restrict__ row, int k0, const uint2*, float (&v)[8]) {
+    const uint8_t* b = row + (k0 >> 8) * 144;  // 144-byte blocks keep 16-byte alignment
+    const uint4 hdr = *reinterpret_cast<const uint4*>(b);
+    const int within = k0 & 255;
+    const int sub = within >> 5;               // sub-block 0..7
+    uint32_t sc, mn;
+    q4k_scale_min(hdr.y, hdr.z, hdr.w, sub, sc, mn);
+    const float dsc = __fmul_rn(dev::half_bits_to_float(hdr.x), static_cast<float>(sc));
+    const float dm = __fmul_rn(dev::half_bits_to_float(hdr.x >> 16), static_cast<float>(mn));
+    // sub-blocks 2j / 2j+1 share 32 bytes: low / high nibbles
+    const uint2 w = *reinterpret_cast<const uint2*>(b + 16 + (sub >> 1) * 32 + (within & 31));
+    const int shift = (sub & 1) * 4;
+    const uint32_t w0 = (w.x >> shift) & 0x0F0F0F0Fu, w1 = (w.y >> shift) & 0x0F0F0F0Fu;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[i] = __fmaf_rn(dsc, byte_to_float(w0, i), -dm);
+      v[4 + i] = __fmaf_rn(dsc, byte_to_float(w1, i), -dm);
+    }
+  }
+};
+
+template <>
+struct Decode8<B2G_IQ2_XXS> {
+  __device__ static __forceinline__ void run(const uint8_t* __restrict__ row, int k0, const uint2* __restrict__ grid,
+                                             float (&v)[8]) {
+    const uint8_t* b = row + (k0 >> 8) * 66;   // 66-byte blocks are only 2-byte aligned
+    const unsigned short* h = reinterpret_cast<const unsigned short*>(b);
+    const float d = dev::half_bits_to_float(h[0]);
+    const int within = k0 & 255;
+    const int grp = within >> 5;               // group of 32 values: 8 bytes at 2 + 8*grp
+    const int sub = (within >> 3) & 3;         // which 8-value row of the group
+    const unsigned short* g = h + 1 + grp * 4;
+    const uint32_t idx4 = static_cast<uint32_t>(g[0]) | (static_cast<uint32_t>(g[1]) << 16);
+    const uint32_t word = static_cast<uint32_t>(g[2]) | (static_cast<uint32_t>(g[3]) << 16);
+    const float db = __fmul_rn(__fmul_rn(d, 0.5f + static_cast<float>(word >> 28)), 0.25f);
+    const uint32_t signs = iq2_sign_byte((word >> (7 * sub)) & 127u);
+    const uint2 mag = grid[(idx4 >> (8 * sub)) & 255u];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t m = ((i < 4 ? mag.x : mag.y) >> (8 * (i & 3))) & 0xFFu;
+      const float mv = __fmul_rn(db, static_cast<float>(m));
+      v[i] = ((signs >> i) & 1u) ? -mv : mv;
+    }
+  }
+};
+
+}  // namespace fmt
+}  // namespace b2g

@@ -1,0 +1,379 @@
+// LoRA rank-side products: the skinny projections (X.A^T, dY.B) and the factor gradients
+// (contractions over the token rows).  Output widths are <= 16, so these kernels are bound by
+// streaming X / dY once from HBM; tiles arrive through a cp.async pipeline and the arithmetic is
+// bf16 mma.sync with fp32 accumulation.  The same kernels serve the dense path (one weight) and the
+// grouped path (one weight per expert segment).
+#include "b2g_common.cuh"
+
+namespace b2g {
+namespace lora {
+
+constexpr int kRankPad = B2G_LORA_PAD;  // 16
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;  // src-size 0 zero-fills the destination
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Row segment handled by one CTA.
+struct Seg { int expert, row0, rows; };
+
+// ------------------------------------------------------------------------------------------------
+// Projection: P[rows,16] = X[rows,C] . W_e^T  (r <= 16 columns live, the rest zero)
+// CTA = 4 warps x 16 rows; reduction in chunks of 128 columns, 3-stage cp.async ring.
+// ------------------------------------------------------------------------------------------------
+constexpr int kDownRows = 64, kDownBK = 128, kDownStages = 3, kDownStride = kDownBK * 2 + 16;  // 272-byte rows
+
+__device__ __forceinline__ Seg down_segment(const int4* tiles, int64_t m_total, int item) {
+  Seg s;
+  if (tiles) {
+    const int rows_per_tile = tiles[0].y;
+    const int per = rows_per_tile / kDownRows;
+    const int4 e = tiles[1 + item / per];
+    const int sub = item % per;
+    s.expert = e.x;
+    s.row0 = e.y + sub * kDownRows;
+    const int left = e.z - sub * kDownRows;
+    s.rows = left < 0 ? 0 : (left < kDownRows ? left : kDownRows);
+  } else {
+    s.expert = 0;
+    s.row0 = item * kDownRows;
+    const int64_t left = m_total - s.row0;
+    s.rows = left < kDownRows ? (int)left : kDownRows;
+  }
+  return s;
+}
+
+template <bool kWisCR>
+__global__ void __launch_bounds__(128) lora_down_kernel(const __nv_bfloat16* __restrict__ x0, const __nv_bfloat16* __restrict__ x1,
+                                                        const __nv_bfloat16* __restrict__ w, float scale, const int4* __restrict__ tiles,
+                                                        __nv_bfloat16* __restrict__ out_plain, __nv_bfloat16* __restrict__ out_scaled,
+                                                        int64_t m_total, int C, int r, int dense_items) {
+  extern __shared__ __align__(16) uint8_t sm[];
+  const uint32_t sbase = dev::smem_u32(sm);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nseg = x1 ? 2 : 1;
+  const int chunks = C / kDownBK;
+  const int total_items = tiles ? tiles[0].x * (tiles[0].y / kDownRows) : dense_items;
+  const int64_t w_per_expert = (int64_t)nseg * C * r;
+
+  for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+    const Seg s = down_segment(tiles, m_total, item);
+    if (s.rows <= 0) continue;
+    const __nv_bfloat16* we = w + s.expert * w_per_expert;
+    float acc[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+    const int total_chunks = nseg * chunks;
+
+    auto issue = [&](int ch) {
+      const int seg = ch / chunks, c0 = (ch - seg * chunks) * kDownBK;
+      const __nv_bfloat16* xs = seg ? x1 : x0;
+      const uint32_t dst = sbase + (ch % kDownStages) * (kDownRows * kDownStride);
+      // 64 rows x 16 vectors of 16 bytes = 1024 vectors over 128 threads
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int v = threadIdx.x + i * 128;
+        const int row = v >> 4, vec = v & 15;
+        const bool ok = row < s.rows;
+        const __nv_bfloat16* src = xs + (int64_t)(s.row0 + (ok ? row : 0)) * C + c0 + vec * 8;
+        cp_async16(dst + row * kDownStride + vec * 16, src, ok);
+      }
+    };
+
+    for (int pre = 0; pre < kDownStages - 1; ++pre) {
+      if (pre < total_chunks) issue(pre);
+      cp_async_commit();
+    }
+    for (int ch = 0; ch < total_chunks; ++ch) {
+      if (ch + kDownStages - 1 < total_chunks) issue(ch + kDownStages - 1);
+      cp_async_commit();
+      cp_async_wait<kDownStages - 1>();
+      __syncthreads();
+      const int seg = ch / chunks, c0 = (ch - seg * chunks) * kDownBK;
+      const uint32_t tile = sbase + (ch % kDownStages) * (kDownRows * kDownStride);
+#pragma unroll
+      for (int kk = 0; kk < kDownBK / 16; ++kk) {
+        uint32_t a[4];
+        ldmatrix_x4(tile + (warp * 16 + (lane & 15)) * kDownStride + (kk * 16 + (lane >> 4) * 8) * 2, a);
+        const int kcol = seg * C + c0 + kk * 16 + (lane & 3) * 2;  // reduction index of b0 (b1 is +8)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          const int n = nt * 8 + (lane >> 2);
+          uint32_t b0 = 0, b1 = 0;
+          if (n < r) {
+            if (kWisCR) {  // W[(k), n] with r columns
+              const unsigned short* wp = reinterpret_cast<const unsigned short*>(we);
+              b0 = wp[(int64_t)kcol * r + n] | (static_cast<uint32_t>(wp[(int64_t)(kcol + 1) * r + n]) << 16);
+              b1 = wp[(int64_t)(kcol + 8) * r + n] | (static_cast<uint32_t>(wp[(int64_t)(kcol + 9) * r + n]) << 16);
+            } else {       // W[n, k] with nseg*C columns
+              const __nv_bfloat16* wp = we + (int64_t)n * (nseg * C) + kcol;
+              b0 = *reinterpret_cast<const uint32_t*>(wp);
+              b1 = *reinterpret_cast<const uint32_t*>(wp + 8);
+            }
+          }
+          mma_bf16(acc[nt], a, b0, b1);
+        }
+      }
+      __syncthreads();
+    }
+    cp_async_wait<0>();
+    // store: thread holds rows g and g+8, columns nt*8 + 2*(lane%4) + {0,1}
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int row = warp * 16 + (lane >> 2) + half * 8;
+      if (row < s.rows) {
+        const int64_t o = (int64_t)(s.row0 + row) * kRankPad;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          const int col = nt * 8 + (lane & 3) * 2;
+          const float v0 = acc[nt][half * 2], v1 = acc[nt][half * 2 + 1];
+          if (out_plain) *reinterpret_cast<uint32_t*>(out_plain + o + col) = dev::pack_bf16(v0, v1);
+          if (out_scaled) *reinterpret_cast<uint32_t*>(out_scaled + o + col) = dev::pack_bf16(v0 * scale, v1 * scale);
+        }
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Factor gradient: G[16, 128-column chunk] = S[rows,16]^T . T[rows, chunk] over one row segment.
+// CTA = 4 warps x 32 columns; rows stream in steps of 64 through a 3-stage cp.async ring.
+//   kPartial = true : dense path, segment = one split of M, fp32 partial to the workspace
+//   kPartial = false: grouped path, segment = one expert, scaled bf16 straight to the output
+// ------------------------------------------------------------------------------------------------
+constexpr int kWgCols = 128, kWgRows = 64, kWgStages = 3, kWgTStride = kWgCols * 2 + 16, kWgSStride = 48;
+constexpr int kWgStageBytes = kWgRows * kWgTStride + kWgRows * kWgSStride;
+
+template <bool kPartial>
+__global__ void __launch_bounds__(128) lora_wgrad_kernel(const __nv_bfloat16* __restrict__ s, const __nv_bfloat16* __restrict__ t, float scale,
+                                                         const int32_t* __restrict__ offsets, int64_t m_total, int rows_per_split,
+                                                         int C, int r, float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
+                                                         int transpose_out, int64_t out_col_offset, int64_t out_cols_total) {
+  extern __shared__ __align__(16) uint8_t sm[];
+  const uint32_t sbase = dev::smem_u32(sm);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int chunk = blockIdx.x, segi = blockIdx.y;
+  const int c0 = chunk * kWgCols;
+  int64_t row0, rows;
+  if (kPartial) {
+    row0 = (int64_t)segi * rows_per_split;
+    rows = m_total - row0 < rows_per_split ? m_total - row0 : rows_per_split;
+    if (rows < 0) rows = 0;
+  } else {
+    row0 = segi > 0 ? offsets[segi - 1] : 0;
+    rows = offsets[segi] - row0;
+  }
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+
+  const int steps = (int)((rows + kWgRows - 1) / kWgRows);
+  auto issue = [&](int st) {
+    const uint32_t dst_t = sbase + (st % kWgStages) * kWgStageBytes;
+    const uint32_t dst_s = dst_t + kWgRows * kWgTStride;
+    const int64_t base = row0 + (int64_t)st * kWgRows;
+    const int live = (int)(rows - (int64_t)st * kWgRows < kWgRows ? rows - (int64_t)st * kWgRows : kWgRows);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {  // T tile: 64 rows x 16 vectors
+      const int v = threadIdx.x + i * 128;
+      const int row = v >> 4, vec = v & 15;
+      const bool ok = row < live && c0 + vec * 8 < C;
+      cp_async16(dst_t + row * kWgTStride + vec * 16, t + (base + (ok ? row : 0)) * C + c0 + (ok ? vec * 8 : 0), ok);
+    }
+    {  // S tile: 64 rows x 2 vectors
+      const int row = threadIdx.x >> 1, vec = threadIdx.x & 1;
+      const bool ok = row < live;
+      cp_async16(dst_s + row * kWgSStride + vec * 16, s + (base + (ok ? row : 0)) * kRankPad + vec * 8, ok);
+    }
+  };
+  for (int pre = 0; pre < kWgStages - 1; ++pre) {
+    if (pre < steps) issue(pre);
+    cp_async_commit();
+  }
+  for (int st = 0; st < steps; ++st) {
+    if (st + kWgStages - 1 < steps) issue(st + kWgStages - 1);
+    cp_async_commit();
+    cp_async_wait<kWgStages - 1>();
+    __syncthreads();
+    const uint32_t tt = sbase + (st % kWgStages) * kWgStageBytes;
+    const uint32_t ss = tt + kWgRows * kWgTStride;
+#pragma unroll
+    for (int kk = 0; kk < kWgRows / 16; ++kk) {
+      uint32_t a[4];  // S^T fragment: rows = rank index, k = token row
+      ldmatrix_x4_trans(ss + (kk * 16 + (lane >> 4) * 8 + (lane & 7)) * kWgSStride + ((lane >> 3) & 1) * 16, a);
+#pragma unroll
+      for (int np = 0; np < 2; ++np) {  // two pairs of 8-column tiles
+        uint32_t b[4];
+        ldmatrix_x4_trans(tt + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * kWgTStride + (warp * 32 + np * 16 + (lane >> 4) * 8) * 2, b);
+        mma_bf16(acc[np * 2], a, b[0], b[1]);
+        mma_bf16(acc[np * 2 + 1], a, b[2], b[3]);
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  // acc[nt]: rank rows g, g+8; columns c0 + warp*32 + nt*8 + 2*(lane%4) + {0,1}
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int i = (lane >> 2) + half * 8;
+      const int col = c0 + warp * 32 + nt * 8 + (lane & 3) * 2;
+      if (col >= C) continue;
+      const float v0 = acc[nt][half * 2], v1 = acc[nt][half * 2 + 1];
+      if (kPartial) {
+        float* p = partial + ((int64_t)segi * kRankPad + i) * C + col;
+        p[0] = v0; p[1] = v1;
+      } else if (i < r) {
+        if (transpose_out) {
+          __nv_bfloat16* o = out + ((int64_t)segi * out_cols_total + out_col_offset + col) * r + i;
+          o[0] = __float2bfloat16_rn(v0 * scale);
+          o[r] = __float2bfloat16_rn(v1 * scale);
+        } else {
+          __nv_bfloat16* o = out + ((int64_t)segi * r + i) * out_cols_total + out_col_offset + col;
+          o[0] = __float2bfloat16_rn(v0 * scale);
+          o[1] = __float2bfloat16_rn(v1 * scale);
+        }
+      }
+    }
+  }
+}
+
+// Sum the per-split partials in split order (deterministic), scale, round, store.
+__global__ void __launch_bounds__(256) lora_wgrad_reduce_kernel(const float* __restrict__ partial, int splits, int C, int r, float scale,
+                                                                __nv_bfloat16* __restrict__ out, int transpose_out) {
+  const int64_t n = (int64_t)r * C;
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < n; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int i = (int)(idx / C), c = (int)(idx - (int64_t)i * C);
+    float sum = 0.f;
+    for (int sp = 0; sp < splits; ++sp) sum += partial[((int64_t)sp * kRankPad + i) * C + c];
+    const __nv_bfloat16 v = __float2bfloat16_rn(sum * scale);
+    if (transpose_out) out[(int64_t)c * r + i] = v;
+    else out[idx] = v;
+  }
+}
+
+inline int wgrad_splits(int64_t M, int64_t C) {
+  const int chunks = (int)((C + kWgCols - 1) / kWgCols);
+  int splits = (4 * sm_count() + chunks - 1) / chunks;
+  const int64_t max_splits = (M + kWgRows - 1) / kWgRows;
+  if (splits > max_splits) splits = (int)max_splits;
+  if (splits < 1) splits = 1;
+  return splits;
+}
+
+}  // namespace lora
+}  // namespace b2g
+
+using namespace b2g;
+
+static int lora_down_launch(const void* x, const void* x1, const void* w, int w_is_cr, float scale, const int32_t* tiles, void* out_plain,
+                            void* out_scaled, int64_t M, int64_t C, int r, void* stream, const char* what) {
+  B2G_REQUIRE(r >= 1 && r <= lora::kRankPad, "%s: rank %d outside 1..16", what, r);
+  B2G_REQUIRE(C > 0 && C % lora::kDownBK == 0, "%s: reduction width %lld must be a multiple of 128", what, (long long)C);
+  B2G_REQUIRE(M >= 0 && M < (1ll << 31), "%s: bad row count", what);
+  if (M == 0) return 0;
+  B2G_REQUIRE(x && w && (out_plain || out_scaled), "%s: null pointer", what);
+  B2G_REQUIRE(aligned16(x) && (!x1 || aligned16(x1)), "%s: activations must be 16-byte aligned", what);
+  B2G_REQUIRE(w_is_cr || (reinterpret_cast<uintptr_t>(w) & 3) == 0, "%s: weight must be 4-byte aligned", what);
+  const size_t smem = (size_t)lora::kDownStages * lora::kDownRows * lora::kDownStride;
+  const int dense_items = (int)((M + lora::kDownRows - 1) / lora::kDownRows);
+  int grid = sm_count() * 4;
+  if (!tiles && dense_items < grid) grid = dense_items;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  auto* xb = static_cast<const __nv_bfloat16*>(x);
+  auto* x1b = static_cast<const __nv_bfloat16*>(x1);
+  auto* wb = static_cast<const __nv_bfloat16*>(w);
+  auto* op = static_cast<__nv_bfloat16*>(out_plain);
+  auto* os = static_cast<__nv_bfloat16*>(out_scaled);
+  auto* tl = reinterpret_cast<const int4*>(tiles);
+  if (w_is_cr) {
+    B2G_CUDA_OK(cudaFuncSetAttribute(lora::lora_down_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    lora::lora_down_kernel<true><<<grid, 128, smem, s>>>(xb, x1b, wb, scale, tl, op, os, M, (int)C, r, dense_items);
+  } else {
+    B2G_CUDA_OK(cudaFuncSetAttribute(lora::lora_down_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    lora::lora_down_kernel<false><<<grid, 128, smem, s>>>(xb, x1b, wb, scale, tl, op, os, M, (int)C, r, dense_items);
+  }
+  B2G_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int b2g_lora_down(const void* x, const void* w, int w_is_cr, float scale, void* out_plain, void* out_scaled, int64_t M,
+                             int64_t C, int r, void* stream) {
+  return lora_down_launch(x, nullptr, w, w_is_cr, scale, nullptr, out_plain, out_scaled, M, C, r, stream, "lora_down");
+}
+
+extern "C" int b2g_grouped_lora_down(const void* x, const void* x1, const void* w, int w_is_cr, float scale, const int32_t* tiles,
+                                     void* out_plain, void* out_scaled, int64_t R, int64_t C, int r, int num_experts, void* stream) {
+  B2G_REQUIRE(tiles != nullptr && num_experts >= 1, "grouped_lora_down: tile table missing");
+  B2G_REQUIRE(x1 == nullptr || w_is_cr, "grouped_lora_down: a two-part input needs the [2C, r] weight layout");
+  return lora_down_launch(x, x1, w, w_is_cr, scale, tiles, out_plain, out_scaled, R, C, r, stream, "grouped_lora_down");
+}
+
+extern "C" int64_t b2g_lora_wgrad_workspace_bytes(int64_t M, int64_t C) {
+  if (M <= 0 || C <= 0) return 16;
+  return (int64_t)lora::wgrad_splits(M, C) * lora::kRankPad * C * (int64_t)sizeof(float);
+}
+
+extern "C" int b2g_lora_wgrad(const void* s, const void* t, float scale, void* out, int transpose_out, void* workspace,
+                              int64_t workspace_bytes, int64_t M, int64_t C, int r, void* stream) {
+  B2G_REQUIRE(r >= 1 && r <= lora::kRankPad, "lora_wgrad: rank %d outside 1..16", r);
+  B2G_REQUIRE(C > 0 && C % 8 == 0 && M > 0 && M < (1ll << 31), "lora_wgrad: bad shape M=%lld C=%lld", (long long)M, (long long)C);
+  B2G_REQUIRE(s && t && out && workspace, "lora_wgrad: null pointer");
+  B2G_REQUIRE(aligned16(s) && aligned16(t) && aligned16(workspace), "lora_wgrad: operands must be 16-byte aligned");
+  B2G_REQUIRE(workspace_bytes >= b2g_lora_wgrad_workspace_bytes(M, C), "lora_wgrad: workspace of %lld bytes is smaller than %lld",
+              (long long)workspace_bytes, (long long)b2g_lora_wgrad_workspace_bytes(M, C));
+  const int splits = lora::wgrad_splits(M, C);
+  int rows_per_split = (int)((M + splits - 1) / splits);
+  rows_per_split = (rows_per_split + lora::kWgRows - 1) / lora::kWgRows * lora::kWgRows;
+  const int chunks = (int)((C + lora::kWgCols - 1) / lora::kWgCols);
+  const size_t smem = (size_t)lora::kWgStages * lora::kWgStageBytes;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  B2G_CUDA_OK(cudaFuncSetAttribute(lora::lora_wgrad_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  lora::lora_wgrad_kernel<true><<<dim3(chunks, splits), 128, smem, st>>>(
+      static_cast<const __nv_bfloat16*>(s), static_cast<const __nv_bfloat16*>(t), scale, nullptr, M, rows_per_split, (int)C, r,
+      static_cast<float*>(workspace), nullptr, 0, 0, 0);
+  B2G_CUDA_OK(cudaGetLastError());
+  const int64_t n = (int64_t)r * C;
+  lora::lora_wgrad_reduce_kernel<<<(int)((n + 255) / 256), 256, 0, st>>>(static_cast<const float*>(workspace), splits, (int)C, r, scale,
+                                                                       static_cast<__nv_bfloat16*>(out), transpose_out);
+  B2G_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int b2g_grouped_lora_wgrad(const void* s, const void* t, float scale, const int32_t* offsets_full, void* out, int transpose_out,
+                                      int64_t R, int64_t C, int r, int num_experts, int64_t out_col_offset, int64_t out_cols_total,
+                                      void* stream) {
+  B2G_REQUIRE(r >= 1 && r <= lora::kRankPad, "grouped_lora_wgrad: rank %d outside 1..16", r);
+  B2G_REQUIRE(C > 0 && C % 8 == 0 && R >= 0, "grouped_lora_wgrad: bad shape");
+  B2G_REQUIRE(num_experts >= 1 && num_experts <= 65535, "grouped_lora_wgrad: bad expert count %d", num_experts);
+  B2G_REQUIRE(s && t && out && offsets_full, "grouped_lora_wgrad: null pointer");
+  B2G_REQUIRE(aligned16(s) && aligned16(t), "grouped_lora_wgrad: operands must be 16-byte aligned");
+  B2G_REQUIRE(out_col_offset >= 0 && out_col_offset + C <= out_cols_total, "grouped_lora_wgrad: output slice out of range");
+  const int chunks = (int)((C + lora::kWgCols - 1) / lora::kWgCols);
+  const size_t smem = (size_t)lora::kWgStages * lora::kWgStageBytes;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  B2G_CUDA_OK(cudaFuncSetAttribute(lora::lora_wgrad_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  lora::lora_wgrad_kernel<false><<<dim3(chunks, num_experts), 128, smem, st>>>(
+      static_cast<const __nv_bfloat16*>(s), static_cast<const __nv_bfloat16*>(t), scale, offsets_full, R, 0, (int)C, r, nullptr,
+      static_cast<__nv_bfloat16*>(out), transpose_out, out_col_offset, out_cols_total);
+  B2G_CUDA_OK(cudaGetLastError());
+  return 0;
+}

@@ -1,0 +1,764 @@
+// Quantized-weight GEMM for sm_100a: activations by TMA, packed GGUF blocks by TMA in their on-disk
+// layout, unpack to bf16 in shared memory, tcgen05.mma with fp32 accumulators in TMEM.
+//
+// One persistent, warp-specialised kernel serves four entry points:
+//   dense   forward   Y[M,N]  = X[M,K] . deq(W[N,K])^T                 (+ bias, + LoRA)
+//   dense   dgrad     dX[M,K] = dY[M,N] . deq(W[N,K])                  (+ LoRA)
+//   grouped forward   per ragged expert segment, one or two (gate, up) weight tensors
+//   grouped dgrad     per segment, one or two gradient/weight pairs summed in one accumulator
+//
+// Tile: 128*MT rows x 256 output columns, reduction step 64.  Per step the CTA holds
+//   A  : MT x [128 rows x 64] bf16, 128-byte swizzle, written by TMA          (A operand, K-major)
+//   B  : [R rows of W x 64 k] bf16 sub-tiles, 128-byte swizzle, written by the unpack warps.
+//        forward: one sub-tile of 256 W rows  -> B operand K-major  (N = W rows, K = k)
+//        dgrad  : four sub-tiles of 64 W rows -> B operand MN-major (N = k,      K = W rows)
+//        The unpack warps therefore write the same [w_row][k] layout in both directions; only the
+//        shared-memory descriptors differ, so no packed transpose is ever built.
+// The LoRA up-projection is one extra K=16 MMA per tile on 32-byte-swizzled [rows x 16] tiles.
+//
+// Warp roles (448 threads): 0 = TMA producer, 1 = MMA issuer + TMEM owner, 2-5 = epilogue
+// (TMEM -> registers -> global), 6-13 = unpack.  All mbarrier waits are bounded.
+#include "b2g_formats.cuh"
+
+namespace b2g {
+int iq2xxs_grid(const uint2** out);
+
+namespace qg {
+
+constexpr int kFwd = 0, kDgrad = 1;
+constexpr int kBM = 128;          // rows per MMA
+constexpr int kBN = 256;          // output columns per tile
+constexpr int kBK = 64;           // reduction step
+constexpr int kATile = kBM * kBK * 2;       // 16384
+constexpr int kBStage = kBN * kBK * 2;      // 32768
+constexpr int kBStages = 2;
+constexpr int kUnpackWarps = 8;
+constexpr int kThreads = 32 * (6 + kUnpackWarps);
+constexpr int kLoraATile = kBM * 32;        // [128 x 16] bf16
+constexpr int kLoraBTile = kBN * 32;        // 8192 either way
+constexpr int kTmemCols = 512;
+
+// Packed-stage geometry: what one reduction step needs of the packed weight, as TMA boxes over the
+// payload viewed as uint32 [rows, pitch/4].  x coordinates are always multiples of 4 words (16 bytes).
+template <int QT, int MODE> struct Packed;
+// Q4_K forward: header (d, dmin, 12 scale bytes) + the 32 nibble bytes of one 64-value pair, as
+// three [256 rows x 16 B] boxes so that each thread reads its row with conflict-free 16-byte loads.
+template <> struct Packed<B2G_Q4_K, kFwd> { static constexpr int kBoxWords = 4, kBoxRows = 256, kBoxes = 3, kBytes = 3 * 4096; };
+// Q4_K dgrad: whole 144-byte super-blocks of 64 rows (row stride 144 B: conflict-free 16-byte loads).
+template <> struct Packed<B2G_Q4_K, kDgrad> { static constexpr int kBoxWords = 36, kBoxRows = 64, kBoxes = 1, kBytes = 64 * 144; };
+// Q8_0 forward: two 34-byte blocks start at byte 68*step; an 80-byte window from the 16-byte boundary below covers them
+// (the start is at most 12 bytes into the window).
+template <> struct Packed<B2G_Q8_0, kFwd> { static constexpr int kBoxWords = 20, kBoxRows = 256, kBoxes = 1, kBytes = 256 * 80; };
+// Q8_0 dgrad: eight blocks (272 B = 17 x 16) per row.
+template <> struct Packed<B2G_Q8_0, kDgrad> { static constexpr int kBoxWords = 68, kBoxRows = 64, kBoxes = 1, kBytes = 64 * 272; };
+// IQ2_XXS: 66-byte super-blocks are not 16-byte aligned; an 80-byte window from the boundary below covers one
+// (the start is at most 14 bytes into the window).
+template <> struct Packed<B2G_IQ2_XXS, kFwd> { static constexpr int kBoxWords = 20, kBoxRows = 256, kBoxes = 1, kBytes = 256 * 80; };
+template <> struct Packed<B2G_IQ2_XXS, kDgrad> { static constexpr int kBoxWords = 20, kBoxRows = 64, kBoxes = 1, kBytes = 64 * 80; };
+
+template <int QT, int MODE, int MT>
+struct Cfg {
+  using P = Packed<QT, MODE>;
+  static constexpr int kAStages = MT == 1 ? 4 : 3;
+  static constexpr int kAStage = MT * kATile;
+  static constexpr int kPStages = (P::kBytes > 16384 && MT == 2) ? 2 : 3;
+  static constexpr int kPStage = (P::kBytes + 1023) / 1024 * 1024;
+  static constexpr int kAccBufs = MT == 1 ? 2 : 1;
+  // shared-memory map (offsets from a 1024-byte aligned base)
+  static constexpr int kOffA = 0;
+  static constexpr int kOffB = kOffA + kAStages * kAStage;
+  static constexpr int kOffP = kOffB + kBStages * kBStage;
+  static constexpr int kOffLA = kOffP + kPStages * kPStage;
+  static constexpr int kOffLB = kOffLA + MT * kLoraATile;
+  static constexpr int kOffGrid = kOffLB + kLoraBTile;                      // IQ2_XXS table (2 KB)
+  static constexpr int kOffBar = kOffGrid + (QT == B2G_IQ2_XXS ? 2048 : 0);
+  static constexpr int kNumBars = 2 * kAStages + 2 * kBStages + 2 * kPStages + 2 + 2 * kAccBufs;
+  static constexpr int kOffMisc = kOffBar + kNumBars * 8;                   // tmem slot, abort flag
+  static constexpr int kSmemBytes = kOffMisc + 16 + 1024;                   // + alignment slack
+  static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
+};
+
+struct Params {
+  int m_total;        // activation rows (M, or all routed rows R)
+  int n;              // W rows per expert and per payload
+  int k;              // W logical columns
+  int nseg;           // payload tensors (1, or 2 for gate|up)
+  int num_ct;         // output column tiles
+  int ct_per_seg;     // forward: column tiles per payload
+  int num_iters;      // reduction steps per tile
+  int iters_per_seg;  // dgrad: steps per payload
+  int dense_m_tiles;  // dense only
+  int has_lora;
+  int lora_rows;      // forward: rows per expert of the padded LoRA-B tensor
+  int ldc;
+  const int4* tiles;  // grouped: [0] = {count, rows_per_tile, ..}, [1..] = {expert, row0, rows, _}
+  __nv_bfloat16* out0;
+  __nv_bfloat16* out1;
+  const __nv_bfloat16* bias;
+  const uint2* grid;  // IQ2_XXS table in global memory
+  int* status;
+};
+
+struct Tile { int expert, row0, rows, ct; };
+
+template <int MT>
+__device__ __forceinline__ int num_m_tiles(const Params& p) { return p.tiles ? p.tiles[0].x : p.dense_m_tiles; }
+
+template <int MT>
+__device__ __forceinline__ Tile get_tile(const Params& p, int item) {
+  Tile t;
+  const int mt = item / p.num_ct;
+  t.ct = item - mt * p.num_ct;
+  if (p.tiles) {
+    const int4 e = p.tiles[1 + mt];
+    t.expert = e.x; t.row0 = e.y; t.rows = e.z;
+  } else {
+    t.expert = 0; t.row0 = mt * (kBM * MT);
+    const int left = p.m_total - t.row0;
+    t.rows = left < kBM * MT ? left : kBM * MT;
+  }
+  return t;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Row decoders: 64 consecutive values of one W row -> 32 packed bf16 pairs, out[4*c + i] being values
+// 8c+2i and 8c+2i+1 (chunk c = one 16-byte shared-memory vector).
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void q4k_row64(const uint4 hdr, const uint4 qa, const uint4 qb, int pair, uint32_t (&out)[32]) {
+  uint32_t sc0, mn0, sc1, mn1;
+  fmt::q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * pair, sc0, mn0);
+  fmt::q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * pair + 1, sc1, mn1);
+  const float d = dev::half_bits_to_float(hdr.x), dmin = dev::half_bits_to_float(hdr.x >> 16);
+  const float dsc0 = __fmul_rn(d, static_cast<float>(sc0)), ndm0 = -__fmul_rn(dmin, static_cast<float>(mn0));
+  const float dsc1 = __fmul_rn(d, static_cast<float>(sc1)), ndm1 = -__fmul_rn(dmin, static_cast<float>(mn1));
+  const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t lo = w[i] & 0x0F0F0F0Fu, hi = (w[i] >> 4) & 0x0F0F0F0Fu;
+    // word i holds bytes 4i..4i+3: low nibbles are values 4i.., high nibbles values 32+4i..
+    out[2 * i] = dev::pack_bf16(__fmaf_rn(dsc0, fmt::byte_to_float(lo, 0), ndm0), __fmaf_rn(dsc0, fmt::byte_to_float(lo, 1), ndm0));
+    out[2 * i + 1] = dev::pack_bf16(__fmaf_rn(dsc0, fmt::byte_to_float(lo, 2), ndm0), __fmaf_rn(dsc0, fmt::byte_to_float(lo, 3), ndm0));
+    out[16 + 2 * i] = dev::pack_bf16(__fmaf_rn(dsc1, fmt::byte_to_float(hi, 0), ndm1), __fmaf_rn(dsc1, fmt::byte_to_float(hi, 1), ndm1));
+    out[16 + 2 * i + 1] = dev::pack_bf16(__fmaf_rn(dsc1, fmt::byte_to_float(hi, 2), ndm1), __fmaf_rn(dsc1, fmt::byte_to_float(hi, 3), ndm1));
+  }
+}
+
+// int8 (already XOR 0x80 per byte) at byte i of `word` -> exact float
+__device__ __forceinline__ float sbyte_to_float(uint32_t word_x80, int i) {
+  const uint32_t magic = __byte_perm(word_x80, 0x4B000000u, 0x7540u + i);
+  return __uint_as_float(magic) - 8388736.0f;  // 2^23 + 128
+}
+
+// Two consecutive Q8_0 blocks (68 bytes) given as 17 words starting at the first block's scale.
+__device__ __forceinline__ void q8_row64(const uint32_t (&w)[17], uint32_t (&out)[32]) {
+  const float d0 = dev::half_bits_to_float(w[0]);        // bytes 0-1
+  const float d1 = dev::half_bits_to_float(w[8] >> 16);  // bytes 34-35
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    // block 0, values 8c..8c+7 live at bytes 2+8c..9+8c: straddle three words
+    const uint32_t a = __byte_perm(w[2 * c], w[2 * c + 1], 0x5432) ^ 0x80808080u;
+    const uint32_t b = __byte_perm(w[2 * c + 1], w[2 * c + 2], 0x5432) ^ 0x80808080u;
+    out[4 * c + 0] = dev::pack_bf16(__fmul_rn(sbyte_to_float(a, 0), d0), __fmul_rn(sbyte_to_float(a, 1), d0));
+    out[4 * c + 1] = dev::pack_bf16(__fmul_rn(sbyte_to_float(a, 2), d0), __fmul_rn(sbyte_to_float(a, 3), d0));
+    out[4 * c + 2] = dev::pack_bf16(__fmul_rn(sbyte_to_float(b, 0), d0), __fmul_rn(sbyte_to_float(b, 1), d0));
+    out[4 * c + 3] = dev::pack_bf16(__fmul_rn(sbyte_to_float(b, 2), d0), __fmul_rn(sbyte_to_float(b, 3), d0));
+    // block 1, values at bytes 36+8c..: word aligned
+    const uint32_t e = w[9 + 2 * c] ^ 0x80808080u, f = w[10 + 2 * c] ^ 0x80808080u;
+    out[16 + 4 * c + 0] = dev::pack_bf16(__fmul_rn(sbyte_to_float(e, 0), d1), __fmul_rn(sbyte_to_float(e, 1), d1));
+    out[16 + 4 * c + 1] = dev::pack_bf16(__fmul_rn(sbyte_to_float(e, 2), d1), __fmul_rn(sbyte_to_float(e, 3), d1));
+    out[16 + 4 * c + 2] = dev::pack_bf16(__fmul_rn(sbyte_to_float(f, 0), d1), __fmul_rn(sbyte_to_float(f, 1), d1));
+    out[16 + 4 * c + 3] = dev::pack_bf16(__fmul_rn(sbyte_to_float(f, 2), d1), __fmul_rn(sbyte_to_float(f, 3), d1));
+  }
+}
+
+// Read `N` words starting at byte offset `off` (a multiple of 4, < 16) of a 16-byte aligned row.
+template <int N>
+__device__ __forceinline__ void load_words_shifted(const uint8_t* row16, int off, uint32_t (&w)[N]) {
+  constexpr int kVec = (N + 3 + 3) / 4;  // enough 16-byte vectors for any shift
+  uint32_t raw[kVec * 4];
+#pragma unroll
+  for (int v = 0; v < kVec; ++v) {
+    const uint4 q = *reinterpret_cast<const uint4*>(row16 + 16 * v);
+    raw[4 * v] = q.x; raw[4 * v + 1] = q.y; raw[4 * v + 2] = q.z; raw[4 * v + 3] = q.w;
+  }
+  const int s = off >> 2;  // warp-uniform
+  if (s == 0) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) w[i] = raw[i];
+  } else if (s == 1) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) w[i] = raw[i + 1];
+  } else if (s == 2) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) w[i] = raw[i + 2];
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i) w[i] = raw[i + 3];
+  }
+}
+
+// IQ2_XXS: 64 values = two 8-byte groups.  `g` = the 4 words {idx_lo, signs_lo, idx_hi, signs_hi}.
+__device__ __forceinline__ void iq2_row64(float d, const uint32_t (&g)[4], const uint2* __restrict__ grid_s, uint32_t (&out)[32]) {
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint32_t idx4 = g[2 * h], word = g[2 * h + 1];
+    const float db = __fmul_rn(__fmul_rn(d, 0.5f + static_cast<float>(word >> 28)), 0.25f);
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      const uint2 mag = grid_s[(idx4 >> (8 * s)) & 255u];
+      const uint32_t sg = fmt::iq2_sign_byte((word >> (7 * s)) & 127u);
+      float v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float m = __fmul_rn(db, fmt::byte_to_float(i < 4 ? mag.x : mag.y, i & 3));
+        v[i] = __uint_as_float(__float_as_uint(m) ^ (((sg >> i) & 1u) << 31));
+      }
+      const int c = 4 * h + s;
+      out[4 * c + 0] = dev::pack_bf16(v[0], v[1]);
+      out[4 * c + 1] = dev::pack_bf16(v[2], v[3]);
+      out[4 * c + 2] = dev::pack_bf16(v[4], v[5]);
+      out[4 * c + 3] = dev::pack_bf16(v[6], v[7]);
+    }
+  }
+}
+
+// Unpack the 64 values this thread owns for reduction step `it` from packed stage `pk`.
+//   forward: thread = W row (0..255), the step selects which 64 of the row's values
+//   dgrad  : thread = (W row 0..63, quarter 0..3 of the 256-value column tile `ct`)
+template <int QT, int MODE>
+__device__ __forceinline__ void unpack_row(const uint8_t* pk, int tid, int it, int ct, const uint2* grid_s, uint32_t (&out)[32]) {
+  if constexpr (QT == B2G_Q4_K) {
+    if constexpr (MODE == kFwd) {
+      const uint4 hdr = *reinterpret_cast<const uint4*>(pk + tid * 16);
+      const uint4 qa = *reinterpret_cast<const uint4*>(pk + 4096 + tid * 16);
+      const uint4 qb = *reinterpret_cast<const uint4*>(pk + 8192 + tid * 16);
+      q4k_row64(hdr, qa, qb, it & 3, out);
+    } else {
+      const int row = tid & 63, pair = tid >> 6;
+      const uint8_t* r = pk + row * 144;
+      const uint4 hdr = *reinterpret_cast<const uint4*>(r);
+      const uint4 qa = *reinterpret_cast<const uint4*>(r + 16 + 32 * pair);
+      const uint4 qb = *reinterpret_cast<const uint4*>(r + 32 + 32 * pair);
+      q4k_row64(hdr, qa, qb, pair, out);
+    }
+  } else if constexpr (QT == B2G_Q8_0) {
+    uint32_t w[17];
+    if constexpr (MODE == kFwd) {
+      load_words_shifted<17>(pk + tid * 80, (68 * it) & 15, w);
+    } else {
+      const int row = tid & 63, pair = tid >> 6;   // byte 68*pair of the 272-byte row
+      load_words_shifted<17>(pk + row * 272 + ((68 * pair) & ~15), (68 * pair) & 15, w);
+    }
+    q8_row64(w, out);
+  } else {
+    // 66-byte super-block inside an 80-byte window; `off` (even) is where it starts.
+    const int sb = MODE == kFwd ? (it >> 2) : ct;
+    const int pair = MODE == kFwd ? (it & 3) : (tid >> 6);
+    const int row = MODE == kFwd ? tid : (tid & 63);
+    const int off = (66 * sb) & 15;
+    const unsigned short* h = reinterpret_cast<const unsigned short*>(pk + row * 80 + off);
+    const float d = dev::half_bits_to_float(h[0]);
+    const unsigned short* q = h + 1 + 8 * pair;  // 16 bytes: two groups
+    uint32_t g[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) g[i] = static_cast<uint32_t>(q[2 * i]) | (static_cast<uint32_t>(q[2 * i + 1]) << 16);
+    iq2_row64(d, g, grid_s, out);
+  }
+}
+
+template <int QT, int MODE, int MT>
+__global__ void __launch_bounds__(kThreads, 1)
+qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_a1,
+             const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1,
+             const __grid_constant__ CUtensorMap tm_la, const __grid_constant__ CUtensorMap tm_lb) {
+  using C = Cfg<QT, MODE, MT>;
+  using P = Packed<QT, MODE>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const uint32_t sbase = dev::smem_u32(smem);
+  const uint32_t sA = sbase + C::kOffA, sB = sbase + C::kOffB, sP = sbase + C::kOffP;
+  const uint32_t sLA = sbase + C::kOffLA, sLB = sbase + C::kOffLB;
+  const uint32_t bars = sbase + C::kOffBar;
+  // barrier indices
+  constexpr int kFullA = 0, kEmptyA = kFullA + C::kAStages, kFullB = kEmptyA + C::kAStages, kEmptyB = kFullB + kBStages,
+                kFullP = kEmptyB + kBStages, kEmptyP = kFullP + C::kPStages, kFullL = kEmptyP + C::kPStages, kEmptyL = kFullL + 1,
+                kAccFull = kEmptyL + 1, kAccEmpty = kAccFull + C::kAccBufs;
+  auto bar = [&](int i) { return bars + 8u * i; };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + C::kOffMisc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::kOffMisc + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < C::kAStages; ++i) { dev::mbar_init(bar(kFullA + i), 1); dev::mbar_init(bar(kEmptyA + i), 1); }
+    for (int i = 0; i < kBStages; ++i) { dev::mbar_init(bar(kFullB + i), kUnpackWarps); dev::mbar_init(bar(kEmptyB + i), 1); }
+    for (int i = 0; i < C::kPStages; ++i) { dev::mbar_init(bar(kFullP + i), 1); dev::mbar_init(bar(kEmptyP + i), kUnpackWarps); }
+    dev::mbar_init(bar(kFullL), 1);
+    dev::mbar_init(bar(kEmptyL), 1);
+    for (int i = 0; i < C::kAccBufs; ++i) { dev::mbar_init(bar(kAccFull + i), 1); dev::mbar_init(bar(kAccEmpty + i), 4); }
+    *abort_flag = 0;
+    dev::fence_barrier_init();
+    dev::fence_proxy_async_smem();
+    dev::prefetch_tmap(&tm_a0);
+    dev::prefetch_tmap(&tm_w0);
+  }
+  if constexpr (QT == B2G_IQ2_XXS) {
+    uint2* gs = reinterpret_cast<uint2*>(smem + C::kOffGrid);
+    for (int i = threadIdx.x; i < 256; i += kThreads) gs[i] = p.grid[i];
+  }
+  if (warp == 1) {
+    dev::tmem_alloc(dev::smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
+    dev::tmem_relinquish();
+  }
+  dev::tc_fence_before();
+  __syncthreads();
+  dev::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_items = num_m_tiles<MT>(p) * p.num_ct;
+
+  if (warp == 0) {
+    // ============================== TMA producer ==============================
+    if (lane == 0) {
+      int sa = 0, pa = 0, sp = 0, pp = 0, pl = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+        const Tile t = get_tile<MT>(p, item);
+        const int nmt = (MT == 2 && t.rows > kBM) ? 2 : 1;
+        int fseg = 0, col0 = 0;
+        if (MODE == kFwd) { fseg = t.ct / p.ct_per_seg; col0 = (t.ct - fseg * p.ct_per_seg) * kBN; }
+        else col0 = t.ct * kBN;
+        if (p.has_lora) {
+          ok = dev::mbar_wait(bar(kEmptyL), pl ^ 1, abort_flag, p.status, 101);
+          if (!ok) break;
+          dev::mbar_arrive_expect_tx(bar(kFullL), nmt * kLoraATile + kLoraBTile);
+          for (int m = 0; m < nmt; ++m) dev::tma_load_2d(sLA + m * kLoraATile, &tm_la, bar(kFullL), 0, t.row0 + m * kBM);
+          if (MODE == kFwd) {
+            dev::tma_load_2d(sLB, &tm_lb, bar(kFullL), 0, t.expert * p.lora_rows + fseg * p.n + col0);
+          } else {
+            for (int i = 0; i < 4; ++i) dev::tma_load_2d(sLB + i * 2048, &tm_lb, bar(kFullL), col0 + 64 * i, t.expert * 16);
+          }
+          pl ^= 1;
+        }
+        for (int it = 0; it < p.num_iters; ++it) {
+          int seg = fseg, red0 = it * kBK;
+          if (MODE == kDgrad) { seg = it / p.iters_per_seg; red0 = (it - seg * p.iters_per_seg) * kBK; }
+          ok = dev::mbar_wait(bar(kEmptyA + sa), pa ^ 1, abort_flag, p.status, 102);
+          if (!ok) break;
+          dev::mbar_arrive_expect_tx(bar(kFullA + sa), nmt * kATile);
+          const CUtensorMap* am = (MODE == kDgrad && seg) ? &tm_a1 : &tm_a0;
+          for (int m = 0; m < nmt; ++m)
+            dev::tma_load_2d(sA + sa * C::kAStage + m * kATile, am, bar(kFullA + sa), red0, t.row0 + m * kBM);
+          if (++sa == C::kAStages) { sa = 0; pa ^= 1; }
+
+          ok = dev::mbar_wait(bar(kEmptyP + sp), pp ^ 1, abort_flag, p.status, 103);
+          if (!ok) break;
+          dev::mbar_arrive_expect_tx(bar(kFullP + sp), P::kBytes);
+          const CUtensorMap* wm = seg ? &tm_w1 : &tm_w0;
+          const uint32_t dst = sP + sp * C::kPStage;
+          if (MODE == kFwd) {
+            const int y = t.expert * p.n + col0;
+            if (QT == B2G_Q4_K) {
+              const int xb = 36 * (it >> 2), xq = xb + 4 + 8 * (it & 3);
+              dev::tma_load_2d(dst, wm, bar(kFullP + sp), xb, y);
+              dev::tma_load_2d(dst + 4096, wm, bar(kFullP + sp), xq, y);
+              dev::tma_load_2d(dst + 8192, wm, bar(kFullP + sp), xq + 4, y);
+            } else if (QT == B2G_Q8_0) {
+              dev::tma_load_2d(dst, wm, bar(kFullP + sp), ((68 * it) & ~15) >> 2, y);
+            } else {
+              dev::tma_load_2d(dst, wm, bar(kFullP + sp), ((66 * (it >> 2)) & ~15) >> 2, y);
+            }
+          } else {
+            const int y = t.expert * p.n + red0;
+            if (QT == B2G_Q4_K) dev::tma_load_2d(dst, wm, bar(kFullP + sp), 36 * t.ct, y);
+            else if (QT == B2G_Q8_0) dev::tma_load_2d(dst, wm, bar(kFullP + sp), 68 * t.ct, y);
+            else dev::tma_load_2d(dst, wm, bar(kFullP + sp), ((66 * t.ct) & ~15) >> 2, y);
+          }
+          if (++sp == C::kPStages) { sp = 0; pp ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ============================== MMA issuer ==============================
+    if (lane == 0) {
+      constexpr uint32_t idesc = dev::make_idesc_bf16(kBM, kBN, 0, MODE == kDgrad ? 1 : 0);
+      int sa = 0, pa = 0, sb = 0, pb = 0, pl = 0, ab = 0, pacc = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+        const Tile t = get_tile<MT>(p, item);
+        const int nmt = (MT == 2 && t.rows > kBM) ? 2 : 1;
+        ok = dev::mbar_wait(bar(kAccEmpty + ab), pacc ^ 1, abort_flag, p.status, 201);
+        if (!ok) break;
+        dev::tc_fence_after();
+        const uint32_t acc = tmem_base + (C::kAccBufs == 2 ? ab * kBN : 0);
+        for (int it = 0; it < p.num_iters; ++it) {
+          ok = dev::mbar_wait(bar(kFullA + sa), pa, abort_flag, p.status, 202) &&
+               dev::mbar_wait(bar(kFullB + sb), pb, abort_flag, p.status, 203);
+          if (!ok) break;
+          dev::tc_fence_after();
+          const uint32_t a_base = sA + sa * C::kAStage, b_base = sB + sb * kBStage;
+#pragma unroll
+          for (int k16 = 0; k16 < 4; ++k16) {
+            const uint64_t bdesc = MODE == kFwd ? dev::make_smem_desc(b_base + k16 * 32, 16, 1024, 2)
+                                                : dev::make_smem_desc(b_base + k16 * 2048, 8192, 1024, 2);
+            for (int m = 0; m < nmt; ++m) {
+              const uint64_t adesc = dev::make_smem_desc(a_base + m * kATile + k16 * 32, 16, 1024, 2);
+              dev::umma_bf16(acc + m * kBN, adesc, bdesc, idesc, (it | k16) != 0 ? 1u : 0u);
+            }
+          }
+          dev::umma_commit(bar(kEmptyA + sa));
+          dev::umma_commit(bar(kEmptyB + sb));
+          if (++sa == C::kAStages) { sa = 0; pa ^= 1; }
+          if (++sb == kBStages) { sb = 0; pb ^= 1; }
+        }
+        if (!ok) break;
+        if (p.has_lora) {
+          ok = dev::mbar_wait(bar(kFullL), pl, abort_flag, p.status, 204);
+          if (!ok) break;
+          dev::tc_fence_after();
+          const uint64_t bdesc = MODE == kFwd ? dev::make_smem_desc(sLB, 16, 256, 6) : dev::make_smem_desc(sLB, 2048, 1024, 2);
+          for (int m = 0; m < nmt; ++m) {
+            const uint64_t adesc = dev::make_smem_desc(sLA + m * kLoraATile, 16, 256, 6);
+            dev::umma_bf16(acc + m * kBN, adesc, bdesc, idesc, 1u);
+          }
+          dev::umma_commit(bar(kEmptyL));
+          pl ^= 1;
+        }
+        dev::umma_commit(bar(kAccFull + ab));
+        if (++ab == C::kAccBufs) { ab = 0; pacc ^= 1; }
+      }
+    }
+  } else if (warp < 6) {
+    // ============================== epilogue ==============================
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int ab = 0, pacc = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+      const Tile t = get_tile<MT>(p, item);
+      const int nmt = (MT == 2 && t.rows > kBM) ? 2 : 1;
+      int seg = 0, col0;
+      if (MODE == kFwd) { seg = t.ct / p.ct_per_seg; col0 = (t.ct - seg * p.ct_per_seg) * kBN; }
+      else col0 = t.ct * kBN;
+      const int ncols = MODE == kFwd ? p.n : p.k;
+      __nv_bfloat16* outp = seg ? p.out1 : p.out0;
+      ok = dev::mbar_wait(bar(kAccFull + ab), pacc, abort_flag, p.status, 301);
+      if (!ok) break;
+      dev::tc_fence_after();
+      const uint32_t acc = tmem_base + (C::kAccBufs == 2 ? ab * kBN : 0) + (static_cast<uint32_t>(q * 32) << 16);
+      const bool vec_ok = (p.ldc & 7) == 0;
+      for (int m = 0; m < nmt; ++m) {
+        const int row_local = m * kBM + q * 32 + lane;
+        const bool row_ok = row_local < t.rows;
+        __nv_bfloat16* orow = outp + static_cast<int64_t>(t.row0 + row_local) * p.ldc;
+#pragma unroll 1
+        for (int c = 0; c < kBN / 32; ++c) {
+          uint32_t r[32];
+          dev::tmem_ld_32x32(acc + m * kBN + c * 32, r);
+          dev::tmem_ld_wait();
+          const int cbase = col0 + c * 32;
+          if (row_ok && cbase < ncols) {
+            if (MODE == kFwd && p.bias) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (cbase + i < ncols) r[i] = __float_as_uint(__uint_as_float(r[i]) + __bfloat162float(p.bias[cbase + i]));
+            }
+            if (vec_ok && cbase + 32 <= ncols) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint4 o;
+                o.x = dev::pack_bf16(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                o.y = dev::pack_bf16(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                o.z = dev::pack_bf16(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                o.w = dev::pack_bf16(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                *reinterpret_cast<uint4*>(orow + cbase + 8 * v) = o;
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (cbase + i < ncols) orow[cbase + i] = __float2bfloat16_rn(__uint_as_float(r[i]));
+            }
+          }
+        }
+      }
+      dev::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) dev::mbar_arrive(bar(kAccEmpty + ab));
+      if (++ab == C::kAccBufs) { ab = 0; pacc ^= 1; }
+    }
+  } else {
+    // ============================== unpack ==============================
+    const int tid = threadIdx.x - 6 * 32;  // 0..255
+    const uint2* grid_s = reinterpret_cast<const uint2*>(smem + C::kOffGrid);
+    int sp = 0, pp = 0, sb = 0, pb = 0;
+    bool ok = true;
+    // destination of this thread's 128-byte row inside a B stage
+    const int drow = MODE == kFwd ? tid : (tid & 63);
+    const uint32_t doff = (MODE == kFwd ? 0u : static_cast<uint32_t>(tid >> 6) * 8192u) + static_cast<uint32_t>(drow) * 128u;
+    const uint32_t sw = static_cast<uint32_t>(drow & 7);
+    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+      const int ct = item % p.num_ct;
+      for (int it = 0; it < p.num_iters; ++it) {
+        ok = dev::mbar_wait(bar(kFullP + sp), pp, abort_flag, p.status, 401);
+        if (!ok) break;
+        uint32_t out[32];
+        unpack_row<QT, MODE>(smem + C::kOffP + sp * C::kPStage, tid, it, ct, grid_s, out);
+        __syncwarp();
+        if (lane == 0) dev::mbar_arrive(bar(kEmptyP + sp));
+        if (++sp == C::kPStages) { sp = 0; pp ^= 1; }
+        ok = dev::mbar_wait(bar(kEmptyB + sb), pb ^ 1, abort_flag, p.status, 402);
+        if (!ok) break;
+        uint8_t* dst = smem + C::kOffB + sb * kBStage + doff;
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          *reinterpret_cast<uint4*>(dst + ((static_cast<uint32_t>(c) ^ sw) << 4)) =
+              make_uint4(out[4 * c], out[4 * c + 1], out[4 * c + 2], out[4 * c + 3]);
+        dev::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) dev::mbar_arrive(bar(kFullB + sb));
+        if (++sb == kBStages) { sb = 0; pb ^= 1; }
+      }
+    }
+  }
+
+  dev::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    dev::tc_fence_after();
+    dev::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------------
+struct Launch {
+  int qtype, mode;
+  const void *a0, *a1;        // activations [m_total, red_dim]
+  const void *w0, *w1;        // payloads
+  const void *la, *lb;        // LoRA operands
+  int64_t m_total, n, k;
+  int num_experts;
+  const int32_t* tiles;       // nullptr = dense
+  int64_t lora_rows;
+  void *out0, *out1;
+  const void* bias;
+  int* status;
+  cudaStream_t stream;
+};
+
+template <int QT, int MODE, int MT>
+int launch_impl(const Launch& L) {
+  using C = Cfg<QT, MODE, MT>;
+  using P = Packed<QT, MODE>;
+  Params p{};
+  p.m_total = (int)L.m_total; p.n = (int)L.n; p.k = (int)L.k;
+  p.nseg = L.w1 ? 2 : 1;
+  const int red_cols = MODE == kFwd ? p.k : p.n;  // width of the activation operand
+  if (MODE == kFwd) {
+    p.ct_per_seg = (p.n + kBN - 1) / kBN;
+    p.num_ct = p.nseg * p.ct_per_seg;
+    p.num_iters = p.k / kBK;
+    p.iters_per_seg = p.num_iters;
+    p.ldc = p.n;
+  } else {
+    p.ct_per_seg = p.k / kBN;
+    p.num_ct = p.k / kBN;
+    p.iters_per_seg = (p.n + kBK - 1) / kBK;
+    p.num_iters = p.nseg * p.iters_per_seg;
+    p.ldc = p.k;
+  }
+  p.dense_m_tiles = (int)((L.m_total + kBM * MT - 1) / (kBM * MT));
+  p.has_lora = L.la != nullptr;
+  p.lora_rows = (int)L.lora_rows;
+  p.tiles = reinterpret_cast<const int4*>(L.tiles);
+  p.out0 = static_cast<__nv_bfloat16*>(L.out0);
+  p.out1 = static_cast<__nv_bfloat16*>(L.out1);
+  p.bias = static_cast<const __nv_bfloat16*>(L.bias);
+  p.status = L.status;
+  p.grid = nullptr;
+  if (QT == B2G_IQ2_XXS) {
+    int rc = iq2xxs_grid(&p.grid);
+    if (rc) return rc;
+  }
+
+  CUtensorMap tm_a0, tm_a1, tm_w0, tm_w1, tm_la, tm_lb;
+  int rc;
+  const uint64_t a_pitch = (uint64_t)red_cols * 2;
+  if ((rc = make_tmap_2d(&tm_a0, L.a0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, red_cols, L.m_total, a_pitch, kBK, kBM,
+                         CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  tm_a1 = tm_a0;
+  if (L.a1 && (rc = make_tmap_2d(&tm_a1, L.a1, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, red_cols, L.m_total, a_pitch, kBK, kBM,
+                                 CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  const uint64_t w_pitch = (uint64_t)fmt::row_bytes(QT, L.k);
+  const uint64_t w_rows = (uint64_t)L.num_experts * L.n;
+  if ((rc = make_tmap_2d(&tm_w0, L.w0, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, w_pitch / 4, w_rows, w_pitch, P::kBoxWords, P::kBoxRows,
+                         CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
+  tm_w1 = tm_w0;
+  if (L.w1 && (rc = make_tmap_2d(&tm_w1, L.w1, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, w_pitch / 4, w_rows, w_pitch, P::kBoxWords,
+                                 P::kBoxRows, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
+  tm_la = tm_a0; tm_lb = tm_a0;
+  if (p.has_lora) {
+    if ((rc = make_tmap_2d(&tm_la, L.la, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 16, L.m_total, 32, 16, kBM,
+                           CU_TENSOR_MAP_SWIZZLE_32B))) return rc;
+    if (MODE == kFwd) {
+      if ((rc = make_tmap_2d(&tm_lb, L.lb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 16, (uint64_t)L.num_experts * L.lora_rows, 32, 16,
+                             kBN, CU_TENSOR_MAP_SWIZZLE_32B))) return rc;
+    } else {
+      if ((rc = make_tmap_2d(&tm_lb, L.lb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, L.k, (uint64_t)L.num_experts * 16, (uint64_t)L.k * 2,
+                             64, 16, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+    }
+  }
+
+  auto kern = qgemm_kernel<QT, MODE, MT>;
+  B2G_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+  int grid = sm_count();
+  if (!L.tiles) {
+    const int64_t items = (int64_t)p.dense_m_tiles * p.num_ct;
+    if (items < grid) grid = (int)items;
+  }
+  if (grid < 1) return 0;
+  kern<<<grid, kThreads, C::kSmemBytes, L.stream>>>(p, tm_a0, tm_a1, tm_w0, tm_w1, tm_la, tm_lb);
+  B2G_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// Rows per M-block: two 128-row MMAs share every unpacked weight tile.
+constexpr int kMT = 2;
+
+template <int MODE>
+int launch_mode(const Launch& L) {
+  switch (L.qtype) {
+    case B2G_Q4_K: return launch_impl<B2G_Q4_K, MODE, kMT>(L);
+    case B2G_Q8_0: return launch_impl<B2G_Q8_0, MODE, kMT>(L);
+    case B2G_IQ2_XXS: return launch_impl<B2G_IQ2_XXS, MODE, kMT>(L);
+    default: return fail(B2G_E_ARG, "unsupported GGUF type id %d (supported: 8 Q8_0, 12 Q4_K, 16 IQ2_XXS)", L.qtype);
+  }
+}
+
+int check_common(const Launch& L, const char* what) {
+  B2G_REQUIRE(L.m_total >= 0 && L.n > 0 && L.k > 0, "%s: bad shape M=%lld N=%lld K=%lld", what, (long long)L.m_total,
+              (long long)L.n, (long long)L.k);
+  B2G_REQUIRE(L.k % 256 == 0, "%s: K=%lld must be a multiple of 256", what, (long long)L.k);
+  B2G_REQUIRE(L.m_total < (1ll << 31) && (int64_t)L.num_experts * L.n < (1ll << 31), "%s: shape too large", what);
+  B2G_REQUIRE(L.a0 && L.w0 && L.out0, "%s: null pointer", what);
+  B2G_REQUIRE((L.la == nullptr) == (L.lb == nullptr), "%s: the two LoRA operands come together", what);
+  return 0;
+}
+
+// ---- grouped tile table ------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) schedule_kernel(const int64_t* __restrict__ expert_indices, const int32_t* __restrict__ offsets,
+                                                       int G, int rows_per_tile, int4* __restrict__ tiles) {
+  __shared__ int scan[256];
+  __shared__ int carry;
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  for (int g0 = 0; g0 < G; g0 += 256) {
+    const int g = g0 + threadIdx.x;
+    int begin = 0, rows = 0;
+    if (g < G) {
+      begin = g > 0 ? offsets[g - 1] : 0;
+      rows = offsets[g] - begin;
+      if (rows < 0) rows = 0;
+    }
+    const int nt = (rows + rows_per_tile - 1) / rows_per_tile;
+    scan[threadIdx.x] = nt;
+    __syncthreads();
+    for (int off = 1; off < 256; off <<= 1) {
+      const int add = threadIdx.x >= off ? scan[threadIdx.x - off] : 0;
+      __syncthreads();
+      scan[threadIdx.x] += add;
+      __syncthreads();
+    }
+    const int first = carry + scan[threadIdx.x] - nt;
+    if (g < G) {
+      const int e = static_cast<int>(expert_indices[g]);
+      for (int i = 0; i < nt; ++i) {
+        const int r0 = begin + i * rows_per_tile;
+        const int left = rows - i * rows_per_tile;
+        tiles[1 + first + i] = make_int4(e, r0, left < rows_per_tile ? left : rows_per_tile, g);
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 255) carry += scan[255];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) tiles[0] = make_int4(carry, rows_per_tile, G, 0);
+}
+
+}  // namespace qg
+}  // namespace b2g
+
+using namespace b2g;
+
+extern "C" int b2g_qlinear_fwd(int qtype, const void* x, const void* payload, const void* bias, const void* xas, const void* lora_b16,
+                               void* y, int64_t M, int64_t N, int64_t K, int* status, void* stream) {
+  qg::Launch L{};
+  L.qtype = qtype; L.mode = qg::kFwd; L.a0 = x; L.w0 = payload; L.la = xas; L.lb = lora_b16;
+  L.m_total = M; L.n = N; L.k = K; L.num_experts = 1; L.lora_rows = N; L.out0 = y; L.bias = bias; L.status = status;
+  L.stream = static_cast<cudaStream_t>(stream);
+  int rc = qg::check_common(L, "qlinear_fwd");
+  if (rc) return rc;
+  if (M == 0) return 0;
+  return qg::launch_mode<qg::kFwd>(L);
+}
+
+extern "C" int b2g_qlinear_dgrad(int qtype, const void* dy, const void* payload, const void* dybs, const void* lora_a16, void* dx,
+                                 int64_t M, int64_t N, int64_t K, int* status, void* stream) {
+  qg::Launch L{};
+  L.qtype = qtype; L.mode = qg::kDgrad; L.a0 = dy; L.w0 = payload; L.la = dybs; L.lb = lora_a16;
+  L.m_total = M; L.n = N; L.k = K; L.num_experts = 1; L.lora_rows = 16; L.out0 = dx; L.status = status;
+  L.stream = static_cast<cudaStream_t>(stream);
+  int rc = qg::check_common(L, "qlinear_dgrad");
+  if (rc) return rc;
+  B2G_REQUIRE(N % 8 == 0, "qlinear_dgrad: N=%lld must be a multiple of 8 (pad dY)", (long long)N);
+  if (M == 0) return 0;
+  return qg::launch_mode<qg::kDgrad>(L);
+}
+
+extern "C" int64_t b2g_grouped_tiles_bytes(int64_t R, int G) {
+  const int64_t rows_per_tile = qg::kBM * qg::kMT;
+  return (1 + R / rows_per_tile + G + 1) * (int64_t)sizeof(int4);
+}
+
+extern "C" int b2g_grouped_schedule(const int64_t* expert_indices, const int32_t* offsets, int G, int64_t R, int32_t* tiles,
+                                    void* stream) {
+  B2G_REQUIRE(G >= 0 && R >= 0 && tiles, "bad arguments");
+  B2G_REQUIRE(aligned16(tiles), "tile table must be 16-byte aligned");
+  B2G_REQUIRE(G == 0 || (expert_indices && offsets), "null pointer");
+  qg::schedule_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(expert_indices, offsets, G, qg::kBM * qg::kMT,
+                                                                       reinterpret_cast<int4*>(tiles));
+  B2G_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int b2g_grouped_fwd(int qtype, const void* x, const void* payload0, const void* payload1, const int32_t* tiles,
+                               const void* xas, const void* lora_b16, int64_t lora_rows, void* y0, void* y1, int64_t R, int64_t N,
+                               int64_t K, int num_experts, int* status, void* stream) {
+  qg::Launch L{};
+  L.qtype = qtype; L.mode = qg::kFwd; L.a0 = x; L.w0 = payload0; L.w1 = payload1; L.la = xas; L.lb = lora_b16;
+  L.m_total = R; L.n = N; L.k = K; L.num_experts = num_experts; L.tiles = tiles; L.lora_rows = lora_rows;
+  L.out0 = y0; L.out1 = y1; L.status = status; L.stream = static_cast<cudaStream_t>(stream);
+  int rc = qg::check_common(L, "grouped_fwd");
+  if (rc) return rc;
+  B2G_REQUIRE(tiles && num_experts >= 1, "grouped_fwd: tile table missing");
+  B2G_REQUIRE((payload1 == nullptr) == (y1 == nullptr), "grouped_fwd: second payload and second output come together");
+  B2G_REQUIRE(N % 8 == 0, "grouped_fwd: N=%lld must be a multiple of 8", (long long)N);
+  if (R == 0) return 0;
+  return qg::launch_mode<qg::kFwd>(L);
+}
+
+extern "C" int b2g_grouped_dgrad(int qtype, const void* dy0, const void* dy1, const void* payload0, const void* payload1,
+                                 const int32_t* tiles, const void* dybs, const void* lora_a16, void* dx, int64_t R, int64_t N,
+                                 int64_t K, int num_experts, int* status, void* stream) {
+  qg::Launch L{};
+  L.qtype = qtype; L.mode = qg::kDgrad; L.a0 = dy0; L.a1 = dy1; L.w0 = payload0; L.w1 = payload1; L.la = dybs; L.lb = lora_a16;
+  L.m_total = R; L.n = N; L.k = K; L.num_experts = num_experts; L.tiles = tiles; L.lora_rows = 16;
+  L.out0 = dx; L.status = status; L.stream = static_cast<cudaStream_t>(stream);
+  int rc = qg::check_common(L, "grouped_dgrad");
+  if (rc) return rc;
+  B2G_REQUIRE(tiles && num_experts >= 1, "grouped_dgrad: tile table missing");
+  B2G_REQUIRE((payload1 == nullptr) == (dy1 == nullptr), "grouped_dgrad: second payload and second gradient come together");
+  B2G_REQUIRE(N % 64 == 0, "grouped_dgrad: N=%lld must be a multiple of 64", (long long)N);
+  if (R == 0) return 0;
+  return qg::launch_mode<qg::kDgrad>(L);
+}
