@@ -1,0 +1,325 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized LoRA-linear hot path on B200.
+
+One "step" = forward + backward of the three Q4_K LoRA linears of a Qwen3.5-35B-A3B attention
+block (K = 2048, N in {4096, 512, 2048}, r = 16, alpha = 32) over M = 32768 tokens of synthetic
+bf16 activations: Y = X.deq(W)^T + s.(X.A^T).B^T, then dX, dA, dB from a given dY.
+Prints one JSON line (tokens/s, roofline of the dominant kernel, host-buffer e2e, CPU baseline).
+
+    python bench.py                        # 1 GPU
+    torchrun ... bench.py --gpus N ...     # N independent replicas (the dense path does not shard)
+    python bench.py --impl reference       # the reference's dequantize-then-matmul path on the host CPU
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+PKG = ROOT / "transformers5-qwen3.5-recipe_b200"
+sys.path.insert(0, str(PKG))
+sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+
+K_DIM = 2048
+N_DIMS = (4096, 512, 2048)
+RANK, ALPHA = 16, 32
+SCALING = ALPHA / RANK
+Q4_K = 12
+SEED = 19260817 + 1
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def flops_per_step(m: int) -> float:
+    return float(sum(4 * m * n * K_DIM + 6 * m * RANK * (K_DIM + n) for n in N_DIMS))
+
+
+def load_peaks() -> tuple[dict, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return json.loads(p.read_text()), "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+def make_inputs(m: int, device, with_payload=True):
+    """Seeded synthetic weights/activations of the configuration, drawn on the CPU in a fixed order."""
+    from b2g import gguf_quant
+
+    g = torch.Generator().manual_seed(SEED)
+    layers = []
+    for n in N_DIMS:
+        w = torch.randn(n, K_DIM, generator=g) * 0.02
+        a = (torch.randn(RANK, K_DIM, generator=g) / 16).to(torch.bfloat16)
+        b = (torch.randn(n, RANK, generator=g) * 0.01).to(torch.bfloat16)
+        payload = gguf_quant.quantize_q4_k(w)
+        layers.append({"n": n, "payload": payload.to(device) if with_payload else payload, "a": a.to(device), "b": b.to(device)})
+    x = torch.randn(m, K_DIM, generator=g).to(torch.bfloat16)
+    dys = [torch.randn(m, n, generator=g).to(torch.bfloat16) for n in N_DIMS]
+    return layers, x, dys
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.gpu_index), "-lms", "200"], stdout=f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        try:
+            self.proc.terminate()
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        try:
+            rows = [r.split(",") for r in Path(self.path).read_text().strip().splitlines() if r.strip()]
+            sm = [float(r[1]) for r in rows if len(r) >= 9]
+            names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+            reasons = set()
+            for r in rows:
+                if len(r) >= 9:
+                    for name, val in zip(names, r[5:9]):
+                        if val.strip().lower().startswith("active"):
+                            reasons.add(name)
+            if sm:
+                out.update(sm_mhz=statistics.median(sm), sm_max_mhz=float(rows[0][2]), reasons=sorted(reasons), samples=len(sm))
+            os.unlink(self.path)
+        except Exception:
+            pass
+        return out
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arm: the reference's dequantize-then-matmul path (oracle port) on the host cores
+# ---------------------------------------------------------------------------------------------
+def cpu_step_fn(layers_cpu):
+    from oracle import dense_ref
+
+    weights = [dense_ref.dequant_bf16(l["payload"].numpy(), Q4_K) for l in layers_cpu]   # outside the timed region
+
+    def step(x, dys):
+        for l, w, dy in zip(layers_cpu, weights, dys):
+            dense_ref.lora_linear_fwd_bwd(x, w, l["a"], l["b"], SCALING, dy, torch.bfloat16)
+
+    return step
+
+
+def run_cpu(steps: int, warmup: int, budget_s: float, m_full: int) -> dict:
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    layers, x, dys = make_inputs(2048, "cpu")
+    step = cpu_step_fn(layers)
+    step(x[:64], [d[:64] for d in dys])                      # first-call overheads
+    t0 = time.perf_counter()
+    step(x[:256], [d[:256] for d in dys])
+    per_row = (time.perf_counter() - t0) / 256
+    per_step_budget = max(0.05, budget_s / max(1, steps + warmup))
+    m = int(min(2048, max(64, per_step_budget / per_row)))
+    m = max(64, m // 64 * 64)
+    xs, ds = x[:m].contiguous(), [d[:m].contiguous() for d in dys]
+    for _ in range(warmup):
+        step(xs, ds)
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        step(xs, ds)
+        times.append(time.perf_counter() - t0)
+    total = sum(times)
+    return {"tokens_per_s": m * steps / total, "ms_per_step": 1e3 * total / steps, "cores": threads, "m": m,
+            "sample": f"{m} of {m_full} tokens per step through the same three linears, weights dequantised once outside the timed region, "
+                      f"{steps} timed steps, torch {torch.get_num_threads()} threads"}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--tokens", type=int, default=32768, help="M: tokens per step and per GPU")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    m = args.tokens
+    config = {"workload": "dense Q4_K LoRA linears, Qwen3.5-35B-A3B attention shapes (BASELINE configs[1])",
+              "K": K_DIM, "N": list(N_DIMS), "M_tokens_per_gpu": m, "lora_rank": RANK, "lora_alpha": ALPHA,
+              "parallelism": f"replicas x{args.gpus} (dense path does not shard)", "l2": "inputs larger than L2 (X 128 MiB, dY up to 256 MiB)"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        res = run_cpu(args.steps, max(1, args.warmup), budget_s=150.0, m_full=m)
+        line = {"impl": "reference", "metric": "quantized LoRA-linear fwd+bwd tokens/s", "value": res["tokens_per_s"], "unit": "tokens/s",
+                "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_step"],
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": config,
+                "cpu_baseline": {"value": res["tokens_per_s"], "unit": "tokens/s", "cores": res["cores"], "kind": "port", "sample": res["sample"]},
+                "e2e": {"value": res["tokens_per_s"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return 0
+
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "no CUDA device: the product path has no CPU fallback"}))
+        return 1
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+
+    from b2g import _lib, autograd as ag, ops
+
+    layers, x_cpu, dys_cpu = make_inputs(m, dev)
+    x_pin = x_cpu.pin_memory()
+    dys_pin = [d.pin_memory() for d in dys_cpu]
+    x_dev = x_cpu.to(dev)
+    dys_dev = [d.to(dev) for d in dys_cpu]
+    for l in layers:
+        l["a"].requires_grad_(True)
+        l["b"].requires_grad_(True)
+
+    def step(x, dys):
+        x = x.detach().requires_grad_(True)
+        for l in layers:
+            l["a"].grad = None
+            l["b"].grad = None
+        outs = [ag.lora_qlinear(x, l["payload"], Q4_K, l["n"], l["a"], l["b"], SCALING) for l in layers]
+        torch.autograd.backward(outs, dys)
+        return x.grad
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step(x_dev, dys_dev)
+    torch.cuda.synchronize()
+    ops.check_status()
+
+    # ---- timed region: inputs resident in HBM ----
+    _lib.COUNT_LAUNCHES = True
+    _lib.LAUNCHES = 0
+    _lib.TIMED = {"b2g_qlinear_fwd"}
+    _lib.EVENTS.clear()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step(x_dev, dys_dev)
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    launches = _lib.LAUNCHES
+    _lib.COUNT_LAUNCHES = False
+    _lib.TIMED = set()
+    clocks = sampler.stop() if rank == 0 else {}
+    ops.check_status()
+
+    # dominant kernel: the quantized forward GEMM of the widest layer, timed by CUDA events on its stream
+    n_big = max(N_DIMS)
+    durs = [a.elapsed_time(b) for (name, key, a, b) in _lib.EVENTS if key == (m, n_big, K_DIM)]
+    _lib.EVENTS.clear()
+    kernel_ms = statistics.mean(durs) if durs else None
+
+    # ---- e2e: host buffers in, host buffers out ----
+    grads_host = [(torch.empty_like(l["a"], device="cpu").pin_memory(), torch.empty_like(l["b"], device="cpu").pin_memory()) for l in layers]
+    x_stage = torch.empty_like(x_dev)
+    dys_stage = [torch.empty_like(d) for d in dys_dev]
+
+    def step_e2e():
+        x_stage.copy_(x_pin, non_blocking=True)
+        for s, p in zip(dys_stage, dys_pin):
+            s.copy_(p, non_blocking=True)
+        step(x_stage, dys_stage)
+        for (ha, hb), l in zip(grads_host, layers):
+            ha.copy_(l["a"].grad, non_blocking=True)
+            hb.copy_(l["b"].grad, non_blocking=True)
+        torch.cuda.current_stream().synchronize()          # the host reads the step's result
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(2):
+        step_e2e()
+    barrier()
+    e0.record()
+    for _ in range(e2e_steps):
+        step_e2e()
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+    h2d = x_pin.numel() * 2 + sum(d.numel() * 2 for d in dys_pin)
+    d2h = sum(a.numel() * 2 + b.numel() * 2 for a, b in grads_host)
+
+    if dist is not None:
+        t = torch.tensor([ms_total, ms_e2e], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total, ms_e2e = float(t[0]), float(t[1])
+
+    if rank == 0:
+        peaks, peak_src = load_peaks()
+        ms_step = ms_total / args.steps
+        value = world * m / (ms_step * 1e-3)
+        flops = flops_per_step(m)
+        peak_tf = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+        roof = None
+        if kernel_ms:
+            achieved = 2.0 * m * n_big * K_DIM / (kernel_ms * 1e-3) / 1e12
+            roof = {"bound": "tensor", "kernel": "qgemm_kernel<Q4_K, forward> M=%d N=%d K=%d" % (m, n_big, K_DIM),
+                    "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
+                    "peak_source": f"{peak_src} burst cuBLAS bf16", "kernel_ms": kernel_ms, "traffic": None}
+        line = {"metric": "quantized LoRA-linear fwd+bwd tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world,
+                "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
+                "step_tflops": world * flops / (ms_step * 1e-3) / 1e12,
+                "step_frac_of_tensor_peak": flops / (ms_step * 1e-3) / 1e12 / peak_tf,
+                "roofline": roof, "clocks": clocks, "gpu_launches": launches,
+                "e2e": {"value": world * m / (ms_e2e / e2e_steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                        "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / e2e_steps}}
+        if world == 1 and not args.no_cpu_baseline:
+            res = run_cpu(3, 1, budget_s=20.0, m_full=m)
+            line["cpu_baseline"] = {"value": res["tokens_per_s"], "unit": "tokens/s", "cores": res["cores"], "kind": "port", "sample": res["sample"]}
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

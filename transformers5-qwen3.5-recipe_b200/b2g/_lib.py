@@ -67,10 +67,35 @@ def load() -> C.CDLL:
     return _lib
 
 
+# Kernels launched by one call of each entry point (the benchmark reports the total it issued).
+KERNELS_PER_CALL = {
+    "b2g_dequant": 1, "b2g_qlinear_fwd": 1, "b2g_qlinear_dgrad": 1, "b2g_lora_down": 1, "b2g_lora_wgrad": 2,
+    "b2g_router_topk": 1, "b2g_route_plan": 3, "b2g_route_gather": 1, "b2g_route_gather_bwd": 1, "b2g_route_combine": 1,
+    "b2g_route_combine_bwd": 1, "b2g_grouped_schedule": 1, "b2g_grouped_fwd": 1, "b2g_grouped_dgrad": 1,
+    "b2g_grouped_lora_down": 1, "b2g_grouped_lora_wgrad": 1, "b2g_swiglu_fwd": 1, "b2g_swiglu_bwd": 1,
+}
+COUNT_LAUNCHES = False
+LAUNCHES = 0
+TIMED: set = set()      # entry points to bracket with CUDA events on the launching stream
+EVENTS: list = []       # (name, (int args...), start_event, end_event)
+
+
 def call(name: str, *args):
     """Invoke an int-returning entry point; raise B2GError with the library's message on failure."""
+    global LAUNCHES
     lib = load()
-    rc = getattr(lib, name)(*args)
+    if COUNT_LAUNCHES:
+        LAUNCHES += KERNELS_PER_CALL.get(name, 0)
+    if name in TIMED:
+        import torch
+
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        rc = getattr(lib, name)(*args)
+        b.record()
+        EVENTS.append((name, tuple(v for v in args if isinstance(v, int))[-3:], a, b))
+    else:
+        rc = getattr(lib, name)(*args)
     if rc != 0:
         msg = lib.b2g_last_error().decode("utf-8", "replace")
         kind = ValueError if rc == -1 else B2GError

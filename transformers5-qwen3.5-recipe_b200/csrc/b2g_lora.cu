@@ -69,7 +69,7 @@ __global__ void __launch_bounds__(128) lora_down_kernel(const __nv_bfloat16* __r
   const uint32_t sbase = dev::smem_u32(sm);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nseg = x1 ? 2 : 1;
-  const int chunks = C / kDownBK;
+  const int chunks = (C + kDownBK - 1) / kDownBK;
   const int total_items = tiles ? tiles[0].x * (tiles[0].y / kDownRows) : dense_items;
   const int64_t w_per_expert = (int64_t)nseg * C * r;
 
@@ -89,8 +89,8 @@ __global__ void __launch_bounds__(128) lora_down_kernel(const __nv_bfloat16* __r
       for (int i = 0; i < 8; ++i) {
         const int v = threadIdx.x + i * 128;
         const int row = v >> 4, vec = v & 15;
-        const bool ok = row < s.rows;
-        const __nv_bfloat16* src = xs + (int64_t)(s.row0 + (ok ? row : 0)) * C + c0 + vec * 8;
+        const bool ok = row < s.rows && c0 + vec * 8 < C;  // zero-fill past the last row / column
+        const __nv_bfloat16* src = xs + (int64_t)(s.row0 + (ok ? row : 0)) * C + (ok ? c0 + vec * 8 : 0);
         cp_async16(dst + row * kDownStride + vec * 16, src, ok);
       }
     };
@@ -110,7 +110,9 @@ __global__ void __launch_bounds__(128) lora_down_kernel(const __nv_bfloat16* __r
       for (int kk = 0; kk < kDownBK / 16; ++kk) {
         uint32_t a[4];
         ldmatrix_x4(tile + (warp * 16 + (lane & 15)) * kDownStride + (kk * 16 + (lane >> 4) * 8) * 2, a);
-        const int kcol = seg * C + c0 + kk * 16 + (lane & 3) * 2;  // reduction index of b0 (b1 is +8)
+        const int kloc = c0 + kk * 16 + (lane & 3) * 2;            // column inside this input part
+        const int kcol = seg * C + kloc;                            // reduction index of b0 (b1 is +8)
+        const bool k0_ok = kloc < C, k1_ok = kloc + 8 < C;
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
           const int n = nt * 8 + (lane >> 2);
@@ -118,12 +120,12 @@ __global__ void __launch_bounds__(128) lora_down_kernel(const __nv_bfloat16* __r
           if (n < r) {
             if (kWisCR) {  // W[(k), n] with r columns
               const unsigned short* wp = reinterpret_cast<const unsigned short*>(we);
-              b0 = wp[(int64_t)kcol * r + n] | (static_cast<uint32_t>(wp[(int64_t)(kcol + 1) * r + n]) << 16);
-              b1 = wp[(int64_t)(kcol + 8) * r + n] | (static_cast<uint32_t>(wp[(int64_t)(kcol + 9) * r + n]) << 16);
+              if (k0_ok) b0 = wp[(int64_t)kcol * r + n] | (static_cast<uint32_t>(wp[(int64_t)(kcol + 1) * r + n]) << 16);
+              if (k1_ok) b1 = wp[(int64_t)(kcol + 8) * r + n] | (static_cast<uint32_t>(wp[(int64_t)(kcol + 9) * r + n]) << 16);
             } else {       // W[n, k] with nseg*C columns
               const __nv_bfloat16* wp = we + (int64_t)n * (nseg * C) + kcol;
-              b0 = *reinterpret_cast<const uint32_t*>(wp);
-              b1 = *reinterpret_cast<const uint32_t*>(wp + 8);
+              if (k0_ok) b0 = *reinterpret_cast<const uint32_t*>(wp);
+              if (k1_ok) b1 = *reinterpret_cast<const uint32_t*>(wp + 8);
             }
           }
           mma_bf16(acc[nt], a, b0, b1);
@@ -287,7 +289,7 @@ using namespace b2g;
 static int lora_down_launch(const void* x, const void* x1, const void* w, int w_is_cr, float scale, const int32_t* tiles, void* out_plain,
                             void* out_scaled, int64_t M, int64_t C, int r, void* stream, const char* what) {
   B2G_REQUIRE(r >= 1 && r <= lora::kRankPad, "%s: rank %d outside 1..16", what, r);
-  B2G_REQUIRE(C > 0 && C % lora::kDownBK == 0, "%s: reduction width %lld must be a multiple of 128", what, (long long)C);
+  B2G_REQUIRE(C > 0 && C % 8 == 0, "%s: reduction width %lld must be a multiple of 8", what, (long long)C);
   B2G_REQUIRE(M >= 0 && M < (1ll << 31), "%s: bad row count", what);
   if (M == 0) return 0;
   B2G_REQUIRE(x && w && (out_plain || out_scaled), "%s: null pointer", what);

@@ -639,6 +639,9 @@ int check_common(const Launch& L, const char* what) {
   B2G_REQUIRE(L.m_total >= 0 && L.n > 0 && L.k > 0, "%s: bad shape M=%lld N=%lld K=%lld", what, (long long)L.m_total,
               (long long)L.n, (long long)L.k);
   B2G_REQUIRE(L.k % 256 == 0, "%s: K=%lld must be a multiple of 256", what, (long long)L.k);
+  B2G_REQUIRE(fmt::row_bytes(L.qtype, L.k) % 16 == 0,
+              "%s: packed rows of %lld bytes are not 16-byte multiples (IQ2_XXS needs K %% 2048 == 0 on this path)", what,
+              (long long)fmt::row_bytes(L.qtype, L.k));
   B2G_REQUIRE(L.m_total < (1ll << 31) && (int64_t)L.num_experts * L.n < (1ll << 31), "%s: shape too large", what);
   B2G_REQUIRE(L.a0 && L.w0 && L.out0, "%s: null pointer", what);
   B2G_REQUIRE((L.la == nullptr) == (L.lb == nullptr), "%s: the two LoRA operands come together", what);
