@@ -165,6 +165,13 @@ B2G_API int b2g_grouped_lora_wgrad(const void* s, const void* t, float scale, co
                            int transpose_out, int64_t R, int64_t C, int r, int num_experts, int64_t out_col_offset,
                            int64_t out_cols_total, void* stream);
 
+/* Per-expert up-projection from the rank: Y[rows_e, N] = P[rows_e, :r] . W[e]^T with P of row stride
+ * `ldp` and W per expert as [N,r] (w_is_nr = 1) or [r,N] (w_is_nr = 0).  Replaces the second AITER gmm
+ * of _lora_grouped_linear (fast_moe_lora.py:675-682) where a caller wants it as a separate operator;
+ * the fused expert path folds this product into b2g_grouped_fwd instead. */
+B2G_API int b2g_grouped_lora_up(const void* p, int64_t ldp, const void* w, int w_is_nr, const int32_t* offsets_full, void* y,
+                        int64_t R, int64_t N, int r, int num_experts, void* stream);
+
 /* SwiGLU between the two grouped products: z = silu(g) * u (optionally clamped as the DeepSeek
  * experts do: g <= limit, |u| <= limit; limit <= 0 disables).  Replaces GGUFExperts._apply_split_gate
  * (called at fast_moe_lora.py:747; clamp semantics at test_deepseek_v4_moe_lora.py:194-196). */

@@ -1,0 +1,53 @@
+"""Generate tests/golden/gguf_dequant.npz: packed payloads and their float32 decode by gguf-py.
+
+Run in the build container (needs the `gguf` package, which is the normative restatement of the
+GGUF block formats the reference's dequantiser implements):
+
+    python tests/golden/make_golden.py
+
+Payload sources: gguf-py's own Q8_0 encoder; this repository's oracle encoders for Q4_K and
+IQ2_XXS (gguf-py has none); uniformly random valid blocks; and the constant-byte payload of the
+reference's own grouped test (test_deepseek_v4_moe_lora.py:55-64: every byte = 32).  The answers
+always come from gguf.quants.dequantize, never from this repository's code.
+"""
+import sys
+from pathlib import Path
+
+import gguf
+import numpy as np
+from gguf import quants as gq
+
+ROOT = Path(__file__).resolve().parents[2]
+sys.path.insert(0, str(ROOT))
+from oracle import gguf_oracle as go  # noqa: E402
+
+
+def main() -> None:
+    rng = np.random.default_rng(19260817)
+    out = {}
+    w = (rng.standard_normal((12, 512)) * 0.02).astype(np.float32)
+    w[3] = 0.0                                     # an all-zero row: zero scales
+    w[5, :256] *= 50.0                             # a block with a large dynamic range
+    cases = {
+        "q8_0_gguf_encoder": (go.Q8_0, gq.quantize(w, gguf.GGMLQuantizationType.Q8_0)),
+        "q4_k_oracle_encoder": (go.Q4_K, go.quantize(w, go.Q4_K)),
+        "iq2_xxs_oracle_encoder": (go.IQ2_XXS, go.quantize(w, go.IQ2_XXS)),
+        "q8_0_random": (go.Q8_0, go.random_payload(go.Q8_0, (6, 512), 1)),
+        "q4_k_random": (go.Q4_K, go.random_payload(go.Q4_K, (6, 512), 2)),
+        "iq2_xxs_random": (go.IQ2_XXS, go.random_payload(go.IQ2_XXS, (6, 512), 3)),
+        "iq2_xxs_const32": (go.IQ2_XXS, np.full((4, 66), 32, dtype=np.uint8)),
+        "q4_k_const32": (go.Q4_K, np.full((4, 144), 32, dtype=np.uint8)),
+    }
+    for name, (qt, payload) in cases.items():
+        ref = gq.dequantize(payload, gguf.GGMLQuantizationType(qt)).astype(np.float32)
+        out[name + "__payload"] = payload
+        out[name + "__f32bits"] = ref.view(np.uint32)
+        out[name + "__qtype"] = np.int32(qt)
+    gq.IQ2_XXS.init_grid()
+    out["iq2_xxs_ksigns"] = np.frombuffer(gq.IQ2_XXS.ksigns, dtype=np.uint8).copy()
+    np.savez_compressed(Path(__file__).with_name("gguf_dequant.npz"), **out)
+    print("wrote", len(cases), "cases")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,99 @@
+"""CPU: host-side logic of the package (no kernels run)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import gguf_oracle as go
+
+
+def test_payload_geometry():
+    from b2g import ops
+
+    assert ops.payload_row_bytes(12, 2048) == 1152 and ops.payload_row_bytes(8, 2048) == 2176
+    assert ops.payload_row_bytes(16, 4096) == 1056
+    with pytest.raises(ValueError):
+        ops.payload_row_bytes(12, 100)
+
+
+def test_torch_encoders_match_oracle_encoders():
+    from b2g import gguf_quant
+
+    w = torch.randn(32, 1024, generator=torch.Generator().manual_seed(1)) * 0.02
+    assert np.array_equal(gguf_quant.quantize_q8_0(w).numpy(), go.quantize(w.numpy(), go.Q8_0))
+    assert np.array_equal(gguf_quant.quantize_q4_k(w).numpy(), go.quantize(w.numpy(), go.Q4_K))
+    for qt in (8, 12, 16):
+        p = gguf_quant.random_payload(qt, (3, 2, 2048), 5)
+        d = go.dequantize(p.numpy(), qt)
+        assert np.isfinite(d).all() and 0.005 < d.std() < 0.06
+
+
+def test_rank_padding():
+    from b2g import ops
+
+    b = torch.randn(5, 4).bfloat16()
+    pb = ops.pad_rank_cols(b)
+    assert pb.shape == (5, 16) and torch.equal(pb[:, :4], b) and float(pb[:, 4:].abs().max()) == 0
+    a = torch.randn(3, 8, 32).bfloat16()
+    pa = ops.pad_rank_rows(a)
+    assert pa.shape == (3, 16, 32) and torch.equal(pa[:, :8], a)
+    full = torch.randn(7, 16).bfloat16()
+    assert ops.pad_rank_cols(full).data_ptr() == full.data_ptr()
+
+
+def test_cpu_tensors_are_rejected_not_routed_elsewhere():
+    from b2g import autograd as ag, ops
+
+    x = torch.zeros(4, 256, dtype=torch.bfloat16)
+    p = torch.zeros(8 * 144, dtype=torch.uint8)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        ops.qlinear_fwd(x, p, 12, 8)
+    with pytest.raises((RuntimeError, NotImplementedError)):
+        ag.mmq(x, p, 12, 8)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        ops.dequantize(p, 12, (8, 256))
+
+
+def test_operators_registered_with_meta_kernels():
+    from b2g import autograd as ag  # noqa: F401
+
+    x = torch.empty(3, 5, 256, dtype=torch.bfloat16, device="meta")
+    p = torch.empty(64 * 144, dtype=torch.uint8, device="meta")
+    assert torch.ops.b2g.mmq(x, p, 12, 64).shape == (3, 5, 64)
+    g = torch.empty(7, 64, dtype=torch.bfloat16, device="meta")
+    assert torch.ops.b2g.mmq_grad_input(g, p, 12, 256).shape == (7, 256)
+    idx = torch.empty(2, dtype=torch.int64, device="meta")
+    off = torch.empty(2, dtype=torch.int32, device="meta")
+    y0, y1 = torch.ops.b2g.grouped_mmq_pair(g.new_empty(7, 256), p, p, idx, off, 12, 32)
+    assert y0.shape == (7, 32) and y1.shape == (7, 32)
+
+
+def test_bench_flop_formula():
+    import bench
+
+    m = 32768
+    assert bench.flops_per_step(m) == sum(4 * m * n * 2048 + 6 * m * 16 * (2048 + n) for n in (4096, 512, 2048))
+
+
+def test_oracle_dense_reference_shapes():
+    from oracle import dense_ref
+
+    g = torch.Generator().manual_seed(0)
+    w = go.quantize((np.random.default_rng(0).standard_normal((24, 256)) * 0.02).astype(np.float32), go.Q4_K)
+    wb = dense_ref.dequant_bf16(w, go.Q4_K)
+    x = torch.randn(9, 256, generator=g).bfloat16()
+    a = torch.randn(4, 256, generator=g).bfloat16()
+    b = torch.randn(24, 4, generator=g).bfloat16()
+    out = dense_ref.lora_linear_fwd_bwd(x, wb, a, b, 1.0, torch.randn(9, 24, generator=g).bfloat16())
+    assert out["y"].shape == (9, 24) and out["dx"].shape == (9, 256) and out["da"].shape == (4, 256) and out["db"].shape == (24, 4)
+
+
+def test_oracle_routing_reference_is_stable_and_consistent():
+    from oracle import moe_ref
+
+    idx = torch.tensor([[3, 1], [1, 3], [0, 1]])
+    plan = moe_ref.route_plan(idx, 4)
+    assert plan["expert_indices"].tolist() == [0, 1, 1, 1, 3, 3]
+    assert plan["permutation"].tolist() == [4, 1, 2, 5, 0, 3]           # equal ids keep flat order
+    assert plan["group_sizes"].tolist() == [1, 3, 0, 2] and plan["offsets"].tolist() == [1, 4, 4, 6]
+    logits = torch.zeros(2, 256)
+    assert moe_ref.router_topk(logits, 8).tolist() == [list(range(8))] * 2  # ties -> smaller id

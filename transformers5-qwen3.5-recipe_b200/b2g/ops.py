@@ -430,3 +430,19 @@ def grouped_lora_wgrad(s16: torch.Tensor, t: torch.Tensor, scale: float, r: int,
         _lib.call("b2g_grouped_lora_wgrad", _p(s16), _p(t), float(scale), _p(offsets_full), _p(out), int(transpose_out), rows, c,
                   int(r), int(e), int(out_col_offset), int(ctot), _stream(t))
     return out
+
+
+def grouped_lora_up(p: torch.Tensor, w: torch.Tensor, w_is_nr: bool, offsets_full: torch.Tensor) -> torch.Tensor:
+    """Y[rows_e, N] = P[rows_e, :r] . W[e]^T; ``p`` is [R, >=r] (row stride taken from the tensor),
+    ``w`` is [E, N, r] (w_is_nr) or [E, r, N]."""
+    _need(w, torch.bfloat16, "w")
+    _need(offsets_full, torch.int32, "offsets")
+    if p.dtype != torch.bfloat16 or not p.is_cuda or p.stride(1) != 1:
+        raise RuntimeError("p must be a CUDA bf16 matrix with unit column stride")
+    e = w.shape[0]
+    n, r = (w.shape[1], w.shape[2]) if w_is_nr else (w.shape[2], w.shape[1])
+    y = torch.empty(p.shape[0], n, dtype=torch.bfloat16, device=p.device)
+    with _DeviceCtx(p):
+        _lib.call("b2g_grouped_lora_up", _p(p), p.stride(0), _p(w), int(w_is_nr), _p(offsets_full), _p(y), p.shape[0], n, int(r),
+                  int(e), _stream(p))
+    return y

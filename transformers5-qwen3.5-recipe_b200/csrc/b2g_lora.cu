@@ -272,6 +272,36 @@ __global__ void __launch_bounds__(256) lora_wgrad_reduce_kernel(const float* __r
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Up-projection from the rank: Y[row, n] = sum_j P[row, j] * W_e[n, j]  (j < r <= 16), one expert per
+// row segment.  Bound by writing Y; used by the un-fused operator surface (the fused path folds this
+// product into the quantized GEMM as one extra MMA step).
+// ------------------------------------------------------------------------------------------------
+template <bool kWisNR>
+__global__ void __launch_bounds__(128) lora_up_kernel(const __nv_bfloat16* __restrict__ p, int ldp, const __nv_bfloat16* __restrict__ w,
+                                                      const int32_t* __restrict__ offsets_full, int num_experts,
+                                                      __nv_bfloat16* __restrict__ y, int64_t rows, int N, int r) {
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    // expert of this row: first e with offsets[e] > row (binary search; E is small)
+    int lo = 0, hi = num_experts - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (offsets_full[mid] > row) hi = mid; else lo = mid + 1;
+    }
+    const __nv_bfloat16* we = w + (int64_t)lo * N * r;
+    float pv[kRankPad];
+#pragma unroll
+    for (int j = 0; j < kRankPad; ++j) pv[j] = j < r ? __bfloat162float(p[row * ldp + j]) : 0.f;
+    for (int n = threadIdx.x; n < N; n += blockDim.x) {
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < kRankPad; ++j)
+        if (j < r) acc = fmaf(pv[j], __bfloat162float(kWisNR ? we[(int64_t)n * r + j] : we[(int64_t)j * N + n]), acc);
+      y[row * N + n] = __float2bfloat16_rn(acc);
+    }
+  }
+}
+
 inline int wgrad_splits(int64_t M, int64_t C) {
   const int chunks = (int)((C + kWgCols - 1) / kWgCols);
   int splits = (4 * sm_count() + chunks - 1) / chunks;
@@ -376,6 +406,25 @@ extern "C" int b2g_grouped_lora_wgrad(const void* s, const void* t, float scale,
   lora::lora_wgrad_kernel<false><<<dim3(chunks, num_experts), 128, smem, st>>>(
       static_cast<const __nv_bfloat16*>(s), static_cast<const __nv_bfloat16*>(t), scale, offsets_full, R, 0, (int)C, r, nullptr,
       static_cast<__nv_bfloat16*>(out), transpose_out, out_col_offset, out_cols_total);
+  B2G_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int b2g_grouped_lora_up(const void* p, int64_t ldp, const void* w, int w_is_nr, const int32_t* offsets_full, void* y,
+                                   int64_t R, int64_t N, int r, int num_experts, void* stream) {
+  B2G_REQUIRE(r >= 1 && r <= lora::kRankPad && ldp >= r, "grouped_lora_up: rank %d / row stride %lld invalid", r, (long long)ldp);
+  B2G_REQUIRE(N > 0 && R >= 0 && num_experts >= 1, "grouped_lora_up: bad shape");
+  if (R == 0) return 0;
+  B2G_REQUIRE(p && w && y && offsets_full, "grouped_lora_up: null pointer");
+  const int64_t cap = (int64_t)sm_count() * 16;
+  const int grid = (int)(R < cap ? R : cap);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (w_is_nr)
+    lora::lora_up_kernel<true><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(p), (int)ldp, static_cast<const __nv_bfloat16*>(w),
+                                                     offsets_full, num_experts, static_cast<__nv_bfloat16*>(y), R, (int)N, r);
+  else
+    lora::lora_up_kernel<false><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(p), (int)ldp, static_cast<const __nv_bfloat16*>(w),
+                                                      offsets_full, num_experts, static_cast<__nv_bfloat16*>(y), R, (int)N, r);
   B2G_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -643,7 +643,7 @@ int check_common(const Launch& L, const char* what) {
               "%s: packed rows of %lld bytes are not 16-byte multiples (IQ2_XXS needs K %% 2048 == 0 on this path)", what,
               (long long)fmt::row_bytes(L.qtype, L.k));
   B2G_REQUIRE(L.m_total < (1ll << 31) && (int64_t)L.num_experts * L.n < (1ll << 31), "%s: shape too large", what);
-  B2G_REQUIRE(L.a0 && L.w0 && L.out0, "%s: null pointer", what);
+  B2G_REQUIRE(L.m_total == 0 || (L.a0 && L.w0 && L.out0), "%s: null pointer", what);
   B2G_REQUIRE((L.la == nullptr) == (L.lb == nullptr), "%s: the two LoRA operands come together", what);
   return 0;
 }
