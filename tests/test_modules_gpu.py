@@ -124,7 +124,7 @@ def test_fast_gguf_moe_lora_layer(cuda):
     fused = (out.detach().clone(), hc.grad.clone(), {n: v.grad.clone() for n, v in lora.items()})
 
     # operator-by-operator composition (grouped_mmq_pair, grouped rank products, add, SwiGLU, grouped_mmq)
-    del experts.swiglu_limit
+    experts._b2g_fused = False
     for v in lora.values():
         v.grad = None
     hc2 = hidden.to(cuda).requires_grad_(True)

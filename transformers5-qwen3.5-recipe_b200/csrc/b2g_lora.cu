@@ -39,6 +39,8 @@ struct Seg { int expert, row0, rows; };
 // CTA = 4 warps x 16 rows; reduction in chunks of 128 columns, 3-stage cp.async ring.
 // ------------------------------------------------------------------------------------------------
 constexpr int kDownRows = 64, kDownBK = 128, kDownStages = 3, kDownStride = kDownBK * 2 + 16;  // 272-byte rows
+constexpr int kDownXBytes = kDownRows * kDownStride, kDownWBytes = kRankPad * kDownStride;
+constexpr int kDownStageBytes = kDownXBytes + kDownWBytes;
 
 __device__ __forceinline__ Seg down_segment(const int4* tiles, int64_t m_total, int item) {
   Seg s;
@@ -60,6 +62,9 @@ __device__ __forceinline__ Seg down_segment(const int4* tiles, int64_t m_total, 
   return s;
 }
 
+// Each stage holds a [64 x 128] slice of X and the matching [16 x 128] slice of W^T (rank rows, reduction
+// columns); both feed mma.sync through ldmatrix.  W given as [r, C] streams in with cp.async; W given as
+// [C, r] is transposed on the way in (one reduction column per thread, registers as the staging buffer).
 template <bool kWisCR>
 __global__ void __launch_bounds__(128) lora_down_kernel(const __nv_bfloat16* __restrict__ x0, const __nv_bfloat16* __restrict__ x1,
                                                         const __nv_bfloat16* __restrict__ w, float scale, const int4* __restrict__ tiles,
@@ -72,65 +77,88 @@ __global__ void __launch_bounds__(128) lora_down_kernel(const __nv_bfloat16* __r
   const int chunks = (C + kDownBK - 1) / kDownBK;
   const int total_items = tiles ? tiles[0].x * (tiles[0].y / kDownRows) : dense_items;
   const int64_t w_per_expert = (int64_t)nseg * C * r;
+  const int total_chunks = nseg * chunks;
+
+  // rank rows >= r of every W stage stay zero for the whole kernel
+  for (int i = threadIdx.x; i < kDownStages * kRankPad * (kDownStride / 4); i += blockDim.x) {
+    const int st = i / (kRankPad * (kDownStride / 4)), rem = i - st * (kRankPad * (kDownStride / 4));
+    reinterpret_cast<uint32_t*>(sm + st * kDownStageBytes + kDownXBytes)[rem] = 0u;
+  }
+  __syncthreads();
 
   for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
     const Seg s = down_segment(tiles, m_total, item);
     if (s.rows <= 0) continue;
     const __nv_bfloat16* we = w + s.expert * w_per_expert;
     float acc[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
-    const int total_chunks = nseg * chunks;
 
-    auto issue = [&](int ch) {
+    auto issue_x = [&](int ch) {
       const int seg = ch / chunks, c0 = (ch - seg * chunks) * kDownBK;
       const __nv_bfloat16* xs = seg ? x1 : x0;
-      const uint32_t dst = sbase + (ch % kDownStages) * (kDownRows * kDownStride);
-      // 64 rows x 16 vectors of 16 bytes = 1024 vectors over 128 threads
+      const uint32_t dst = sbase + (ch % kDownStages) * kDownStageBytes;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
+      for (int i = 0; i < 8; ++i) {  // 64 rows x 16 vectors of 16 bytes over 128 threads
         const int v = threadIdx.x + i * 128;
         const int row = v >> 4, vec = v & 15;
         const bool ok = row < s.rows && c0 + vec * 8 < C;  // zero-fill past the last row / column
         const __nv_bfloat16* src = xs + (int64_t)(s.row0 + (ok ? row : 0)) * C + (ok ? c0 + vec * 8 : 0);
         cp_async16(dst + row * kDownStride + vec * 16, src, ok);
       }
+      if (!kWisCR) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {  // 16 rank rows x 16 vectors
+          const int v = threadIdx.x + i * 128;
+          const int row = v >> 4, vec = v & 15;
+          const bool ok = row < r && c0 + vec * 8 < C;
+          const __nv_bfloat16* src = we + (int64_t)(ok ? row : 0) * (nseg * C) + seg * C + (ok ? c0 + vec * 8 : 0);
+          if (row < r) cp_async16(dst + kDownXBytes + row * kDownStride + vec * 16, src, ok);
+        }
+      }
+    };
+    // [C, r] layout: this thread's reduction column of chunk `ch` -> registers / registers -> stage
+    unsigned short wv[kRankPad];
+    auto load_w = [&](int ch) {
+      const int seg = ch / chunks, k = (ch - seg * chunks) * kDownBK + threadIdx.x;
+      const unsigned short* src = reinterpret_cast<const unsigned short*>(we) + ((int64_t)seg * C + k) * r;
+      const bool ok = k < C;
+#pragma unroll
+      for (int n = 0; n < kRankPad; ++n) wv[n] = (ok && n < r) ? src[n] : (unsigned short)0;
+    };
+    auto store_w = [&](int ch) {
+      uint8_t* dst = sm + (ch % kDownStages) * kDownStageBytes + kDownXBytes + threadIdx.x * 2;
+#pragma unroll
+      for (int n = 0; n < kRankPad; ++n)
+        if (n < r) *reinterpret_cast<unsigned short*>(dst + n * kDownStride) = wv[n];
     };
 
     for (int pre = 0; pre < kDownStages - 1; ++pre) {
-      if (pre < total_chunks) issue(pre);
+      if (pre < total_chunks) {
+        issue_x(pre);
+        if (kWisCR) { load_w(pre); store_w(pre); }
+      }
       cp_async_commit();
     }
     for (int ch = 0; ch < total_chunks; ++ch) {
-      if (ch + kDownStages - 1 < total_chunks) issue(ch + kDownStages - 1);
+      const int nxt = ch + kDownStages - 1;
+      if (nxt < total_chunks) {
+        issue_x(nxt);
+        if (kWisCR) load_w(nxt);   // lands in registers while this chunk is multiplied
+      }
       cp_async_commit();
       cp_async_wait<kDownStages - 1>();
       __syncthreads();
-      const int seg = ch / chunks, c0 = (ch - seg * chunks) * kDownBK;
-      const uint32_t tile = sbase + (ch % kDownStages) * (kDownRows * kDownStride);
+      const uint32_t tile = sbase + (ch % kDownStages) * kDownStageBytes;
+      const uint32_t wtile = tile + kDownXBytes;
 #pragma unroll
       for (int kk = 0; kk < kDownBK / 16; ++kk) {
-        uint32_t a[4];
+        uint32_t a[4], b[4];
         ldmatrix_x4(tile + (warp * 16 + (lane & 15)) * kDownStride + (kk * 16 + (lane >> 4) * 8) * 2, a);
-        const int kloc = c0 + kk * 16 + (lane & 3) * 2;            // column inside this input part
-        const int kcol = seg * C + kloc;                            // reduction index of b0 (b1 is +8)
-        const bool k0_ok = kloc < C, k1_ok = kloc + 8 < C;
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-          const int n = nt * 8 + (lane >> 2);
-          uint32_t b0 = 0, b1 = 0;
-          if (n < r) {
-            if (kWisCR) {  // W[(k), n] with r columns
-              const unsigned short* wp = reinterpret_cast<const unsigned short*>(we);
-              if (k0_ok) b0 = wp[(int64_t)kcol * r + n] | (static_cast<uint32_t>(wp[(int64_t)(kcol + 1) * r + n]) << 16);
-              if (k1_ok) b1 = wp[(int64_t)(kcol + 8) * r + n] | (static_cast<uint32_t>(wp[(int64_t)(kcol + 9) * r + n]) << 16);
-            } else {       // W[n, k] with nseg*C columns
-              const __nv_bfloat16* wp = we + (int64_t)n * (nseg * C) + kcol;
-              if (k0_ok) b0 = *reinterpret_cast<const uint32_t*>(wp);
-              if (k1_ok) b1 = *reinterpret_cast<const uint32_t*>(wp + 8);
-            }
-          }
-          mma_bf16(acc[nt], a, b0, b1);
-        }
+        // W^T tile rows = rank index n, columns = k: matrices (n0-7,k0-7) (n0-7,k8-15) (n8-15,k0-7) (n8-15,k8-15)
+        ldmatrix_x4(wtile + ((lane & 7) + ((lane >> 4) << 3)) * kDownStride + (kk * 16 + ((lane >> 3) & 1) * 8) * 2, b);
+        mma_bf16(acc[0], a, b[0], b[1]);
+        mma_bf16(acc[1], a, b[2], b[3]);
       }
+      if (kWisCR && nxt < total_chunks) store_w(nxt);  // stage (ch-1)%3: every warp finished reading it before this iteration's barrier
       __syncthreads();
     }
     cp_async_wait<0>();
@@ -149,6 +177,7 @@ __global__ void __launch_bounds__(128) lora_down_kernel(const __nv_bfloat16* __r
         }
       }
     }
+    __syncthreads();  // the next item's prologue rewrites stages this item may still be reading
   }
 }
 
@@ -259,13 +288,21 @@ __global__ void __launch_bounds__(128) lora_wgrad_kernel(const __nv_bfloat16* __
 }
 
 // Sum the per-split partials in split order (deterministic), scale, round, store.
-__global__ void __launch_bounds__(256) lora_wgrad_reduce_kernel(const float* __restrict__ partial, int splits, int C, int r, float scale,
+__global__ void __launch_bounds__(64) lora_wgrad_reduce_kernel(const float* __restrict__ partial, int splits, int C, int r, float scale,
                                                                 __nv_bfloat16* __restrict__ out, int transpose_out) {
   const int64_t n = (int64_t)r * C;
   for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < n; idx += (int64_t)gridDim.x * blockDim.x) {
     const int i = (int)(idx / C), c = (int)(idx - (int64_t)i * C);
     float sum = 0.f;
-    for (int sp = 0; sp < splits; ++sp) sum += partial[((int64_t)sp * kRankPad + i) * C + c];
+    int sp = 0;
+    for (; sp + 8 <= splits; sp += 8) {   // eight loads in flight, summed in split order
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = partial[((int64_t)(sp + u) * kRankPad + i) * C + c];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) sum += v[u];
+    }
+    for (; sp < splits; ++sp) sum += partial[((int64_t)sp * kRankPad + i) * C + c];
     const __nv_bfloat16 v = __float2bfloat16_rn(sum * scale);
     if (transpose_out) out[(int64_t)c * r + i] = v;
     else out[idx] = v;
@@ -325,9 +362,9 @@ static int lora_down_launch(const void* x, const void* x1, const void* w, int w_
   B2G_REQUIRE(x && w && (out_plain || out_scaled), "%s: null pointer", what);
   B2G_REQUIRE(aligned16(x) && (!x1 || aligned16(x1)), "%s: activations must be 16-byte aligned", what);
   B2G_REQUIRE(w_is_cr || (reinterpret_cast<uintptr_t>(w) & 3) == 0, "%s: weight must be 4-byte aligned", what);
-  const size_t smem = (size_t)lora::kDownStages * lora::kDownRows * lora::kDownStride;
+  const size_t smem = (size_t)lora::kDownStages * lora::kDownStageBytes;
   const int dense_items = (int)((M + lora::kDownRows - 1) / lora::kDownRows);
-  int grid = sm_count() * 4;
+  int grid = sm_count() * 3;
   if (!tiles && dense_items < grid) grid = dense_items;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   auto* xb = static_cast<const __nv_bfloat16*>(x);
@@ -384,7 +421,7 @@ extern "C" int b2g_lora_wgrad(const void* s, const void* t, float scale, void* o
       static_cast<float*>(workspace), nullptr, 0, 0, 0);
   B2G_CUDA_OK(cudaGetLastError());
   const int64_t n = (int64_t)r * C;
-  lora::lora_wgrad_reduce_kernel<<<(int)((n + 255) / 256), 256, 0, st>>>(static_cast<const float*>(workspace), splits, (int)C, r, scale,
+  lora::lora_wgrad_reduce_kernel<<<(int)((n + 63) / 64), 64, 0, st>>>(static_cast<const float*>(workspace), splits, (int)C, r, scale,
                                                                        static_cast<__nv_bfloat16*>(out), transpose_out);
   B2G_CUDA_OK(cudaGetLastError());
   return 0;

@@ -16,9 +16,10 @@
 //        shared-memory descriptors differ, so no packed transpose is ever built.
 // The LoRA up-projection is one extra K=16 MMA per tile on 32-byte-swizzled [rows x 16] tiles.
 //
-// Warp roles (448 threads): 0 = TMA producer, 1 = MMA issuer + TMEM owner, 2-5 = epilogue
-// (TMEM -> registers -> global), 6-13 = unpack.  All mbarrier waits are bounded.
+// Warp roles (704 threads): 0 = TMA producer, 1 = MMA issuer + TMEM owner, 2-5 = epilogue
+// (TMEM -> registers -> global), 6-21 = unpack.  All mbarrier waits are bounded.
 #include "b2g_formats.cuh"
+#include <cstdlib>
 
 namespace b2g {
 int iq2xxs_grid(const uint2** out);
@@ -32,7 +33,7 @@ constexpr int kBK = 64;           // reduction step
 constexpr int kATile = kBM * kBK * 2;       // 16384
 constexpr int kBStage = kBN * kBK * 2;      // 32768
 constexpr int kBStages = 2;
-constexpr int kUnpackWarps = 8;
+constexpr int kUnpackWarps = 16;          // 512 threads: (256 W rows x 2 halves) or (64 rows x 4 quarters x 2 halves)
 constexpr int kThreads = 32 * (6 + kUnpackWarps);
 constexpr int kLoraATile = kBM * 32;        // [128 x 16] bf16
 constexpr int kLoraBTile = kBN * 32;        // 8192 either way
@@ -97,6 +98,7 @@ struct Params {
   const __nv_bfloat16* bias;
   const uint2* grid;  // IQ2_XXS table in global memory
   int* status;
+  int debug;          // timing experiments only (0 = normal)
 };
 
 struct Tile { int expert, row0, rows, ct; };
@@ -121,25 +123,22 @@ __device__ __forceinline__ Tile get_tile(const Params& p, int item) {
 }
 
 // ------------------------------------------------------------------------------------------------
-// Row decoders: 64 consecutive values of one W row -> 32 packed bf16 pairs, out[4*c + i] being values
-// 8c+2i and 8c+2i+1 (chunk c = one 16-byte shared-memory vector).
+// Row decoders.  One unpack thread owns 32 consecutive values of one W row per reduction step (half of
+// the 64-value slice): out[4*c + i] holds values 8c+2i, 8c+2i+1 of its half as a bf16 pair, chunk c being
+// one 16-byte shared-memory vector.  `half` is uniform across a warp.
 // ------------------------------------------------------------------------------------------------
-__device__ __forceinline__ void q4k_row64(const uint4 hdr, const uint4 qa, const uint4 qb, int pair, uint32_t (&out)[32]) {
-  uint32_t sc0, mn0, sc1, mn1;
-  fmt::q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * pair, sc0, mn0);
-  fmt::q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * pair + 1, sc1, mn1);
-  const float d = dev::half_bits_to_float(hdr.x), dmin = dev::half_bits_to_float(hdr.x >> 16);
-  const float dsc0 = __fmul_rn(d, static_cast<float>(sc0)), ndm0 = -__fmul_rn(dmin, static_cast<float>(mn0));
-  const float dsc1 = __fmul_rn(d, static_cast<float>(sc1)), ndm1 = -__fmul_rn(dmin, static_cast<float>(mn1));
+__device__ __forceinline__ void q4k_half(const uint4 hdr, const uint4 qa, const uint4 qb, int pair, int half, uint32_t (&out)[16]) {
+  uint32_t sc, mn;
+  fmt::q4k_scale_min(hdr.y, hdr.z, hdr.w, 2 * pair + half, sc, mn);
+  const float dsc = __fmul_rn(dev::half_bits_to_float(hdr.x), static_cast<float>(sc));
+  const float ndm = -__fmul_rn(dev::half_bits_to_float(hdr.x >> 16), static_cast<float>(mn));
   const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+  const int shift = 4 * half;  // sub-block 2*pair lives in the low nibbles, 2*pair+1 in the high nibbles
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const uint32_t lo = w[i] & 0x0F0F0F0Fu, hi = (w[i] >> 4) & 0x0F0F0F0Fu;
-    // word i holds bytes 4i..4i+3: low nibbles are values 4i.., high nibbles values 32+4i..
-    out[2 * i] = dev::pack_bf16(__fmaf_rn(dsc0, fmt::byte_to_float(lo, 0), ndm0), __fmaf_rn(dsc0, fmt::byte_to_float(lo, 1), ndm0));
-    out[2 * i + 1] = dev::pack_bf16(__fmaf_rn(dsc0, fmt::byte_to_float(lo, 2), ndm0), __fmaf_rn(dsc0, fmt::byte_to_float(lo, 3), ndm0));
-    out[16 + 2 * i] = dev::pack_bf16(__fmaf_rn(dsc1, fmt::byte_to_float(hi, 0), ndm1), __fmaf_rn(dsc1, fmt::byte_to_float(hi, 1), ndm1));
-    out[16 + 2 * i + 1] = dev::pack_bf16(__fmaf_rn(dsc1, fmt::byte_to_float(hi, 2), ndm1), __fmaf_rn(dsc1, fmt::byte_to_float(hi, 3), ndm1));
+    const uint32_t q = (w[i] >> shift) & 0x0F0F0F0Fu;  // bytes 4i..4i+3 -> values 4i..4i+3 of the sub-block
+    out[2 * i] = dev::pack_bf16(__fmaf_rn(dsc, fmt::byte_to_float(q, 0), ndm), __fmaf_rn(dsc, fmt::byte_to_float(q, 1), ndm));
+    out[2 * i + 1] = dev::pack_bf16(__fmaf_rn(dsc, fmt::byte_to_float(q, 2), ndm), __fmaf_rn(dsc, fmt::byte_to_float(q, 3), ndm));
   }
 }
 
@@ -149,25 +148,29 @@ __device__ __forceinline__ float sbyte_to_float(uint32_t word_x80, int i) {
   return __uint_as_float(magic) - 8388736.0f;  // 2^23 + 128
 }
 
-// Two consecutive Q8_0 blocks (68 bytes) given as 17 words starting at the first block's scale.
-__device__ __forceinline__ void q8_row64(const uint32_t (&w)[17], uint32_t (&out)[32]) {
-  const float d0 = dev::half_bits_to_float(w[0]);        // bytes 0-1
-  const float d1 = dev::half_bits_to_float(w[8] >> 16);  // bytes 34-35
+// One of two consecutive Q8_0 blocks (68 bytes, given as 17 words from the first block's scale).
+__device__ __forceinline__ void q8_half(const uint32_t (&w)[17], int half, uint32_t (&out)[16]) {
+  if (half == 0) {
+    const float d = dev::half_bits_to_float(w[0]);  // bytes 0-1; values at bytes 2..33 straddle words
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    // block 0, values 8c..8c+7 live at bytes 2+8c..9+8c: straddle three words
-    const uint32_t a = __byte_perm(w[2 * c], w[2 * c + 1], 0x5432) ^ 0x80808080u;
-    const uint32_t b = __byte_perm(w[2 * c + 1], w[2 * c + 2], 0x5432) ^ 0x80808080u;
-    out[4 * c + 0] = dev::pack_bf16(__fmul_rn(sbyte_to_float(a, 0), d0), __fmul_rn(sbyte_to_float(a, 1), d0));
-    out[4 * c + 1] = dev::pack_bf16(__fmul_rn(sbyte_to_float(a, 2), d0), __fmul_rn(sbyte_to_float(a, 3), d0));
-    out[4 * c + 2] = dev::pack_bf16(__fmul_rn(sbyte_to_float(b, 0), d0), __fmul_rn(sbyte_to_float(b, 1), d0));
-    out[4 * c + 3] = dev::pack_bf16(__fmul_rn(sbyte_to_float(b, 2), d0), __fmul_rn(sbyte_to_float(b, 3), d0));
-    // block 1, values at bytes 36+8c..: word aligned
-    const uint32_t e = w[9 + 2 * c] ^ 0x80808080u, f = w[10 + 2 * c] ^ 0x80808080u;
-    out[16 + 4 * c + 0] = dev::pack_bf16(__fmul_rn(sbyte_to_float(e, 0), d1), __fmul_rn(sbyte_to_float(e, 1), d1));
-    out[16 + 4 * c + 1] = dev::pack_bf16(__fmul_rn(sbyte_to_float(e, 2), d1), __fmul_rn(sbyte_to_float(e, 3), d1));
-    out[16 + 4 * c + 2] = dev::pack_bf16(__fmul_rn(sbyte_to_float(f, 0), d1), __fmul_rn(sbyte_to_float(f, 1), d1));
-    out[16 + 4 * c + 3] = dev::pack_bf16(__fmul_rn(sbyte_to_float(f, 2), d1), __fmul_rn(sbyte_to_float(f, 3), d1));
+    for (int c = 0; c < 4; ++c) {
+      const uint32_t a = __byte_perm(w[2 * c], w[2 * c + 1], 0x5432) ^ 0x80808080u;
+      const uint32_t b = __byte_perm(w[2 * c + 1], w[2 * c + 2], 0x5432) ^ 0x80808080u;
+      out[4 * c + 0] = dev::pack_bf16(__fmul_rn(sbyte_to_float(a, 0), d), __fmul_rn(sbyte_to_float(a, 1), d));
+      out[4 * c + 1] = dev::pack_bf16(__fmul_rn(sbyte_to_float(a, 2), d), __fmul_rn(sbyte_to_float(a, 3), d));
+      out[4 * c + 2] = dev::pack_bf16(__fmul_rn(sbyte_to_float(b, 0), d), __fmul_rn(sbyte_to_float(b, 1), d));
+      out[4 * c + 3] = dev::pack_bf16(__fmul_rn(sbyte_to_float(b, 2), d), __fmul_rn(sbyte_to_float(b, 3), d));
+    }
+  } else {
+    const float d = dev::half_bits_to_float(w[8] >> 16);  // bytes 34-35; values at bytes 36..67, word aligned
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const uint32_t e = w[9 + 2 * c] ^ 0x80808080u, f = w[10 + 2 * c] ^ 0x80808080u;
+      out[4 * c + 0] = dev::pack_bf16(__fmul_rn(sbyte_to_float(e, 0), d), __fmul_rn(sbyte_to_float(e, 1), d));
+      out[4 * c + 1] = dev::pack_bf16(__fmul_rn(sbyte_to_float(e, 2), d), __fmul_rn(sbyte_to_float(e, 3), d));
+      out[4 * c + 2] = dev::pack_bf16(__fmul_rn(sbyte_to_float(f, 0), d), __fmul_rn(sbyte_to_float(f, 1), d));
+      out[4 * c + 3] = dev::pack_bf16(__fmul_rn(sbyte_to_float(f, 2), d), __fmul_rn(sbyte_to_float(f, 3), d));
+    }
   }
 }
 
@@ -197,72 +200,60 @@ __device__ __forceinline__ void load_words_shifted(const uint8_t* row16, int off
   }
 }
 
-// IQ2_XXS: 64 values = two 8-byte groups.  `g` = the 4 words {idx_lo, signs_lo, idx_hi, signs_hi}.
-__device__ __forceinline__ void iq2_row64(float d, const uint32_t (&g)[4], const uint2* __restrict__ grid_s, uint32_t (&out)[32]) {
+// IQ2_XXS: one 8-byte group (32 values): four grid-row indices and the sign/scale word.
+__device__ __forceinline__ void iq2_half(float d, uint32_t idx4, uint32_t word, const uint2* __restrict__ grid_s, uint32_t (&out)[16]) {
+  const float db = __fmul_rn(__fmul_rn(d, 0.5f + static_cast<float>(word >> 28)), 0.25f);
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const uint32_t idx4 = g[2 * h], word = g[2 * h + 1];
-    const float db = __fmul_rn(__fmul_rn(d, 0.5f + static_cast<float>(word >> 28)), 0.25f);
+  for (int s = 0; s < 4; ++s) {
+    const uint2 mag = grid_s[(idx4 >> (8 * s)) & 255u];
+    const uint32_t sg = fmt::iq2_sign_byte((word >> (7 * s)) & 127u);
+    float v[8];
 #pragma unroll
-    for (int s = 0; s < 4; ++s) {
-      const uint2 mag = grid_s[(idx4 >> (8 * s)) & 255u];
-      const uint32_t sg = fmt::iq2_sign_byte((word >> (7 * s)) & 127u);
-      float v[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float m = __fmul_rn(db, fmt::byte_to_float(i < 4 ? mag.x : mag.y, i & 3));
-        v[i] = __uint_as_float(__float_as_uint(m) ^ (((sg >> i) & 1u) << 31));
-      }
-      const int c = 4 * h + s;
-      out[4 * c + 0] = dev::pack_bf16(v[0], v[1]);
-      out[4 * c + 1] = dev::pack_bf16(v[2], v[3]);
-      out[4 * c + 2] = dev::pack_bf16(v[4], v[5]);
-      out[4 * c + 3] = dev::pack_bf16(v[6], v[7]);
+    for (int i = 0; i < 8; ++i) {
+      const float m = __fmul_rn(db, fmt::byte_to_float(i < 4 ? mag.x : mag.y, i & 3));
+      v[i] = __uint_as_float(__float_as_uint(m) ^ (((sg >> i) & 1u) << 31));
     }
+    out[4 * s + 0] = dev::pack_bf16(v[0], v[1]);
+    out[4 * s + 1] = dev::pack_bf16(v[2], v[3]);
+    out[4 * s + 2] = dev::pack_bf16(v[4], v[5]);
+    out[4 * s + 3] = dev::pack_bf16(v[6], v[7]);
   }
 }
 
-// Unpack the 64 values this thread owns for reduction step `it` from packed stage `pk`.
-//   forward: thread = W row (0..255), the step selects which 64 of the row's values
-//   dgrad  : thread = (W row 0..63, quarter 0..3 of the 256-value column tile `ct`)
+// Unpack the 32 values this thread owns for reduction step `it` from packed stage `pk`.
+//   forward: thread = (W row 0..255, half); the step selects which 64 of the row's values
+//   dgrad  : thread = (W row 0..63, 64-value quarter 0..3 of the 256-value column tile `ct`, half)
 template <int QT, int MODE>
-__device__ __forceinline__ void unpack_row(const uint8_t* pk, int tid, int it, int ct, const uint2* grid_s, uint32_t (&out)[32]) {
+__device__ __forceinline__ void unpack_half(const uint8_t* pk, int row, int pair, int half, int it, int ct, const uint2* grid_s,
+                                            uint32_t (&out)[16]) {
   if constexpr (QT == B2G_Q4_K) {
     if constexpr (MODE == kFwd) {
-      const uint4 hdr = *reinterpret_cast<const uint4*>(pk + tid * 16);
-      const uint4 qa = *reinterpret_cast<const uint4*>(pk + 4096 + tid * 16);
-      const uint4 qb = *reinterpret_cast<const uint4*>(pk + 8192 + tid * 16);
-      q4k_row64(hdr, qa, qb, it & 3, out);
+      const uint4 hdr = *reinterpret_cast<const uint4*>(pk + row * 16);
+      const uint4 qa = *reinterpret_cast<const uint4*>(pk + 4096 + row * 16);
+      const uint4 qb = *reinterpret_cast<const uint4*>(pk + 8192 + row * 16);
+      q4k_half(hdr, qa, qb, pair, half, out);
     } else {
-      const int row = tid & 63, pair = tid >> 6;
       const uint8_t* r = pk + row * 144;
       const uint4 hdr = *reinterpret_cast<const uint4*>(r);
       const uint4 qa = *reinterpret_cast<const uint4*>(r + 16 + 32 * pair);
       const uint4 qb = *reinterpret_cast<const uint4*>(r + 32 + 32 * pair);
-      q4k_row64(hdr, qa, qb, pair, out);
+      q4k_half(hdr, qa, qb, pair, half, out);
     }
   } else if constexpr (QT == B2G_Q8_0) {
     uint32_t w[17];
-    if constexpr (MODE == kFwd) {
-      load_words_shifted<17>(pk + tid * 80, (68 * it) & 15, w);
-    } else {
-      const int row = tid & 63, pair = tid >> 6;   // byte 68*pair of the 272-byte row
-      load_words_shifted<17>(pk + row * 272 + ((68 * pair) & ~15), (68 * pair) & 15, w);
-    }
-    q8_row64(w, out);
+    if constexpr (MODE == kFwd) load_words_shifted<17>(pk + row * 80, (68 * it) & 15, w);
+    else load_words_shifted<17>(pk + row * 272 + ((68 * pair) & ~15), (68 * pair) & 15, w);  // byte 68*pair of the 272-byte row
+    q8_half(w, half, out);
   } else {
     // 66-byte super-block inside an 80-byte window; `off` (even) is where it starts.
     const int sb = MODE == kFwd ? (it >> 2) : ct;
-    const int pair = MODE == kFwd ? (it & 3) : (tid >> 6);
-    const int row = MODE == kFwd ? tid : (tid & 63);
     const int off = (66 * sb) & 15;
     const unsigned short* h = reinterpret_cast<const unsigned short*>(pk + row * 80 + off);
     const float d = dev::half_bits_to_float(h[0]);
-    const unsigned short* q = h + 1 + 8 * pair;  // 16 bytes: two groups
-    uint32_t g[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) g[i] = static_cast<uint32_t>(q[2 * i]) | (static_cast<uint32_t>(q[2 * i + 1]) << 16);
-    iq2_row64(d, g, grid_s, out);
+    const unsigned short* q = h + 1 + 8 * pair + 4 * half;  // this thread's 8-byte group
+    const uint32_t idx4 = static_cast<uint32_t>(q[0]) | (static_cast<uint32_t>(q[1]) << 16);
+    const uint32_t word = static_cast<uint32_t>(q[2]) | (static_cast<uint32_t>(q[3]) << 16);
+    iq2_half(d, idx4, word, grid_s, out);
   }
 }
 
@@ -487,21 +478,28 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
     }
   } else {
     // ============================== unpack ==============================
-    const int tid = threadIdx.x - 6 * 32;  // 0..255
+    const int tid = threadIdx.x - 6 * 32;  // 0..511
     const uint2* grid_s = reinterpret_cast<const uint2*>(smem + C::kOffGrid);
     int sp = 0, pp = 0, sb = 0, pb = 0;
     bool ok = true;
-    // destination of this thread's 128-byte row inside a B stage
-    const int drow = MODE == kFwd ? tid : (tid & 63);
-    const uint32_t doff = (MODE == kFwd ? 0u : static_cast<uint32_t>(tid >> 6) * 8192u) + static_cast<uint32_t>(drow) * 128u;
+    const int half = tid >> 8;                                   // warp-uniform
+    const int drow = MODE == kFwd ? (tid & 255) : (tid & 63);    // W row inside the stage
+    const int quarter = MODE == kFwd ? 0 : ((tid >> 6) & 3);     // dgrad: which 64 of the tile's 256 columns
+    // this thread's 64 bytes: row `drow` of sub-tile `quarter`, vectors 4*half .. 4*half+3 (128-byte swizzle)
+    const uint32_t doff = static_cast<uint32_t>(quarter) * 8192u + static_cast<uint32_t>(drow) * 128u;
     const uint32_t sw = static_cast<uint32_t>(drow & 7);
     for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
       const int ct = item % p.num_ct;
       for (int it = 0; it < p.num_iters; ++it) {
         ok = dev::mbar_wait(bar(kFullP + sp), pp, abort_flag, p.status, 401);
         if (!ok) break;
-        uint32_t out[32];
-        unpack_row<QT, MODE>(smem + C::kOffP + sp * C::kPStage, tid, it, ct, grid_s, out);
+        uint32_t out[16];
+        if (p.debug != 1)
+          unpack_half<QT, MODE>(smem + C::kOffP + sp * C::kPStage, drow, MODE == kFwd ? (it & 3) : quarter, half, it, ct, grid_s, out);
+        else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) out[i] = 0;
+        }
         __syncwarp();
         if (lane == 0) dev::mbar_arrive(bar(kEmptyP + sp));
         if (++sp == C::kPStages) { sp = 0; pp ^= 1; }
@@ -509,8 +507,9 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
         if (!ok) break;
         uint8_t* dst = smem + C::kOffB + sb * kBStage + doff;
 #pragma unroll
-        for (int c = 0; c < 8; ++c)
-          *reinterpret_cast<uint4*>(dst + ((static_cast<uint32_t>(c) ^ sw) << 4)) =
+        for (int c = 0; c < 4; ++c)
+          if (p.debug == 0 || (p.debug == 2 && out[4 * c] == 0x12345678u))
+          *reinterpret_cast<uint4*>(dst + ((static_cast<uint32_t>(4 * half + c) ^ sw) << 4)) =
               make_uint4(out[4 * c], out[4 * c + 1], out[4 * c + 2], out[4 * c + 3]);
         dev::fence_proxy_async_smem();
         __syncwarp();
@@ -576,6 +575,7 @@ int launch_impl(const Launch& L) {
   p.bias = static_cast<const __nv_bfloat16*>(L.bias);
   p.status = L.status;
   p.grid = nullptr;
+  { const char* e = getenv("B2G_QGEMM_DEBUG"); p.debug = e ? atoi(e) : 0; }
   if (QT == B2G_IQ2_XXS) {
     int rc = iq2xxs_grid(&p.grid);
     if (rc) return rc;

@@ -372,7 +372,7 @@ def _can_fuse(self: Any, lora: _ExpertLoraWeights | None) -> bool:
         return False
     if self.gate_proj.quant_type != self.up_proj.quant_type or self.gate_proj.logical_shape != self.up_proj.logical_shape:
         return False
-    if self.compute_dtype != torch.bfloat16:
+    if self.compute_dtype != torch.bfloat16 or not getattr(self, "_b2g_fused", True):
         return False
     return lora is None or (lora.gate_up_a.shape[1] <= _ops.LORA_PAD and lora.gate_up_a.dtype == torch.bfloat16)
 
