@@ -158,6 +158,111 @@ def run_cpu(steps: int, warmup: int, budget_s: float, m_full: int) -> dict:
                       f"{steps} timed steps, torch {torch.get_num_threads()} threads"}
 
 
+# ---------------------------------------------------------------------------------------------
+# MoE workload: BASELINE configs[2] on one GPU (16384 tokens) and configs[4] (65536 tokens, skewed router,
+# experts sharded over the ranks, NCCL all-to-all dispatch / combine) when launched on several.
+# ---------------------------------------------------------------------------------------------
+def run_moe(args) -> int:
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "the MoE workload has no bounded CPU sample in this harness; use the dense workload"}))
+        return 0
+    import torch.distributed as dist
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29531")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from b2g import _lib, ep, gguf_quant, ops
+
+    E, H, I, TOPK, R_LORA = 256, 2048, 512, 8, 16
+    t_total = args.tokens if args.tokens != 32768 else (16384 if world == 1 else 65536)
+    skew = world > 1 or t_total == 65536
+    t_local = t_total // world
+    e_local = E // world
+    lo = rank * e_local
+    gen = torch.Generator(device=dev).manual_seed(SEED + 1 + rank)
+
+    def packed(shape, seed):
+        out = []
+        g = torch.Generator(device=dev).manual_seed(seed)
+        for s0 in range(0, shape[0], 32):
+            n = min(32, shape[0] - s0)
+            out.append(gguf_quant.quantize_q4_k(torch.randn(n, *shape[1:], generator=g, device=dev) * 0.02))
+        return torch.cat(out, 0).reshape(-1)
+
+    gate_p, up_p, down_p = packed((e_local, I, H), 100 + rank), packed((e_local, I, H), 200 + rank), packed((e_local, H, I), 300 + rank)
+    lora = {"gate_up_a": (torch.randn(e_local, R_LORA, H, generator=gen, device=dev) / 16).bfloat16().requires_grad_(True),
+            "gate_up_b": (torch.randn(e_local, 2 * I, R_LORA, generator=gen, device=dev) * 0.01).bfloat16().requires_grad_(True),
+            "down_a": (torch.randn(e_local, R_LORA, I, generator=gen, device=dev) / 16).bfloat16().requires_grad_(True),
+            "down_b": (torch.randn(e_local, H, R_LORA, generator=gen, device=dev) * 0.01).bfloat16().requires_grad_(True)}
+    hidden = torch.randn(t_local, H, generator=gen, device=dev).bfloat16()
+    g_out = torch.randn(t_local, H, generator=gen, device=dev).bfloat16()
+    logits = torch.randn(t_local, E, generator=gen, device=dev)
+    if skew:
+        bias = torch.randn(E, generator=torch.Generator(device=dev).manual_seed(SEED + 4), device=dev) * 0.5   # same on every rank
+        logits = logits + bias
+
+    def step():
+        h = hidden.detach().requires_grad_(True)
+        for v in lora.values():
+            v.grad = None
+        idx = ops.router_topk(logits, TOPK, None, False)
+        wts = torch.softmax(logits.gather(1, idx), dim=-1)
+        out = ep.cuda_moe_layer(h, idx, wts, gate_p, up_p, down_p, Q4_K, I, E, lora, SCALING)
+        out.backward(g_out)
+        return out, h.grad
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+    ops.check_status()
+    _lib.COUNT_LAUNCHES, _lib.LAUNCHES = True, 0
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    launches = _lib.LAUNCHES
+    _lib.COUNT_LAUNCHES = False
+    clocks = sampler.stop() if rank == 0 else {}
+    ops.check_status()
+    if rank == 0:
+        peaks, peak_src = load_peaks()
+        ms_step = float(ms) / args.steps
+        rows = t_total * TOPK
+        flops = 4.0 * rows * 3 * H * I + 6.0 * rows * R_LORA * ((H + 2 * I) + (I + H))
+        peak_tf = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+        print(json.dumps({
+            "metric": "quantized MoE (grouped Q4_K experts + LoRA) fwd+bwd tokens/s", "value": t_total / (ms_step * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong" if world > 1 or t_total == 65536 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "grouped MoE Q4_K LoRA, 256 experts top-8, hidden 2048, intermediate 512 (BASELINE configs[%d])" % (4 if skew else 2),
+                       "tokens_total": t_total, "experts_per_gpu": e_local, "skewed_router": skew,
+                       "parallelism": f"ep{world} (experts sharded, NCCL all-to-all dispatch/combine)" if world > 1 else "1 GPU",
+                       "l2": "routed rows 2 GiB, larger than L2"},
+            "step_tflops": flops / (ms_step * 1e-3) / 1e12, "step_frac_of_tensor_peak_all_gpus": flops / (ms_step * 1e-3) / 1e12 / (peak_tf * world),
+            "peak_source": peak_src, "clocks": clocks, "gpu_launches": launches}))
+    dist.destroy_process_group()
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -166,7 +271,11 @@ def main() -> int:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--tokens", type=int, default=32768, help="M: tokens per step and per GPU")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="dense", choices=["dense", "moe"],
+                    help="dense: BASELINE configs[1] (default, replicas at N>1); moe: grouped Q4_K experts, expert-parallel at N>1")
     args = ap.parse_args()
+    if args.workload == "moe":
+        return run_moe(args)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

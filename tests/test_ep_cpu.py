@@ -1,0 +1,146 @@
+"""CPU, world_size 2 and 4 over gloo: the expert-parallel plan, exchange and regroup logic.
+
+The row payload moves through the same torch.distributed calls the GPU path uses; the expert
+computation is stood in for by a per-expert matmul so that no kernel is needed, and the result is
+compared with a single-process evaluation over all experts."""
+import os
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = Path(__file__).resolve().parent.parent
+for p in (str(ROOT), str(ROOT / "transformers5-qwen3.5-recipe_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+
+def _single_process(hidden, idx, wts, experts_w, k):
+    out = torch.zeros_like(hidden)
+    for t in range(hidden.shape[0]):
+        for j in range(k):
+            e = int(idx[t, j])
+            out[t] += wts[t, j] * (hidden[t] @ experts_w[e].t())
+    return out
+
+
+def _worker(rank, world, port, tokens_per_rank, e_total, k, h, result_path, fail_rank):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from b2g import ep
+    from oracle import moe_ref
+
+    g = torch.Generator().manual_seed(1234)
+    experts_w = torch.randn(e_total, h, h, generator=g, dtype=torch.float64) * 0.1
+    hidden_all = torch.randn(world * tokens_per_rank, h, generator=g, dtype=torch.float64)
+    logits = torch.randn(world * tokens_per_rank, e_total, generator=g)
+    logits[:, 0] += 2.0                                   # skewed load; some experts may stay empty
+    idx_all = logits.topk(k, 1).indices
+    wts_all = torch.softmax(logits.gather(1, idx_all), -1).double()
+    sl = slice(rank * tokens_per_rank, (rank + 1) * tokens_per_rank)
+    hidden = hidden_all[sl].clone().requires_grad_(True)
+    lo, hi = ep.expert_owner_ranges(e_total, world)[rank]
+    local_w = experts_w[lo:hi].clone().requires_grad_(True)
+
+    def route_plan_fn(idx, e):
+        plan = moe_ref.route_plan(idx, e)
+        return plan["permutation"], plan["inverse_permutation"], plan["group_sizes"]
+
+    def gather_fn(hs, perm, inverse):
+        return hs[perm // k]
+
+    def combine_fn(rows, weights, perm, inverse):
+        return (rows[inverse].view(-1, k, rows.shape[1]) * weights.unsqueeze(-1)).sum(1)
+
+    def expert_fn(rows, sizes, offsets):
+        assert sizes.dtype == torch.int32 and int(sizes.sum()) == rows.shape[0]
+        assert torch.equal(offsets, torch.cumsum(sizes, 0).to(torch.int32))
+        parts, b = [], 0
+        for e, n in enumerate(sizes.tolist()):
+            parts.append(rows[b:b + n] @ local_w[e].t())
+            b += n
+        return torch.cat(parts, 0) if parts else rows.new_zeros(0, rows.shape[1])
+
+    if fail_rank == rank:
+        # a rank that leaves between steps: it never joins the exchange; the others see a timeout error
+        dist.destroy_process_group()
+        return
+    try:
+        out = ep.expert_parallel_moe(hidden, idx_all[sl], wts_all[sl], expert_fn, e_total, route_plan_fn, gather_fn, combine_fn)
+        out.sum().backward()
+        want = _single_process(hidden_all[sl], idx_all[sl], wts_all[sl], experts_w, k)
+        ok = torch.allclose(out.detach(), want, rtol=1e-9, atol=1e-9)
+        # d(sum out)/d hidden[t] = sum_j w[t,j] * 1^T W_e ; check one token
+        t0 = 0
+        gwant = sum(wts_all[sl][t0, j] * experts_w[int(idx_all[sl][t0, j])].sum(0) for j in range(k))
+        ok = ok and torch.allclose(hidden.grad[t0], gwant, rtol=1e-9, atol=1e-9)
+        # an expert nobody routed to has an exactly zero weight gradient on its owner
+        counts = torch.bincount(idx_all.reshape(-1), minlength=e_total)
+        for e in range(lo, hi):
+            if counts[e] == 0:
+                ok = ok and float(local_w.grad[e - lo].abs().max()) == 0.0
+        torch.save({"ok": bool(ok)}, f"{result_path}.{rank}")
+    except Exception as exc:  # noqa: BLE001
+        torch.save({"ok": False, "error": repr(exc)}, f"{result_path}.{rank}")
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def _free_port():
+    import socket
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.parametrize("world,e_total,k", [(2, 8, 2), (4, 16, 3)])
+def test_expert_parallel_layer_matches_single_process(tmp_path, world, e_total, k):
+    path = str(tmp_path / "res")
+    mp.spawn(_worker, args=(world, _free_port(), 13, e_total, k, 8, path, -1), nprocs=world, join=True)
+    for r in range(world):
+        res = torch.load(f"{path}.{r}")
+        assert res["ok"], res
+
+
+def test_regroup_permutation_and_ranges():
+    from b2g import ep
+
+    counts = torch.tensor([[2, 0, 1], [1, 3, 0]])        # [source rank, local expert]
+    perm, inv = ep.regroup_permutation(counts)
+    arrival = ["a0", "a0", "a2", "b0", "b1", "b1", "b1"]  # rank a then rank b, each sorted by expert
+    assert [arrival[i] for i in perm.tolist()] == ["a0", "a0", "b0", "b1", "b1", "b1", "a2"]
+    assert torch.equal(perm[inv], torch.arange(7)) and torch.equal(inv[perm], torch.arange(7))
+    assert ep.expert_owner_ranges(256, 8)[3] == (96, 128)
+    with pytest.raises(ValueError):
+        ep.expert_owner_ranges(10, 4)
+    empty_perm, _ = ep.regroup_permutation(torch.zeros(2, 3, dtype=torch.int64))
+    assert empty_perm.numel() == 0
+
+
+def _timeout_worker(rank, world, port, result_path):
+    import datetime
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    from b2g import ep
+
+    if rank == 1:                       # leaves between steps, nothing of its own in flight
+        dist.destroy_process_group()
+        return
+    try:
+        ep.build_plan(torch.ones(4, dtype=torch.int32))
+        torch.save({"raised": False}, f"{result_path}.{rank}")
+    except Exception as exc:  # noqa: BLE001
+        torch.save({"raised": True, "error": type(exc).__name__}, f"{result_path}.{rank}")
+
+
+def test_a_missing_rank_surfaces_as_an_error_not_a_hang(tmp_path):
+    path = str(tmp_path / "res")
+    mp.spawn(_timeout_worker, args=(2, _free_port(), path), nprocs=2, join=True)
+    res = torch.load(f"{path}.0")
+    assert res["raised"], res

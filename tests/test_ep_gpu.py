@@ -1,0 +1,53 @@
+"""GPU: the expert-parallel layer on the libb2g kernels.  With one GPU the process group has a single
+rank (the exchange degenerates to a local copy through NCCL); the result must equal the plain
+single-device expert layer bit for bit."""
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+
+from oracle import gguf_oracle as go
+
+pytestmark = pytest.mark.gpu
+
+
+def test_single_rank_expert_parallel_equals_local_layer(cuda):
+    from b2g import autograd as ag, ep, routing
+
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29577")
+    if not dist.is_initialized():
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=cuda)
+    try:
+        e, h, i, t, k, r = 16, 512, 256, 300, 4, 16
+        g = torch.Generator().manual_seed(3)
+        rng = np.random.default_rng(3)
+        pk = [torch.from_numpy(go.quantize((rng.standard_normal(s) * 0.02).astype(np.float32), go.Q4_K)).to(cuda).reshape(-1)
+              for s in ((e, i, h), (e, i, h), (e, h, i))]
+        lora = {"gate_up_a": (torch.randn(e, r, h, generator=g) / 16).bfloat16().to(cuda), "gate_up_b": (torch.randn(e, 2 * i, r, generator=g) * 0.01).bfloat16().to(cuda),
+                "down_a": (torch.randn(e, r, i, generator=g) / 16).bfloat16().to(cuda), "down_b": (torch.randn(e, h, r, generator=g) * 0.01).bfloat16().to(cuda)}
+        hidden = torch.randn(t, h, generator=g).bfloat16().to(cuda)
+        logits = torch.randn(t, e, generator=g)
+        idx = logits.topk(k, 1).indices.to(cuda)
+        wts = torch.softmax(logits.gather(1, idx.cpu()), -1).to(cuda)
+        gout = torch.randn(t, h, generator=g).bfloat16().to(cuda)
+
+        h1 = hidden.clone().requires_grad_(True)
+        l1 = {n: v.clone().requires_grad_(True) for n, v in lora.items()}
+        out1 = ep.cuda_moe_layer(h1, idx, wts, *pk, go.Q4_K, i, e, l1, 2.0)
+        out1.backward(gout)
+
+        h2 = hidden.clone().requires_grad_(True)
+        l2 = {n: v.clone().requires_grad_(True) for n, v in lora.items()}
+        plan = routing.build_plan(h2, idx, wts, e)
+        ex = ag.grouped_lora_experts(plan.selected_hidden_states, *pk, go.Q4_K, go.Q4_K, i, torch.arange(e, device=cuda), plan.group_offsets,
+                                     plan.group_offsets, l2["gate_up_a"], l2["gate_up_b"], l2["down_a"], l2["down_b"], 2.0, 0.0)
+        out2 = routing.combine(ex, plan)
+        out2.backward(gout)
+        assert torch.equal(out1, out2) and torch.equal(h1.grad, h2.grad)
+        for n in lora:
+            assert torch.equal(l1[n].grad, l2[n].grad), n
+    finally:
+        dist.destroy_process_group()
