@@ -87,6 +87,22 @@ B2G_API int64_t b2g_lora_wgrad_workspace_bytes(int64_t M, int64_t C);
 B2G_API int b2g_lora_wgrad(const void* s, const void* t, float scale, void* out, int transpose_out, void* workspace,
                    int64_t workspace_bytes, int64_t M, int64_t C, int r, void* stream);
 
+/* The same factor gradient for callers that cannot allocate device memory (a plug-in inside another
+ * framework's memory plan, a host that was handed only input and output buffers, a process whose pool is
+ * fully committed): the split partials live in a fixed 8 MiB array inside the library image, which every
+ * GPU that loads the library holds until exit.  This entry has no counterpart in the reference.
+ *   - allocates nothing: no cudaMalloc / cudaFree, no allocating library routine;
+ *   - shapes whose scratch need (b2g_lora_wgrad_workspace_bytes) exceeds b2g_lora_wgrad_static_max_bytes()
+ *     are rejected with B2G_E_ARG; use b2g_lora_wgrad with your own workspace for those;
+ *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress, with that
+ *     device current) and caches it: make that first call before any stream capture begins;
+ *   - all calls share the one array.  It keeps the previous call's partials; each call overwrites every
+ *     entry it later reads, so nothing needs clearing, but two calls that overlap on the GPU (different
+ *     streams, or threads without ordering) race on it: order them. */
+B2G_API int64_t b2g_lora_wgrad_static_max_bytes(void);
+B2G_API int b2g_lora_wgrad_static(const void* s, const void* t, float scale, void* out, int transpose_out, int64_t M,
+                          int64_t C, int r, void* stream);
+
 /* ---- router / routing ------------------------------------------------------------------------ */
 
 /* Top-k expert ids per token, best first, ties to the smaller id.  logits_dtype: 0 = bf16, 1 = fp32;

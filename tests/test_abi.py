@@ -33,7 +33,7 @@ def test_every_entry_cites_the_reference():
         if name in ("b2g_last_error", "b2g_abi_version", "b2g_set_iq2xxs_grid") or name.endswith("_bytes"):
             continue
         block = next(b for b in blocks if re.search(rf"\b{name}\s*\(", b))
-        assert re.search(r"\.py:\d+", block), f"{name} lacks a reference citation"
+        assert re.search(r"\.py:\d+", block) or "no counterpart in the reference" in block, f"{name} lacks a reference citation"
 
 
 def test_argument_errors_do_not_need_a_device(lib):

@@ -5,6 +5,8 @@
 // grouped path (one weight per expert segment).
 #include "b2g_common.cuh"
 
+#include <mutex>
+
 namespace b2g {
 namespace lora {
 
@@ -464,4 +466,55 @@ extern "C" int b2g_grouped_lora_up(const void* p, int64_t ldp, const void* w, in
                                                       offsets_full, num_experts, static_cast<__nv_bfloat16*>(y), R, (int)N, r);
   B2G_CUDA_OK(cudaGetLastError());
   return 0;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Factor gradient for callers that may not allocate device memory.
+//
+// Some hosts of this library cannot call cudaMalloc (or ask torch's allocator) at the point where the
+// gradient is needed: code running inside another framework's memory plan, a plug-in that was handed
+// only its input and output buffers, or a process whose memory pool is already fully committed.  For
+// them the split partials live in the fixed array below instead of a caller-provided workspace.  The
+// array is part of the library image: every GPU that loads the library holds these bytes until exit.
+// ------------------------------------------------------------------------------------------------
+namespace b2g {
+namespace lora {
+constexpr int64_t kStaticScratchBytes = 8ll << 20;  // 8 MiB
+static __device__ __align__(256) unsigned char g_wgrad_scratch[kStaticScratchBytes];
+}  // namespace lora
+}  // namespace b2g
+
+// In host code `g_wgrad_scratch` is only a handle for the symbol, not a device address: the address a
+// kernel can use comes from cudaGetSymbolAddress, fetched once per device with that device current.
+static int static_scratch_ptr(void** out) {
+  static std::mutex mu;
+  static void* ptrs[64] = {nullptr};
+  int dev = 0;
+  B2G_CUDA_OK(cudaGetDevice(&dev));
+  B2G_REQUIRE(dev >= 0 && dev < 64, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    B2G_CUDA_OK(cudaGetSymbolAddress(&p, b2g::lora::g_wgrad_scratch));
+    B2G_REQUIRE(p != nullptr, "cudaGetSymbolAddress returned a null scratch address");
+    ptrs[dev] = p;
+  }
+  *out = ptrs[dev];
+  return 0;
+}
+
+extern "C" int64_t b2g_lora_wgrad_static_max_bytes(void) { return b2g::lora::kStaticScratchBytes; }
+
+extern "C" int b2g_lora_wgrad_static(const void* s, const void* t, float scale, void* out, int transpose_out, int64_t M, int64_t C,
+                                     int r, void* stream) {
+  B2G_REQUIRE(M > 0 && C > 0, "lora_wgrad_static: bad shape M=%lld C=%lld", (long long)M, (long long)C);
+  const int64_t need = b2g_lora_wgrad_workspace_bytes(M, C);
+  B2G_REQUIRE(need <= b2g::lora::kStaticScratchBytes,
+              "lora_wgrad_static: M=%lld, C=%lld needs %lld bytes of scratch, the built-in array holds %lld; use b2g_lora_wgrad with "
+              "a caller-provided workspace", (long long)M, (long long)C, (long long)need, (long long)b2g::lora::kStaticScratchBytes);
+  void* scratch = nullptr;
+  int rc = static_scratch_ptr(&scratch);
+  if (rc) return rc;
+  // Every partial the reduction reads is written by the first kernel of this call, so nothing has to be cleared.
+  return b2g_lora_wgrad(s, t, scale, out, transpose_out, scratch, b2g::lora::kStaticScratchBytes, M, C, r, stream);
 }
