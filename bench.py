@@ -233,10 +233,11 @@ def run_moe(args) -> int:
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    torch.cuda.nvtx.range_push("b2g_timed")       # lets a profiler pick out the timed steps
+    torch.cuda.profiler.start()                   # `ncu --profile-from-start off` then sees only the timed steps (all threads)
     for _ in range(args.steps):
         step()
-    torch.cuda.nvtx.range_pop()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
     e1.record()
     barrier()
     ms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
@@ -353,10 +354,11 @@ def main() -> int:
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    torch.cuda.nvtx.range_push("b2g_timed")       # lets a profiler pick out the timed steps
+    torch.cuda.profiler.start()                   # `ncu --profile-from-start off` then sees only the timed steps (all threads)
     for _ in range(args.steps):
         step(x_dev, dys_dev)
-    torch.cuda.nvtx.range_pop()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
     e1.record()
     barrier()
     ms_total = e0.elapsed_time(e1)

@@ -36,7 +36,7 @@ def test_single_rank_expert_parallel_equals_local_layer(cuda):
 
         h1 = hidden.clone().requires_grad_(True)
         l1 = {n: v.clone().requires_grad_(True) for n, v in lora.items()}
-        out1 = ep.cuda_moe_layer(h1, idx, wts, *pk, go.Q4_K, i, e, l1, 2.0)
+        out1 = ep.cuda_moe_layer(h1, idx, wts, *pk, go.Q4_K, i, e, l1, 2.0, always_exchange=True)   # through NCCL and the regroup
         out1.backward(gout)
 
         h2 = hidden.clone().requires_grad_(True)

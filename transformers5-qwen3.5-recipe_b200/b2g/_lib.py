@@ -73,7 +73,7 @@ def load() -> C.CDLL:
 # Kernels launched by one call of each entry point (the benchmark reports the total it issued).
 KERNELS_PER_CALL = {
     "b2g_dequant": 1, "b2g_qlinear_fwd": 1, "b2g_qlinear_dgrad": 1, "b2g_lora_down": 1, "b2g_lora_wgrad": 2, "b2g_lora_wgrad_static": 2,
-    "b2g_router_topk": 1, "b2g_route_plan": 3, "b2g_route_gather": 1, "b2g_route_gather_bwd": 1, "b2g_route_combine": 1,
+    "b2g_router_topk": 1, "b2g_route_plan": 4, "b2g_route_gather": 1, "b2g_route_gather_bwd": 1, "b2g_route_combine": 1,
     "b2g_route_combine_bwd": 1, "b2g_grouped_schedule": 1, "b2g_grouped_fwd": 1, "b2g_grouped_dgrad": 1,
     "b2g_grouped_lora_down": 1, "b2g_grouped_lora_wgrad": 1, "b2g_grouped_lora_up": 1, "b2g_swiglu_fwd": 1, "b2g_swiglu_bwd": 1,
 }

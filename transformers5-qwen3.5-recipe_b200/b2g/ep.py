@@ -133,7 +133,7 @@ ExpertFn = Callable[[torch.Tensor, torch.Tensor, torch.Tensor], torch.Tensor]
 
 
 def expert_parallel_moe(hidden: torch.Tensor, top_k_index: torch.Tensor, top_k_weights: torch.Tensor, expert_fn: ExpertFn,
-                        num_experts: int, route_plan_fn, gather_fn, combine_fn, group=None) -> torch.Tensor:
+                        num_experts: int, route_plan_fn, gather_fn, combine_fn, group=None, always_exchange: bool = False) -> torch.Tensor:
     """One expert-parallel MoE layer.
 
     ``route_plan_fn(top_k_index, num_experts)`` -> (perm, inverse, group_sizes) of the stable sort;
@@ -142,8 +142,13 @@ def expert_parallel_moe(hidden: torch.Tensor, top_k_index: torch.Tensor, top_k_w
     outputs of this rank's experts for rows grouped by local expert.  All are differentiable.
     """
     perm, inverse, group_sizes = route_plan_fn(top_k_index, num_experts)
-    plan = build_plan(group_sizes, group)
     selected = gather_fn(hidden, perm, inverse)
+    if dist.get_world_size(group) == 1 and not always_exchange:
+        # one rank owns every expert: rows are already grouped by expert, nothing to exchange
+        sizes = group_sizes.to(torch.int32)
+        local_out = expert_fn(selected, sizes, torch.cumsum(sizes, 0).to(torch.int32))
+        return combine_fn(local_out, top_k_weights, perm, inverse)
+    plan = build_plan(group_sizes, group)
     local_rows = dispatch(selected, plan, group)
     local_out = expert_fn(local_rows, plan.local_sizes, plan.local_offsets)
     returned = combine(local_out, plan, group)
@@ -153,7 +158,7 @@ def expert_parallel_moe(hidden: torch.Tensor, top_k_index: torch.Tensor, top_k_w
 # ---- the CUDA instantiation ------------------------------------------------------------------------
 def cuda_moe_layer(hidden: torch.Tensor, top_k_index: torch.Tensor, top_k_weights: torch.Tensor, gate_payload: torch.Tensor,
                    up_payload: torch.Tensor, down_payload: torch.Tensor, quant_type: int, inter_dim: int, num_experts: int,
-                   lora: Optional[dict] = None, scaling: float = 1.0, group=None) -> torch.Tensor:
+                   lora: Optional[dict] = None, scaling: float = 1.0, group=None, always_exchange: bool = False) -> torch.Tensor:
     """Expert-parallel layer on the libb2g kernels.  Payloads / LoRA factors hold only THIS rank's experts
     ([E/G, ...]); ``top_k_index`` carries global expert ids."""
     from . import autograd as ag
@@ -176,4 +181,5 @@ def cuda_moe_layer(hidden: torch.Tensor, top_k_index: torch.Tensor, top_k_weight
                                        idx, local_offsets, local_offsets, lo.get("gate_up_a"), lo.get("gate_up_b"),
                                        lo.get("down_a"), lo.get("down_b"), scaling, 0.0)
 
-    return expert_parallel_moe(hidden, top_k_index, top_k_weights, expert_fn, num_experts, route_plan_fn, gather_fn, combine_fn, group)
+    return expert_parallel_moe(hidden, top_k_index, top_k_weights, expert_fn, num_experts, route_plan_fn, gather_fn, combine_fn, group,
+                               always_exchange)

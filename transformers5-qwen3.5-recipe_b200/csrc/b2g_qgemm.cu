@@ -7,17 +7,24 @@
 //   grouped forward   per ragged expert segment, one or two (gate, up) weight tensors
 //   grouped dgrad     per segment, one or two gradient/weight pairs summed in one accumulator
 //
-// Tile: 128*MT rows x 256 output columns, reduction step 64.  Per step the CTA holds
+// CTAs work in PAIRS (a cluster of two, tcgen05 cta_group::2).  A pair owns a tile of up to 512 rows x
+// 256 output columns: each MMA is 256 x 256 x 16 across the pair, each CTA holding 128 of its rows in
+// TMEM, and two such row blocks (MT = 2) share every unpacked weight tile.  Per reduction step of 64 a
+// CTA holds
 //   A  : MT x [128 rows x 64] bf16, 128-byte swizzle, written by TMA          (A operand, K-major)
-//   B  : [R rows of W x 64 k] bf16 sub-tiles, 128-byte swizzle, written by the unpack warps.
-//        forward: one sub-tile of 256 W rows  -> B operand K-major  (N = W rows, K = k)
-//        dgrad  : four sub-tiles of 64 W rows -> B operand MN-major (N = k,      K = W rows)
-//        The unpack warps therefore write the same [w_row][k] layout in both directions; only the
-//        shared-memory descriptors differ, so no packed transpose is ever built.
-// The LoRA up-projection is one extra K=16 MMA per tile on 32-byte-swizzled [rows x 16] tiles.
+//   B  : ITS HALF of the weight tile, 128-byte swizzled bf16 written by its unpack warps:
+//        forward: [128 W rows x 64 k]       -> B operand K-major  (N = W rows, K = k)
+//        dgrad  : 2 x [64 W rows x 64 k]    -> B operand MN-major (N = k,      K = W rows)
+//        The unpack warps write the same [w_row][k] layout in both directions; only the shared-memory
+//        descriptors differ, so no packed transpose is ever built.
+// so each packed block is unpacked once per 512 rows, and each CTA reads only half of B from its own
+// shared memory.  The LoRA up-projection is one extra K=16 MMA per row block on 32-byte-swizzled tiles.
 //
-// Warp roles (704 threads): 0 = TMA producer, 1 = MMA issuer + TMEM owner, 2-5 = epilogue
-// (TMEM -> registers -> global), 6-21 = unpack.  All mbarrier waits are bounded.
+// Warp roles (448 threads per CTA): 0 = TMA producer, 1 = MMA issuer (first CTA of the pair only) + TMEM
+// owner, 2-5 = epilogue (TMEM -> registers -> global), 6-13 = unpack.  Barriers that gate the MMA
+// (A / B / LoRA tiles ready, accumulator drained) live in the first CTA and collect arrivals from both;
+// barriers that release buffers are signalled in both CTAs by tcgen05.commit.  No TMA multicast is used:
+// every CTA loads its own tiles.  All mbarrier waits are bounded.
 #include "b2g_formats.cuh"
 #include <cstdlib>
 
@@ -27,53 +34,57 @@ int iq2xxs_grid(const uint2** out);
 namespace qg {
 
 constexpr int kFwd = 0, kDgrad = 1;
-constexpr int kBM = 128;          // rows per MMA
-constexpr int kBN = 256;          // output columns per tile
+constexpr int kBM = 128;          // rows per CTA and row block
+constexpr int kPairRows = 256;    // rows per row block across the pair
+constexpr int kBN = 256;          // output columns per tile (MMA N across the pair)
+constexpr int kBNh = 128;         // of which this CTA unpacks / holds
 constexpr int kBK = 64;           // reduction step
+constexpr int kMT = 2;            // row blocks per tile
+constexpr int kTileRows = kPairRows * kMT;  // 512
 constexpr int kATile = kBM * kBK * 2;       // 16384
-constexpr int kBStage = kBN * kBK * 2;      // 32768
-constexpr int kBStages = 2;
-constexpr int kUnpackWarps = 16;          // 512 threads: (256 W rows x 2 halves) or (64 rows x 4 quarters x 2 halves)
+constexpr int kBStage = kBNh * kBK * 2;     // 16384
+constexpr int kBStages = 3;
+constexpr int kUnpackWarps = 8;             // 256 threads: (128 W rows x 2 halves) or (64 rows x 2 quarters x 2 halves)
 constexpr int kThreads = 32 * (6 + kUnpackWarps);
 constexpr int kLoraATile = kBM * 32;        // [128 x 16] bf16
-constexpr int kLoraBTile = kBN * 32;        // 8192 either way
+constexpr int kLoraBTile = kBNh * 32;       // 4096 either way
 constexpr int kTmemCols = 512;
 
-// Packed-stage geometry: what one reduction step needs of the packed weight, as TMA boxes over the
-// payload viewed as uint32 [rows, pitch/4].  x coordinates are always multiples of 4 words (16 bytes).
+// Packed-stage geometry: what one reduction step needs of the packed weight in ONE CTA, as TMA boxes over
+// the payload viewed as uint32 [rows, pitch/4].  x coordinates are always multiples of 4 words (16 bytes).
 template <int QT, int MODE> struct Packed;
 // Q4_K forward: header (d, dmin, 12 scale bytes) + the 32 nibble bytes of one 64-value pair, as
-// three [256 rows x 16 B] boxes so that each thread reads its row with conflict-free 16-byte loads.
-template <> struct Packed<B2G_Q4_K, kFwd> { static constexpr int kBoxWords = 4, kBoxRows = 256, kBoxes = 3, kBytes = 3 * 4096; };
-// Q4_K dgrad: whole 144-byte super-blocks of 64 rows (row stride 144 B: conflict-free 16-byte loads).
-template <> struct Packed<B2G_Q4_K, kDgrad> { static constexpr int kBoxWords = 36, kBoxRows = 64, kBoxes = 1, kBytes = 64 * 144; };
-// Q8_0 forward: two 34-byte blocks start at byte 68*step; an 80-byte window from the 16-byte boundary below covers them
-// (the start is at most 12 bytes into the window).
-template <> struct Packed<B2G_Q8_0, kFwd> { static constexpr int kBoxWords = 20, kBoxRows = 256, kBoxes = 1, kBytes = 256 * 80; };
+// three [128 rows x 16 B] boxes so that each thread reads its row with conflict-free 16-byte loads.
+template <> struct Packed<B2G_Q4_K, kFwd> { static constexpr int kBoxWords = 4, kBoxRows = 128, kBytes = 3 * 2048; };
+// Q4_K dgrad: whole 144-byte super-blocks of 64 rows (row stride 144 B: conflict-free 16-byte loads);
+// each CTA decodes the two 64-value pairs of its 128 columns.
+template <> struct Packed<B2G_Q4_K, kDgrad> { static constexpr int kBoxWords = 36, kBoxRows = 64, kBytes = 64 * 144; };
+// Q8_0 forward: two 34-byte blocks start at byte 68*step; an 80-byte window from the 16-byte boundary below
+// covers them (the start is at most 12 bytes into the window).
+template <> struct Packed<B2G_Q8_0, kFwd> { static constexpr int kBoxWords = 20, kBoxRows = 128, kBytes = 128 * 80; };
 // Q8_0 dgrad: eight blocks (272 B = 17 x 16) per row.
-template <> struct Packed<B2G_Q8_0, kDgrad> { static constexpr int kBoxWords = 68, kBoxRows = 64, kBoxes = 1, kBytes = 64 * 272; };
+template <> struct Packed<B2G_Q8_0, kDgrad> { static constexpr int kBoxWords = 68, kBoxRows = 64, kBytes = 64 * 272; };
 // IQ2_XXS: 66-byte super-blocks are not 16-byte aligned; an 80-byte window from the boundary below covers one
 // (the start is at most 14 bytes into the window).
-template <> struct Packed<B2G_IQ2_XXS, kFwd> { static constexpr int kBoxWords = 20, kBoxRows = 256, kBoxes = 1, kBytes = 256 * 80; };
-template <> struct Packed<B2G_IQ2_XXS, kDgrad> { static constexpr int kBoxWords = 20, kBoxRows = 64, kBoxes = 1, kBytes = 64 * 80; };
+template <> struct Packed<B2G_IQ2_XXS, kFwd> { static constexpr int kBoxWords = 20, kBoxRows = 128, kBytes = 128 * 80; };
+template <> struct Packed<B2G_IQ2_XXS, kDgrad> { static constexpr int kBoxWords = 20, kBoxRows = 64, kBytes = 64 * 80; };
 
-template <int QT, int MODE, int MT>
+template <int QT, int MODE>
 struct Cfg {
   using P = Packed<QT, MODE>;
-  static constexpr int kAStages = MT == 1 ? 4 : 3;
-  static constexpr int kAStage = MT * kATile;
-  static constexpr int kPStages = (P::kBytes > 16384 && MT == 2) ? 2 : 3;
+  static constexpr int kAStages = 4;
+  static constexpr int kAStage = kMT * kATile;
+  static constexpr int kPStages = P::kBytes > 12288 ? 2 : 3;
   static constexpr int kPStage = (P::kBytes + 1023) / 1024 * 1024;
-  static constexpr int kAccBufs = MT == 1 ? 2 : 1;
   // shared-memory map (offsets from a 1024-byte aligned base)
   static constexpr int kOffA = 0;
   static constexpr int kOffB = kOffA + kAStages * kAStage;
   static constexpr int kOffP = kOffB + kBStages * kBStage;
   static constexpr int kOffLA = kOffP + kPStages * kPStage;
-  static constexpr int kOffLB = kOffLA + MT * kLoraATile;
+  static constexpr int kOffLB = kOffLA + kMT * kLoraATile;
   static constexpr int kOffGrid = kOffLB + kLoraBTile;                      // IQ2_XXS table (2 KB)
   static constexpr int kOffBar = kOffGrid + (QT == B2G_IQ2_XXS ? 2048 : 0);
-  static constexpr int kNumBars = 2 * kAStages + 2 * kBStages + 2 * kPStages + 2 + 2 * kAccBufs;
+  static constexpr int kNumBars = 2 * kAStages + 2 * kBStages + 2 * kPStages + 2 + 2;
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;                   // tmem slot, abort flag
   static constexpr int kSmemBytes = kOffMisc + 16 + 1024;                   // + alignment slack
   static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
@@ -103,10 +114,8 @@ struct Params {
 
 struct Tile { int expert, row0, rows, ct; };
 
-template <int MT>
 __device__ __forceinline__ int num_m_tiles(const Params& p) { return p.tiles ? p.tiles[0].x : p.dense_m_tiles; }
 
-template <int MT>
 __device__ __forceinline__ Tile get_tile(const Params& p, int item) {
   Tile t;
   const int mt = item / p.num_ct;
@@ -115,9 +124,9 @@ __device__ __forceinline__ Tile get_tile(const Params& p, int item) {
     const int4 e = p.tiles[1 + mt];
     t.expert = e.x; t.row0 = e.y; t.rows = e.z;
   } else {
-    t.expert = 0; t.row0 = mt * (kBM * MT);
+    t.expert = 0; t.row0 = mt * kTileRows;
     const int left = p.m_total - t.row0;
-    t.rows = left < kBM * MT ? left : kBM * MT;
+    t.rows = left < kTileRows ? left : kTileRows;
   }
   return t;
 }
@@ -221,16 +230,16 @@ __device__ __forceinline__ void iq2_half(float d, uint32_t idx4, uint32_t word, 
 }
 
 // Unpack the 32 values this thread owns for reduction step `it` from packed stage `pk`.
-//   forward: thread = (W row 0..255, half); the step selects which 64 of the row's values
-//   dgrad  : thread = (W row 0..63, 64-value quarter 0..3 of the 256-value column tile `ct`, half)
+//   forward: thread = (one of this CTA's 128 W rows, half); the step selects which 64 of the row's values
+//   dgrad  : thread = (W row 0..63, 64-value quarter `pair` (0..3) of the 256-value column tile `ct`, half)
 template <int QT, int MODE>
 __device__ __forceinline__ void unpack_half(const uint8_t* pk, int row, int pair, int half, int it, int ct, const uint2* grid_s,
                                             uint32_t (&out)[16]) {
   if constexpr (QT == B2G_Q4_K) {
     if constexpr (MODE == kFwd) {
       const uint4 hdr = *reinterpret_cast<const uint4*>(pk + row * 16);
-      const uint4 qa = *reinterpret_cast<const uint4*>(pk + 4096 + row * 16);
-      const uint4 qb = *reinterpret_cast<const uint4*>(pk + 8192 + row * 16);
+      const uint4 qa = *reinterpret_cast<const uint4*>(pk + 2048 + row * 16);
+      const uint4 qb = *reinterpret_cast<const uint4*>(pk + 4096 + row * 16);
       q4k_half(hdr, qa, qb, pair, half, out);
     } else {
       const uint8_t* r = pk + row * 144;
@@ -257,12 +266,12 @@ __device__ __forceinline__ void unpack_half(const uint8_t* pk, int row, int pair
   }
 }
 
-template <int QT, int MODE, int MT>
+template <int QT, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_a1,
              const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1,
              const __grid_constant__ CUtensorMap tm_la, const __grid_constant__ CUtensorMap tm_lb) {
-  using C = Cfg<QT, MODE, MT>;
+  using C = Cfg<QT, MODE>;
   using P = Packed<QT, MODE>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -270,23 +279,26 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
   const uint32_t sA = sbase + C::kOffA, sB = sbase + C::kOffB, sP = sbase + C::kOffP;
   const uint32_t sLA = sbase + C::kOffLA, sLB = sbase + C::kOffLB;
   const uint32_t bars = sbase + C::kOffBar;
-  // barrier indices
+  // barrier indices.  "Full" barriers of A / B / LoRA and "accumulator empty" are used in the pair's first CTA only.
   constexpr int kFullA = 0, kEmptyA = kFullA + C::kAStages, kFullB = kEmptyA + C::kAStages, kEmptyB = kFullB + kBStages,
                 kFullP = kEmptyB + kBStages, kEmptyP = kFullP + C::kPStages, kFullL = kEmptyP + C::kPStages, kEmptyL = kFullL + 1,
-                kAccFull = kEmptyL + 1, kAccEmpty = kAccFull + C::kAccBufs;
+                kAccFull = kEmptyL + 1, kAccEmpty = kAccFull + 1;
   auto bar = [&](int i) { return bars + 8u * i; };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + C::kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::kOffMisc + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = dev::cluster_ctarank();   // 0 = first CTA of the pair (issues the MMAs)
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < C::kAStages; ++i) { dev::mbar_init(bar(kFullA + i), 1); dev::mbar_init(bar(kEmptyA + i), 1); }
-    for (int i = 0; i < kBStages; ++i) { dev::mbar_init(bar(kFullB + i), kUnpackWarps); dev::mbar_init(bar(kEmptyB + i), 1); }
+    for (int i = 0; i < kBStages; ++i) { dev::mbar_init(bar(kFullB + i), 2 * kUnpackWarps); dev::mbar_init(bar(kEmptyB + i), 1); }
     for (int i = 0; i < C::kPStages; ++i) { dev::mbar_init(bar(kFullP + i), 1); dev::mbar_init(bar(kEmptyP + i), kUnpackWarps); }
     dev::mbar_init(bar(kFullL), 1);
     dev::mbar_init(bar(kEmptyL), 1);
-    for (int i = 0; i < C::kAccBufs; ++i) { dev::mbar_init(bar(kAccFull + i), 1); dev::mbar_init(bar(kAccEmpty + i), 4); }
+    dev::mbar_init(bar(kAccFull), 1);
+    dev::mbar_init(bar(kAccEmpty), 8);   // four epilogue warps in each CTA
     *abort_flag = 0;
     dev::fence_barrier_init();
     dev::fence_proxy_async_smem();
@@ -298,36 +310,42 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
     for (int i = threadIdx.x; i < 256; i += kThreads) gs[i] = p.grid[i];
   }
   if (warp == 1) {
-    dev::tmem_alloc(dev::smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
-    dev::tmem_relinquish();
+    dev::tmem_alloc_pair(dev::smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
+    dev::tmem_relinquish_pair();
   }
   dev::tc_fence_before();
   __syncthreads();
+  dev::cluster_sync_all();             // both CTAs' barriers exist before anyone signals across the pair
   dev::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int total_items = num_m_tiles<MT>(p) * p.num_ct;
+  const int total_items = num_m_tiles(p) * p.num_ct;
+  // first-CTA copies of the barriers that collect arrivals from both CTAs
+  const uint32_t lead_full_a = dev::map_to_cta(bar(kFullA), 0), lead_full_b = dev::map_to_cta(bar(kFullB), 0);
+  const uint32_t lead_full_l = dev::map_to_cta(bar(kFullL), 0), lead_acc_empty = dev::map_to_cta(bar(kAccEmpty), 0);
 
   if (warp == 0) {
     // ============================== TMA producer ==============================
     if (lane == 0) {
       int sa = 0, pa = 0, sp = 0, pp = 0, pl = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-        const Tile t = get_tile<MT>(p, item);
-        const int nmt = (MT == 2 && t.rows > kBM) ? 2 : 1;
+      for (int item = pair; item < total_items && ok; item += num_pairs) {
+        const Tile t = get_tile(p, item);
+        const int nmt = t.rows > kPairRows ? 2 : 1;
         int fseg = 0, col0 = 0;
         if (MODE == kFwd) { fseg = t.ct / p.ct_per_seg; col0 = (t.ct - fseg * p.ct_per_seg) * kBN; }
         else col0 = t.ct * kBN;
+        const int my_row0 = t.row0 + static_cast<int>(rank) * kBM;
         if (p.has_lora) {
           ok = dev::mbar_wait(bar(kEmptyL), pl ^ 1, abort_flag, p.status, 101);
           if (!ok) break;
-          dev::mbar_arrive_expect_tx(bar(kFullL), nmt * kLoraATile + kLoraBTile);
-          for (int m = 0; m < nmt; ++m) dev::tma_load_2d(sLA + m * kLoraATile, &tm_la, bar(kFullL), 0, t.row0 + m * kBM);
+          if (rank == 0) dev::mbar_arrive_expect_tx(bar(kFullL), 2 * (nmt * kLoraATile + kLoraBTile));
+          for (int m = 0; m < nmt; ++m) dev::tma_load_2d_pair(sLA + m * kLoraATile, &tm_la, lead_full_l, 0, my_row0 + m * kPairRows);
           if (MODE == kFwd) {
-            dev::tma_load_2d(sLB, &tm_lb, bar(kFullL), 0, t.expert * p.lora_rows + fseg * p.n + col0);
+            dev::tma_load_2d_pair(sLB, &tm_lb, lead_full_l, 0, t.expert * p.lora_rows + fseg * p.n + col0 + static_cast<int>(rank) * kBNh);
           } else {
-            for (int i = 0; i < 4; ++i) dev::tma_load_2d(sLB + i * 2048, &tm_lb, bar(kFullL), col0 + 64 * i, t.expert * 16);
+            for (int i = 0; i < 2; ++i)
+              dev::tma_load_2d_pair(sLB + i * 2048, &tm_lb, lead_full_l, col0 + static_cast<int>(rank) * kBNh + 64 * i, t.expert * 16);
           }
           pl ^= 1;
         }
@@ -336,10 +354,10 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
           if (MODE == kDgrad) { seg = it / p.iters_per_seg; red0 = (it - seg * p.iters_per_seg) * kBK; }
           ok = dev::mbar_wait(bar(kEmptyA + sa), pa ^ 1, abort_flag, p.status, 102);
           if (!ok) break;
-          dev::mbar_arrive_expect_tx(bar(kFullA + sa), nmt * kATile);
+          if (rank == 0) dev::mbar_arrive_expect_tx(bar(kFullA + sa), 2 * nmt * kATile);   // bytes of both CTAs
           const CUtensorMap* am = (MODE == kDgrad && seg) ? &tm_a1 : &tm_a0;
           for (int m = 0; m < nmt; ++m)
-            dev::tma_load_2d(sA + sa * C::kAStage + m * kATile, am, bar(kFullA + sa), red0, t.row0 + m * kBM);
+            dev::tma_load_2d_pair(sA + sa * C::kAStage + m * kATile, am, lead_full_a + 8u * sa, red0, my_row0 + m * kPairRows);
           if (++sa == C::kAStages) { sa = 0; pa ^= 1; }
 
           ok = dev::mbar_wait(bar(kEmptyP + sp), pp ^ 1, abort_flag, p.status, 103);
@@ -348,12 +366,12 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
           const CUtensorMap* wm = seg ? &tm_w1 : &tm_w0;
           const uint32_t dst = sP + sp * C::kPStage;
           if (MODE == kFwd) {
-            const int y = t.expert * p.n + col0;
+            const int y = t.expert * p.n + col0 + static_cast<int>(rank) * kBNh;
             if (QT == B2G_Q4_K) {
               const int xb = 36 * (it >> 2), xq = xb + 4 + 8 * (it & 3);
               dev::tma_load_2d(dst, wm, bar(kFullP + sp), xb, y);
-              dev::tma_load_2d(dst + 4096, wm, bar(kFullP + sp), xq, y);
-              dev::tma_load_2d(dst + 8192, wm, bar(kFullP + sp), xq + 4, y);
+              dev::tma_load_2d(dst + 2048, wm, bar(kFullP + sp), xq, y);
+              dev::tma_load_2d(dst + 4096, wm, bar(kFullP + sp), xq + 4, y);
             } else if (QT == B2G_Q8_0) {
               dev::tma_load_2d(dst, wm, bar(kFullP + sp), ((68 * it) & ~15) >> 2, y);
             } else {
@@ -370,18 +388,17 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
       }
     }
   } else if (warp == 1) {
-    // ============================== MMA issuer ==============================
-    if (lane == 0) {
-      constexpr uint32_t idesc = dev::make_idesc_bf16(kBM, kBN, 0, MODE == kDgrad ? 1 : 0);
-      int sa = 0, pa = 0, sb = 0, pb = 0, pl = 0, ab = 0, pacc = 0;
+    // ============================== MMA issuer (first CTA of the pair) ==============================
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = dev::make_idesc_bf16(kPairRows, kBN, 0, MODE == kDgrad ? 1 : 0);
+      int sa = 0, pa = 0, sb = 0, pb = 0, pl = 0, pacc = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-        const Tile t = get_tile<MT>(p, item);
-        const int nmt = (MT == 2 && t.rows > kBM) ? 2 : 1;
-        ok = dev::mbar_wait(bar(kAccEmpty + ab), pacc ^ 1, abort_flag, p.status, 201);
+      for (int item = pair; item < total_items && ok; item += num_pairs) {
+        const Tile t = get_tile(p, item);
+        const int nmt = t.rows > kPairRows ? 2 : 1;
+        ok = dev::mbar_wait(bar(kAccEmpty), pacc ^ 1, abort_flag, p.status, 201);
         if (!ok) break;
         dev::tc_fence_after();
-        const uint32_t acc = tmem_base + (C::kAccBufs == 2 ? ab * kBN : 0);
         for (int it = 0; it < p.num_iters; ++it) {
           ok = dev::mbar_wait(bar(kFullA + sa), pa, abort_flag, p.status, 202) &&
                dev::mbar_wait(bar(kFullB + sb), pb, abort_flag, p.status, 203);
@@ -394,11 +411,11 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
                                                 : dev::make_smem_desc(b_base + k16 * 2048, 8192, 1024, 2);
             for (int m = 0; m < nmt; ++m) {
               const uint64_t adesc = dev::make_smem_desc(a_base + m * kATile + k16 * 32, 16, 1024, 2);
-              dev::umma_bf16(acc + m * kBN, adesc, bdesc, idesc, (it | k16) != 0 ? 1u : 0u);
+              if (p.debug != 3) dev::umma_bf16_pair(tmem_base + m * kBN, adesc, bdesc, idesc, (it | k16) != 0 ? 1u : 0u);
             }
           }
-          dev::umma_commit(bar(kEmptyA + sa));
-          dev::umma_commit(bar(kEmptyB + sb));
+          dev::umma_commit_pair(bar(kEmptyA + sa));
+          dev::umma_commit_pair(bar(kEmptyB + sb));
           if (++sa == C::kAStages) { sa = 0; pa ^= 1; }
           if (++sb == kBStages) { sb = 0; pb ^= 1; }
         }
@@ -410,35 +427,35 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
           const uint64_t bdesc = MODE == kFwd ? dev::make_smem_desc(sLB, 16, 256, 6) : dev::make_smem_desc(sLB, 2048, 1024, 2);
           for (int m = 0; m < nmt; ++m) {
             const uint64_t adesc = dev::make_smem_desc(sLA + m * kLoraATile, 16, 256, 6);
-            dev::umma_bf16(acc + m * kBN, adesc, bdesc, idesc, 1u);
+            dev::umma_bf16_pair(tmem_base + m * kBN, adesc, bdesc, idesc, 1u);
           }
-          dev::umma_commit(bar(kEmptyL));
+          dev::umma_commit_pair(bar(kEmptyL));
           pl ^= 1;
         }
-        dev::umma_commit(bar(kAccFull + ab));
-        if (++ab == C::kAccBufs) { ab = 0; pacc ^= 1; }
+        dev::umma_commit_pair(bar(kAccFull));
+        pacc ^= 1;
       }
     }
   } else if (warp < 6) {
     // ============================== epilogue ==============================
     const int q = warp & 3;  // TMEM lane quarter this warp may read
-    int ab = 0, pacc = 0;
+    int pacc = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-      const Tile t = get_tile<MT>(p, item);
-      const int nmt = (MT == 2 && t.rows > kBM) ? 2 : 1;
+    for (int item = pair; item < total_items && ok; item += num_pairs) {
+      const Tile t = get_tile(p, item);
+      const int nmt = t.rows > kPairRows ? 2 : 1;
       int seg = 0, col0;
       if (MODE == kFwd) { seg = t.ct / p.ct_per_seg; col0 = (t.ct - seg * p.ct_per_seg) * kBN; }
       else col0 = t.ct * kBN;
       const int ncols = MODE == kFwd ? p.n : p.k;
       __nv_bfloat16* outp = seg ? p.out1 : p.out0;
-      ok = dev::mbar_wait(bar(kAccFull + ab), pacc, abort_flag, p.status, 301);
+      ok = dev::mbar_wait(bar(kAccFull), pacc, abort_flag, p.status, 301);
       if (!ok) break;
       dev::tc_fence_after();
-      const uint32_t acc = tmem_base + (C::kAccBufs == 2 ? ab * kBN : 0) + (static_cast<uint32_t>(q * 32) << 16);
+      const uint32_t acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
       const bool vec_ok = (p.ldc & 7) == 0;
       for (int m = 0; m < nmt; ++m) {
-        const int row_local = m * kBM + q * 32 + lane;
+        const int row_local = m * kPairRows + static_cast<int>(rank) * kBM + q * 32 + lane;
         const bool row_ok = row_local < t.rows;
         __nv_bfloat16* orow = outp + static_cast<int64_t>(t.row0 + row_local) * p.ldc;
 #pragma unroll 1
@@ -447,7 +464,7 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
           dev::tmem_ld_32x32(acc + m * kBN + c * 32, r);
           dev::tmem_ld_wait();
           const int cbase = col0 + c * 32;
-          if (row_ok && cbase < ncols) {
+          if (row_ok && cbase < ncols && p.debug != 4) {
             if (MODE == kFwd && p.bias) {
 #pragma unroll
               for (int i = 0; i < 32; ++i)
@@ -473,22 +490,23 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
       }
       dev::tc_fence_before();
       __syncwarp();
-      if (lane == 0) dev::mbar_arrive(bar(kAccEmpty + ab));
-      if (++ab == C::kAccBufs) { ab = 0; pacc ^= 1; }
+      if (lane == 0) dev::mbar_arrive_cluster(lead_acc_empty);
+      pacc ^= 1;
     }
   } else {
     // ============================== unpack ==============================
-    const int tid = threadIdx.x - 6 * 32;  // 0..511
+    const int tid = threadIdx.x - 6 * 32;  // 0..255
     const uint2* grid_s = reinterpret_cast<const uint2*>(smem + C::kOffGrid);
     int sp = 0, pp = 0, sb = 0, pb = 0;
     bool ok = true;
-    const int half = tid >> 8;                                   // warp-uniform
-    const int drow = MODE == kFwd ? (tid & 255) : (tid & 63);    // W row inside the stage
-    const int quarter = MODE == kFwd ? 0 : ((tid >> 6) & 3);     // dgrad: which 64 of the tile's 256 columns
-    // this thread's 64 bytes: row `drow` of sub-tile `quarter`, vectors 4*half .. 4*half+3 (128-byte swizzle)
-    const uint32_t doff = static_cast<uint32_t>(quarter) * 8192u + static_cast<uint32_t>(drow) * 128u;
+    const int half = tid >> 7;                                   // warp-uniform
+    const int drow = MODE == kFwd ? (tid & 127) : (tid & 63);    // W row inside this CTA's stage
+    const int sub = MODE == kFwd ? 0 : ((tid >> 6) & 1);         // dgrad: which 64 of this CTA's 128 columns
+    const int quarter = 2 * static_cast<int>(rank) + sub;        // ... = which 64 of the tile's 256 columns
+    // this thread's 64 bytes: row `drow` of sub-tile `sub`, vectors 4*half .. 4*half+3 (128-byte swizzle)
+    const uint32_t doff = static_cast<uint32_t>(sub) * 8192u + static_cast<uint32_t>(drow) * 128u;
     const uint32_t sw = static_cast<uint32_t>(drow & 7);
-    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+    for (int item = pair; item < total_items && ok; item += num_pairs) {
       const int ct = item % p.num_ct;
       for (int it = 0; it < p.num_iters; ++it) {
         ok = dev::mbar_wait(bar(kFullP + sp), pp, abort_flag, p.status, 401);
@@ -508,22 +526,24 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
         uint8_t* dst = smem + C::kOffB + sb * kBStage + doff;
 #pragma unroll
         for (int c = 0; c < 4; ++c)
-          if (p.debug == 0 || (p.debug == 2 && out[4 * c] == 0x12345678u))
+          if (p.debug != 1)
           *reinterpret_cast<uint4*>(dst + ((static_cast<uint32_t>(4 * half + c) ^ sw) << 4)) =
               make_uint4(out[4 * c], out[4 * c + 1], out[4 * c + 2], out[4 * c + 3]);
         dev::fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) dev::mbar_arrive(bar(kFullB + sb));
+        if (lane == 0) dev::mbar_arrive_cluster(lead_full_b + 8u * sb);
         if (++sb == kBStages) { sb = 0; pb ^= 1; }
       }
     }
   }
 
+  // Neither CTA may leave (or free TMEM) while its partner can still signal it or read its shared memory.
   dev::tc_fence_before();
   __syncthreads();
+  dev::cluster_sync_all();
   if (warp == 1) {
     dev::tc_fence_after();
-    dev::tmem_dealloc(tmem_base, kTmemCols);
+    dev::tmem_dealloc_pair(tmem_base, kTmemCols);
   }
 }
 
@@ -545,9 +565,9 @@ struct Launch {
   cudaStream_t stream;
 };
 
-template <int QT, int MODE, int MT>
+template <int QT, int MODE>
 int launch_impl(const Launch& L) {
-  using C = Cfg<QT, MODE, MT>;
+  using C = Cfg<QT, MODE>;
   using P = Packed<QT, MODE>;
   Params p{};
   p.m_total = (int)L.m_total; p.n = (int)L.n; p.k = (int)L.k;
@@ -566,7 +586,7 @@ int launch_impl(const Launch& L) {
     p.num_iters = p.nseg * p.iters_per_seg;
     p.ldc = p.k;
   }
-  p.dense_m_tiles = (int)((L.m_total + kBM * MT - 1) / (kBM * MT));
+  p.dense_m_tiles = (int)((L.m_total + kTileRows - 1) / kTileRows);
   p.has_lora = L.la != nullptr;
   p.lora_rows = (int)L.lora_rows;
   p.tiles = reinterpret_cast<const int4*>(L.tiles);
@@ -602,35 +622,43 @@ int launch_impl(const Launch& L) {
                            CU_TENSOR_MAP_SWIZZLE_32B))) return rc;
     if (MODE == kFwd) {
       if ((rc = make_tmap_2d(&tm_lb, L.lb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 16, (uint64_t)L.num_experts * L.lora_rows, 32, 16,
-                             kBN, CU_TENSOR_MAP_SWIZZLE_32B))) return rc;
+                             kBNh, CU_TENSOR_MAP_SWIZZLE_32B))) return rc;
     } else {
       if ((rc = make_tmap_2d(&tm_lb, L.lb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, L.k, (uint64_t)L.num_experts * 16, (uint64_t)L.k * 2,
                              64, 16, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
     }
   }
 
-  auto kern = qgemm_kernel<QT, MODE, MT>;
+  auto kern = qgemm_kernel<QT, MODE>;
   B2G_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
-  int grid = sm_count();
+  int pairs = sm_count() / 2;
   if (!L.tiles) {
     const int64_t items = (int64_t)p.dense_m_tiles * p.num_ct;
-    if (items < grid) grid = (int)items;
+    if (items < pairs) pairs = (int)items;
   }
-  if (grid < 1) return 0;
-  kern<<<grid, kThreads, C::kSmemBytes, L.stream>>>(p, tm_a0, tm_a1, tm_w0, tm_w1, tm_la, tm_lb);
-  B2G_CUDA_OK(cudaGetLastError());
+  if (pairs < 1) return 0;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = L.stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  B2G_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p, tm_a0, tm_a1, tm_w0, tm_w1, tm_la, tm_lb));
   return 0;
 }
-
-// Rows per M-block: two 128-row MMAs share every unpacked weight tile.
-constexpr int kMT = 2;
 
 template <int MODE>
 int launch_mode(const Launch& L) {
   switch (L.qtype) {
-    case B2G_Q4_K: return launch_impl<B2G_Q4_K, MODE, kMT>(L);
-    case B2G_Q8_0: return launch_impl<B2G_Q8_0, MODE, kMT>(L);
-    case B2G_IQ2_XXS: return launch_impl<B2G_IQ2_XXS, MODE, kMT>(L);
+    case B2G_Q4_K: return launch_impl<B2G_Q4_K, MODE>(L);
+    case B2G_Q8_0: return launch_impl<B2G_Q8_0, MODE>(L);
+    case B2G_IQ2_XXS: return launch_impl<B2G_IQ2_XXS, MODE>(L);
     default: return fail(B2G_E_ARG, "unsupported GGUF type id %d (supported: 8 Q8_0, 12 Q4_K, 16 IQ2_XXS)", L.qtype);
   }
 }
@@ -719,7 +747,7 @@ extern "C" int b2g_qlinear_dgrad(int qtype, const void* dy, const void* payload,
 }
 
 extern "C" int64_t b2g_grouped_tiles_bytes(int64_t R, int G) {
-  const int64_t rows_per_tile = qg::kBM * qg::kMT;
+  const int64_t rows_per_tile = qg::kTileRows;
   return (1 + R / rows_per_tile + G + 1) * (int64_t)sizeof(int4);
 }
 
@@ -728,7 +756,7 @@ extern "C" int b2g_grouped_schedule(const int64_t* expert_indices, const int32_t
   B2G_REQUIRE(G >= 0 && R >= 0 && tiles, "bad arguments");
   B2G_REQUIRE(aligned16(tiles), "tile table must be 16-byte aligned");
   B2G_REQUIRE(G == 0 || (expert_indices && offsets), "null pointer");
-  qg::schedule_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(expert_indices, offsets, G, qg::kBM * qg::kMT,
+  qg::schedule_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(expert_indices, offsets, G, qg::kTileRows,
                                                                        reinterpret_cast<int4*>(tiles));
   B2G_CUDA_OK(cudaGetLastError());
   return 0;

@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(256) router_topk_kernel(const void* __restrict
 // Routing plan.  Three passes over the flat id array, split into chunks of kChunk ids handled by one
 // warp each so that ranks inside a chunk can be assigned in order (stable):
 //   1. per-chunk histogram                       -> ws[chunk][E]
-//   2. per-expert exclusive scan over chunks     -> ws becomes the chunk's first output slot; sizes/offsets
+//   2. per-expert exclusive scan over chunks     -> ws = rows of that expert in earlier chunks; sizes, then offsets
 //   3. per-chunk ordered scatter                 -> sorted_expert, perm, inv_perm
 // ---------------------------------------------------------------------------------------------
 constexpr int kChunk = 512;
@@ -93,38 +93,46 @@ __global__ void __launch_bounds__(256) plan_hist_kernel(const void* __restrict__
   }
 }
 
-__global__ void __launch_bounds__(1024) plan_scan_kernel(int32_t* __restrict__ ws, int64_t nchunks, int E,
-                                                         int32_t* __restrict__ sizes, int32_t* __restrict__ offsets) {
+// One warp per expert: exclusive scan of that expert's per-chunk counts (32 chunks per step, shuffle scan).
+__global__ void __launch_bounds__(256) plan_scan_kernel(int32_t* __restrict__ ws, int64_t nchunks, int E, int32_t* __restrict__ sizes) {
+  const int lane = threadIdx.x & 31;
+  const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (e >= E) return;
+  int32_t run = 0;
+  for (int64_t c0 = 0; c0 < nchunks; c0 += 32) {
+    const int64_t c = c0 + lane;
+    const int32_t v = c < nchunks ? ws[c * E + e] : 0;
+    int32_t incl = v;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int32_t o = __shfl_up_sync(0xFFFFFFFFu, incl, off);
+      if (lane >= off) incl += o;
+    }
+    if (c < nchunks) ws[c * E + e] = run + incl - v;
+    run += __shfl_sync(0xFFFFFFFFu, incl, 31);
+  }
+  if (lane == 0) sizes[e] = run;
+}
+
+// Cumulative ends over the experts (E <= 1024), one block.
+__global__ void __launch_bounds__(1024) plan_offsets_kernel(const int32_t* __restrict__ sizes, int E, int32_t* __restrict__ offsets) {
   __shared__ int32_t tot[1024];
   const int e = threadIdx.x;
-  int32_t run = 0;
-  if (e < E) {
-    for (int64_t c = 0; c < nchunks; ++c) {
-      const int32_t v = ws[c * E + e];
-      ws[c * E + e] = run;
-      run += v;
-    }
-  }
-  tot[e] = e < E ? run : 0;
+  tot[e] = e < E ? sizes[e] : 0;
   __syncthreads();
-  // inclusive scan over experts (E <= 1024)
   for (int off = 1; off < 1024; off <<= 1) {
     const int32_t add = e >= off ? tot[e - off] : 0;
     __syncthreads();
     tot[e] += add;
     __syncthreads();
   }
-  if (e < E) {
-    sizes[e] = run;
-    offsets[e] = tot[e];
-    const int32_t base = tot[e] - run;
-    for (int64_t c = 0; c < nchunks; ++c) ws[c * E + e] += base;
-  }
+  if (e < E) offsets[e] = tot[e];
 }
 
 template <bool kIdx64>
 __global__ void __launch_bounds__(256) plan_scatter_kernel(const void* __restrict__ ids, int64_t R, int E,
-                                                           const int32_t* __restrict__ ws, int64_t* __restrict__ sorted_expert,
+                                                           const int32_t* __restrict__ ws, const int32_t* __restrict__ sizes,
+                                                           const int32_t* __restrict__ offsets, int64_t* __restrict__ sorted_expert,
                                                            int64_t* __restrict__ perm, int64_t* __restrict__ inv_perm) {
   extern __shared__ int32_t sh[];
   const int warp_in_block = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -132,7 +140,7 @@ __global__ void __launch_bounds__(256) plan_scatter_kernel(const void* __restric
   const int64_t chunk = blockIdx.x * (int64_t)(blockDim.x >> 5) + warp_in_block;
   const int64_t begin = chunk * kChunk;
   if (begin >= R) return;
-  for (int e = lane; e < E; e += 32) next[e] = ws[chunk * E + e];
+  for (int e = lane; e < E; e += 32) next[e] = ws[chunk * E + e] + offsets[e] - sizes[e];  // chunk prefix + first slot of the expert
   __syncwarp();
   const int64_t end = begin + kChunk < R ? begin + kChunk : R;
   for (int64_t base = begin; base < end; base += 32) {
@@ -395,10 +403,11 @@ extern "C" int b2g_route_plan(const void* topk_idx, int idx_dtype, int64_t T, in
     if (idx_dtype) plan_hist_kernel<true><<<blocks, warps * 32, smem, s>>>(topk_idx, R, E, ws, bad);
     else plan_hist_kernel<false><<<blocks, warps * 32, smem, s>>>(topk_idx, R, E, ws, bad);
   }
-  plan_scan_kernel<<<1, 1024, 0, s>>>(ws, nchunks, E, group_sizes, offsets);
+  plan_scan_kernel<<<(E + 7) / 8, 256, 0, s>>>(ws, nchunks, E, group_sizes);
+  plan_offsets_kernel<<<1, 1024, 0, s>>>(group_sizes, E, offsets);
   if (R > 0) {
-    if (idx_dtype) plan_scatter_kernel<true><<<blocks, warps * 32, smem, s>>>(topk_idx, R, E, ws, sorted_expert, perm, inv_perm);
-    else plan_scatter_kernel<false><<<blocks, warps * 32, smem, s>>>(topk_idx, R, E, ws, sorted_expert, perm, inv_perm);
+    if (idx_dtype) plan_scatter_kernel<true><<<blocks, warps * 32, smem, s>>>(topk_idx, R, E, ws, group_sizes, offsets, sorted_expert, perm, inv_perm);
+    else plan_scatter_kernel<false><<<blocks, warps * 32, smem, s>>>(topk_idx, R, E, ws, group_sizes, offsets, sorted_expert, perm, inv_perm);
   }
   B2G_CUDA_OK(cudaGetLastError());
   return 0;
