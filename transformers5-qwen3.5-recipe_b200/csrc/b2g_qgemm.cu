@@ -20,8 +20,9 @@
 // so each packed block is unpacked once per 512 rows, and each CTA reads only half of B from its own
 // shared memory.  The LoRA up-projection is one extra K=16 MMA per row block on 32-byte-swizzled tiles.
 //
-// Warp roles (448 threads per CTA): 0 = TMA producer, 1 = MMA issuer (first CTA of the pair only) + TMEM
-// owner, 2-5 = epilogue (TMEM -> registers -> global), 6-13 = unpack.  Barriers that gate the MMA
+// Warp roles (480 threads per CTA): 0 = activation / LoRA tile producer (TMA), 1 = MMA issuer (first CTA of the
+// pair only) + TMEM owner, 2-5 = epilogue (TMEM -> registers -> global), 6-13 = unpack in four groups that take
+// reduction steps round-robin (four steps in flight), 14 = packed-weight producer (TMA).  Barriers that gate the MMA
 // (A / B / LoRA tiles ready, accumulator drained) live in the first CTA and collect arrivals from both;
 // barriers that release buffers are signalled in both CTAs by tcgen05.commit.  No TMA multicast is used:
 // every CTA loads its own tiles.  All mbarrier waits are bounded.
@@ -43,9 +44,12 @@ constexpr int kMT = 2;            // row blocks per tile
 constexpr int kTileRows = kPairRows * kMT;  // 512
 constexpr int kATile = kBM * kBK * 2;       // 16384
 constexpr int kBStage = kBNh * kBK * 2;     // 16384
-constexpr int kBStages = 3;
-constexpr int kUnpackWarps = 8;             // 256 threads: (128 W rows x 2 halves) or (64 rows x 2 quarters x 2 halves)
-constexpr int kThreads = 32 * (6 + kUnpackWarps);
+constexpr int kBStages = 4;
+constexpr int kUnpackWarps = 8;
+constexpr int kUnpackGroups = 4;            // groups take reduction steps round-robin, so four steps are unpacked concurrently
+constexpr int kGroupWarps = kUnpackWarps / kUnpackGroups;
+constexpr int kGroupThreads = 32 * kGroupWarps;   // 64 threads x 4 items = 256 (row, half) items of one step
+constexpr int kThreads = 32 * (7 + kUnpackWarps);  // + A producer, MMA, 4 epilogue, packed-weight producer
 constexpr int kLoraATile = kBM * 32;        // [128 x 16] bf16
 constexpr int kLoraBTile = kBNh * 32;       // 4096 either way
 constexpr int kTmemCols = 512;
@@ -62,8 +66,9 @@ template <> struct Packed<B2G_Q4_K, kDgrad> { static constexpr int kBoxWords = 3
 // Q8_0 forward: two 34-byte blocks start at byte 68*step; an 80-byte window from the 16-byte boundary below
 // covers them (the start is at most 12 bytes into the window).
 template <> struct Packed<B2G_Q8_0, kFwd> { static constexpr int kBoxWords = 20, kBoxRows = 128, kBytes = 128 * 80; };
-// Q8_0 dgrad: eight blocks (272 B = 17 x 16) per row.
-template <> struct Packed<B2G_Q8_0, kDgrad> { static constexpr int kBoxWords = 68, kBoxRows = 64, kBytes = 64 * 272; };
+// Q8_0 dgrad: this CTA's 128 columns are four blocks (136 B) starting at byte 272*tile + 136*rank of the row; a
+// 144-byte window from the 16-byte boundary below covers them (the start is 0 or 8 bytes into the window).
+template <> struct Packed<B2G_Q8_0, kDgrad> { static constexpr int kBoxWords = 36, kBoxRows = 64, kBytes = 64 * 144; };
 // IQ2_XXS: 66-byte super-blocks are not 16-byte aligned; an 80-byte window from the boundary below covers one
 // (the start is at most 14 bytes into the window).
 template <> struct Packed<B2G_IQ2_XXS, kFwd> { static constexpr int kBoxWords = 20, kBoxRows = 128, kBytes = 128 * 80; };
@@ -72,9 +77,10 @@ template <> struct Packed<B2G_IQ2_XXS, kDgrad> { static constexpr int kBoxWords 
 template <int QT, int MODE>
 struct Cfg {
   using P = Packed<QT, MODE>;
-  static constexpr int kAStages = 4;
+  static constexpr int kAStages = 3;
   static constexpr int kAStage = kMT * kATile;
-  static constexpr int kPStages = P::kBytes > 12288 ? 2 : 3;
+  static constexpr int kPStages = kUnpackGroups;   // slot s always belongs to unpack group s, so each group sees every phase of its barriers
+  static_assert(kBStages == kUnpackGroups, "B slots are owned by unpack groups as well");
   static constexpr int kPStage = (P::kBytes + 1023) / 1024 * 1024;
   // shared-memory map (offsets from a 1024-byte aligned base)
   static constexpr int kOffA = 0;
@@ -251,7 +257,10 @@ __device__ __forceinline__ void unpack_half(const uint8_t* pk, int row, int pair
   } else if constexpr (QT == B2G_Q8_0) {
     uint32_t w[17];
     if constexpr (MODE == kFwd) load_words_shifted<17>(pk + row * 80, (68 * it) & 15, w);
-    else load_words_shifted<17>(pk + row * 272 + ((68 * pair) & ~15), (68 * pair) & 15, w);  // byte 68*pair of the 272-byte row
+    else {
+      const int byte0 = ((136 * (pair >> 1)) & 15) + 68 * (pair & 1);  // two blocks of column quarter `pair` inside the 144-byte window
+      load_words_shifted<17>(pk + row * 144 + (byte0 & ~15), byte0 & 15, w);
+    }
     q8_half(w, half, out);
   } else {
     // 66-byte super-block inside an 80-byte window; `off` (even) is where it starts.
@@ -293,8 +302,8 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < C::kAStages; ++i) { dev::mbar_init(bar(kFullA + i), 1); dev::mbar_init(bar(kEmptyA + i), 1); }
-    for (int i = 0; i < kBStages; ++i) { dev::mbar_init(bar(kFullB + i), 2 * kUnpackWarps); dev::mbar_init(bar(kEmptyB + i), 1); }
-    for (int i = 0; i < C::kPStages; ++i) { dev::mbar_init(bar(kFullP + i), 1); dev::mbar_init(bar(kEmptyP + i), kUnpackWarps); }
+    for (int i = 0; i < kBStages; ++i) { dev::mbar_init(bar(kFullB + i), 2 * kGroupWarps); dev::mbar_init(bar(kEmptyB + i), 1); }
+    for (int i = 0; i < C::kPStages; ++i) { dev::mbar_init(bar(kFullP + i), 1); dev::mbar_init(bar(kEmptyP + i), kGroupWarps); }
     dev::mbar_init(bar(kFullL), 1);
     dev::mbar_init(bar(kEmptyL), 1);
     dev::mbar_init(bar(kAccFull), 1);
@@ -327,7 +336,7 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
   if (warp == 0) {
     // ============================== TMA producer ==============================
     if (lane == 0) {
-      int sa = 0, pa = 0, sp = 0, pp = 0, pl = 0;
+      int sa = 0, pa = 0, pl = 0;
       bool ok = true;
       for (int item = pair; item < total_items && ok; item += num_pairs) {
         const Tile t = get_tile(p, item);
@@ -360,30 +369,6 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
             dev::tma_load_2d_pair(sA + sa * C::kAStage + m * kATile, am, lead_full_a + 8u * sa, red0, my_row0 + m * kPairRows);
           if (++sa == C::kAStages) { sa = 0; pa ^= 1; }
 
-          ok = dev::mbar_wait(bar(kEmptyP + sp), pp ^ 1, abort_flag, p.status, 103);
-          if (!ok) break;
-          dev::mbar_arrive_expect_tx(bar(kFullP + sp), P::kBytes);
-          const CUtensorMap* wm = seg ? &tm_w1 : &tm_w0;
-          const uint32_t dst = sP + sp * C::kPStage;
-          if (MODE == kFwd) {
-            const int y = t.expert * p.n + col0 + static_cast<int>(rank) * kBNh;
-            if (QT == B2G_Q4_K) {
-              const int xb = 36 * (it >> 2), xq = xb + 4 + 8 * (it & 3);
-              dev::tma_load_2d(dst, wm, bar(kFullP + sp), xb, y);
-              dev::tma_load_2d(dst + 2048, wm, bar(kFullP + sp), xq, y);
-              dev::tma_load_2d(dst + 4096, wm, bar(kFullP + sp), xq + 4, y);
-            } else if (QT == B2G_Q8_0) {
-              dev::tma_load_2d(dst, wm, bar(kFullP + sp), ((68 * it) & ~15) >> 2, y);
-            } else {
-              dev::tma_load_2d(dst, wm, bar(kFullP + sp), ((66 * (it >> 2)) & ~15) >> 2, y);
-            }
-          } else {
-            const int y = t.expert * p.n + red0;
-            if (QT == B2G_Q4_K) dev::tma_load_2d(dst, wm, bar(kFullP + sp), 36 * t.ct, y);
-            else if (QT == B2G_Q8_0) dev::tma_load_2d(dst, wm, bar(kFullP + sp), 68 * t.ct, y);
-            else dev::tma_load_2d(dst, wm, bar(kFullP + sp), ((66 * t.ct) & ~15) >> 2, y);
-          }
-          if (++sp == C::kPStages) { sp = 0; pp ^= 1; }
         }
       }
     }
@@ -493,46 +478,87 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
       if (lane == 0) dev::mbar_arrive_cluster(lead_acc_empty);
       pacc ^= 1;
     }
+  } else if (warp == 6 + kUnpackWarps) {
+    // ============================== packed-weight producer ==============================
+    if (lane == 0) {
+      int sp = 0, pp = 0;
+      bool ok = true;
+      for (int item = pair; item < total_items && ok; item += num_pairs) {
+        const Tile t = get_tile(p, item);
+        int fseg = 0, col0 = 0;
+        if (MODE == kFwd) { fseg = t.ct / p.ct_per_seg; col0 = (t.ct - fseg * p.ct_per_seg) * kBN; }
+        else col0 = t.ct * kBN;
+        for (int it = 0; it < p.num_iters; ++it) {
+          int seg = fseg, red0 = it * kBK;
+          if (MODE == kDgrad) { seg = it / p.iters_per_seg; red0 = (it - seg * p.iters_per_seg) * kBK; }
+          ok = dev::mbar_wait(bar(kEmptyP + sp), pp ^ 1, abort_flag, p.status, 104);
+          if (!ok) break;
+          dev::mbar_arrive_expect_tx(bar(kFullP + sp), P::kBytes);
+          const CUtensorMap* wm = seg ? &tm_w1 : &tm_w0;
+          const uint32_t dst = sP + sp * C::kPStage;
+          if (MODE == kFwd) {
+            const int y = t.expert * p.n + col0 + static_cast<int>(rank) * kBNh;
+            if (QT == B2G_Q4_K) {
+              const int xb = 36 * (it >> 2), xq = xb + 4 + 8 * (it & 3);
+              dev::tma_load_2d(dst, wm, bar(kFullP + sp), xb, y);
+              dev::tma_load_2d(dst + 2048, wm, bar(kFullP + sp), xq, y);
+              dev::tma_load_2d(dst + 4096, wm, bar(kFullP + sp), xq + 4, y);
+            } else if (QT == B2G_Q8_0) {
+              dev::tma_load_2d(dst, wm, bar(kFullP + sp), ((68 * it) & ~15) >> 2, y);
+            } else {
+              dev::tma_load_2d(dst, wm, bar(kFullP + sp), ((66 * (it >> 2)) & ~15) >> 2, y);
+            }
+          } else {
+            const int y = t.expert * p.n + red0;
+            if (QT == B2G_Q4_K) dev::tma_load_2d(dst, wm, bar(kFullP + sp), 36 * t.ct, y);
+            else if (QT == B2G_Q8_0) dev::tma_load_2d(dst, wm, bar(kFullP + sp), ((272 * t.ct + 136 * static_cast<int>(rank)) & ~15) >> 2, y);
+            else dev::tma_load_2d(dst, wm, bar(kFullP + sp), ((66 * t.ct) & ~15) >> 2, y);
+          }
+          if (++sp == C::kPStages) { sp = 0; pp ^= 1; }
+        }
+      }
+    }
   } else {
     // ============================== unpack ==============================
-    const int tid = threadIdx.x - 6 * 32;  // 0..255
+    const int tid = threadIdx.x - 6 * 32;      // 0..255
+    const int group = tid / kGroupThreads;     // this group unpacks steps group, group + 4, group + 8, ...
+    const int tg = tid % kGroupThreads;        // 0..63
     const uint2* grid_s = reinterpret_cast<const uint2*>(smem + C::kOffGrid);
-    int sp = 0, pp = 0, sb = 0, pb = 0;
     bool ok = true;
-    const int half = tid >> 7;                                   // warp-uniform
-    const int drow = MODE == kFwd ? (tid & 127) : (tid & 63);    // W row inside this CTA's stage
-    const int sub = MODE == kFwd ? 0 : ((tid >> 6) & 1);         // dgrad: which 64 of this CTA's 128 columns
-    const int quarter = 2 * static_cast<int>(rank) + sub;        // ... = which 64 of the tile's 256 columns
-    // this thread's 64 bytes: row `drow` of sub-tile `sub`, vectors 4*half .. 4*half+3 (128-byte swizzle)
-    const uint32_t doff = static_cast<uint32_t>(sub) * 8192u + static_cast<uint32_t>(drow) * 128u;
-    const uint32_t sw = static_cast<uint32_t>(drow & 7);
+    int n = 0;                                 // running count of reduction steps of this CTA
     for (int item = pair; item < total_items && ok; item += num_pairs) {
       const int ct = item % p.num_ct;
-      for (int it = 0; it < p.num_iters; ++it) {
-        ok = dev::mbar_wait(bar(kFullP + sp), pp, abort_flag, p.status, 401);
+      for (int it = 0; it < p.num_iters; ++it, ++n) {
+        if ((n % kUnpackGroups) != group) continue;
+        const int sp = n % C::kPStages, pp = (n / C::kPStages) & 1;
+        const int sb = n % kBStages, pb = (n / kBStages) & 1;
+        ok = dev::mbar_wait(bar(kFullP + sp), pp, abort_flag, p.status, 401) &&
+             dev::mbar_wait(bar(kEmptyB + sb), pb ^ 1, abort_flag, p.status, 402);
         if (!ok) break;
-        uint32_t out[16];
-        if (p.debug != 1)
-          unpack_half<QT, MODE>(smem + C::kOffP + sp * C::kPStage, drow, MODE == kFwd ? (it & 3) : quarter, half, it, ct, grid_s, out);
-        else {
+        const uint8_t* pk = smem + C::kOffP + sp * C::kPStage;
+        uint8_t* bstage = smem + C::kOffB + sb * kBStage;
 #pragma unroll
-          for (int i = 0; i < 16; ++i) out[i] = 0;
+        for (int j = 0; j < 4; ++j) {
+          // four (row, half) items per thread: forward 128 rows x 2 halves, dgrad 64 rows x 2 column quarters x 2 halves
+          const int half = j >> 1;
+          const int drow = MODE == kFwd ? tg + 64 * (j & 1) : tg;
+          const int sub = MODE == kFwd ? 0 : (j & 1);                 // dgrad: which 64 of this CTA's 128 columns
+          const int quarter = 2 * static_cast<int>(rank) + sub;       // ... = which 64 of the tile's 256 columns
+          uint32_t out[16];
+          unpack_half<QT, MODE>(pk, drow, MODE == kFwd ? (it & 3) : quarter, half, it, ct, grid_s, out);
+          uint8_t* dst = bstage + static_cast<uint32_t>(sub) * 8192u + static_cast<uint32_t>(drow) * 128u;
+          const uint32_t sw = static_cast<uint32_t>(drow & 7);
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            *reinterpret_cast<uint4*>(dst + ((static_cast<uint32_t>(4 * half + c) ^ sw) << 4)) =
+                make_uint4(out[4 * c], out[4 * c + 1], out[4 * c + 2], out[4 * c + 3]);
         }
-        __syncwarp();
-        if (lane == 0) dev::mbar_arrive(bar(kEmptyP + sp));
-        if (++sp == C::kPStages) { sp = 0; pp ^= 1; }
-        ok = dev::mbar_wait(bar(kEmptyB + sb), pb ^ 1, abort_flag, p.status, 402);
-        if (!ok) break;
-        uint8_t* dst = smem + C::kOffB + sb * kBStage + doff;
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-          if (p.debug != 1)
-          *reinterpret_cast<uint4*>(dst + ((static_cast<uint32_t>(4 * half + c) ^ sw) << 4)) =
-              make_uint4(out[4 * c], out[4 * c + 1], out[4 * c + 2], out[4 * c + 3]);
         dev::fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) dev::mbar_arrive_cluster(lead_full_b + 8u * sb);
-        if (++sb == kBStages) { sb = 0; pb ^= 1; }
+        if (lane == 0) {
+          dev::mbar_arrive(bar(kEmptyP + sp));
+          dev::mbar_arrive_cluster(lead_full_b + 8u * sb);
+        }
       }
     }
   }
