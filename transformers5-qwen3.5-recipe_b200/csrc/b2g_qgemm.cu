@@ -20,9 +20,9 @@
 // so each packed block is unpacked once per 512 rows, and each CTA reads only half of B from its own
 // shared memory.  The LoRA up-projection is one extra K=16 MMA per row block on 32-byte-swizzled tiles.
 //
-// Warp roles (480 threads per CTA): 0 = activation / LoRA tile producer (TMA), 1 = MMA issuer (first CTA of the
-// pair only) + TMEM owner, 2-5 = epilogue (TMEM -> registers -> global), 6-13 = unpack in four groups that take
-// reduction steps round-robin (four steps in flight), 14 = packed-weight producer (TMA).  Barriers that gate the MMA
+// Warp roles (736 threads per CTA): 0 = activation / LoRA tile producer (TMA), 1 = MMA issuer (first CTA of the
+// pair only) + TMEM owner, 2-5 = epilogue (TMEM -> registers -> global), 6-21 = unpack in four groups that take
+// reduction steps round-robin (four steps in flight), 22 = packed-weight producer (TMA).  Barriers that gate the MMA
 // (A / B / LoRA tiles ready, accumulator drained) live in the first CTA and collect arrivals from both;
 // barriers that release buffers are signalled in both CTAs by tcgen05.commit.  No TMA multicast is used:
 // every CTA loads its own tiles.  All mbarrier waits are bounded.
@@ -45,14 +45,17 @@ constexpr int kTileRows = kPairRows * kMT;  // 512
 constexpr int kATile = kBM * kBK * 2;       // 16384
 constexpr int kBStage = kBNh * kBK * 2;     // 16384
 constexpr int kBStages = 4;
-constexpr int kUnpackWarps = 8;
+constexpr int kUnpackWarps = 16;
 constexpr int kUnpackGroups = 4;            // groups take reduction steps round-robin, so four steps are unpacked concurrently
 constexpr int kGroupWarps = kUnpackWarps / kUnpackGroups;
-constexpr int kGroupThreads = 32 * kGroupWarps;   // 64 threads x 4 items = 256 (row, half) items of one step
+constexpr int kGroupThreads = 32 * kGroupWarps;   // 128 threads x 2 items = 256 (row, half) items of one step
+constexpr int kItemsPerThread = 256 / kGroupThreads;
 constexpr int kThreads = 32 * (7 + kUnpackWarps);  // + A producer, MMA, 4 epilogue, packed-weight producer
 constexpr int kLoraATile = kBM * 32;        // [128 x 16] bf16
 constexpr int kLoraBTile = kBNh * 32;       // 4096 either way
 constexpr int kTmemCols = 512;
+constexpr int kEpiRowBytes = 80;            // 32 bf16 + 16 B pad: conflict-free 16-byte row writes
+constexpr int kEpiWarpBytes = 32 * kEpiRowBytes;
 
 // Packed-stage geometry: what one reduction step needs of the packed weight in ONE CTA, as TMA boxes over
 // the payload viewed as uint32 [rows, pitch/4].  x coordinates are always multiples of 4 words (16 bytes).
@@ -88,7 +91,8 @@ struct Cfg {
   static constexpr int kOffP = kOffB + kBStages * kBStage;
   static constexpr int kOffLA = kOffP + kPStages * kPStage;
   static constexpr int kOffLB = kOffLA + kMT * kLoraATile;
-  static constexpr int kOffGrid = kOffLB + kLoraBTile;                      // IQ2_XXS table (2 KB)
+  static constexpr int kOffEpi = kOffLB + kLoraBTile;                       // 4 epilogue warps x [32 rows x 80 B] staging
+  static constexpr int kOffGrid = kOffEpi + 4 * kEpiWarpBytes;              // IQ2_XXS table (2 KB)
   static constexpr int kOffBar = kOffGrid + (QT == B2G_IQ2_XXS ? 2048 : 0);
   static constexpr int kNumBars = 2 * kAStages + 2 * kBStages + 2 * kPStages + 2 + 2;
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;                   // tmem slot, abort flag
@@ -439,6 +443,7 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
       dev::tc_fence_after();
       const uint32_t acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
       const bool vec_ok = (p.ldc & 7) == 0;
+      uint8_t* stage = smem + C::kOffEpi + q * kEpiWarpBytes;
       for (int m = 0; m < nmt; ++m) {
         const int row_local = m * kPairRows + static_cast<int>(rank) * kBM + q * 32 + lane;
         const bool row_ok = row_local < t.rows;
@@ -449,13 +454,16 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
           dev::tmem_ld_32x32(acc + m * kBN + c * 32, r);
           dev::tmem_ld_wait();
           const int cbase = col0 + c * 32;
+          const bool fast = vec_ok && cbase + 32 <= ncols;   // uniform across the warp
           if (row_ok && cbase < ncols && p.debug != 4) {
             if (MODE == kFwd && p.bias) {
 #pragma unroll
               for (int i = 0; i < 32; ++i)
                 if (cbase + i < ncols) r[i] = __float_as_uint(__uint_as_float(r[i]) + __bfloat162float(p.bias[cbase + i]));
             }
-            if (vec_ok && cbase + 32 <= ncols) {
+            if (fast) {
+              // own row -> staging buffer (lane = row); written out below with four lanes per row so that every
+              // store instruction fills whole 32-byte sectors
 #pragma unroll
               for (int v = 0; v < 4; ++v) {
                 uint4 o;
@@ -463,13 +471,27 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
                 o.y = dev::pack_bf16(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
                 o.z = dev::pack_bf16(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
                 o.w = dev::pack_bf16(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-                *reinterpret_cast<uint4*>(orow + cbase + 8 * v) = o;
+                *reinterpret_cast<uint4*>(stage + lane * kEpiRowBytes + 16 * v) = o;
               }
             } else {
 #pragma unroll
               for (int i = 0; i < 32; ++i)
                 if (cbase + i < ncols) orow[cbase + i] = __float2bfloat16_rn(__uint_as_float(r[i]));
             }
+          }
+          if (fast && p.debug != 4) {
+            __syncwarp();
+            const int rows_here = t.rows - (m * kPairRows + static_cast<int>(rank) * kBM + q * 32);   // valid rows of this warp's 32
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int rr = (lane >> 2) + 8 * i;
+              if (rr < rows_here) {
+                const uint4 o = *reinterpret_cast<const uint4*>(stage + rr * kEpiRowBytes + 16 * (lane & 3));
+                *reinterpret_cast<uint4*>(outp + static_cast<int64_t>(t.row0 + m * kPairRows + static_cast<int>(rank) * kBM + q * 32 + rr) * p.ldc +
+                                          cbase + 8 * (lane & 3)) = o;
+              }
+            }
+            __syncwarp();
           }
         }
       }
@@ -520,9 +542,9 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
     }
   } else {
     // ============================== unpack ==============================
-    const int tid = threadIdx.x - 6 * 32;      // 0..255
+    const int tid = threadIdx.x - 6 * 32;
     const int group = tid / kGroupThreads;     // this group unpacks steps group, group + 4, group + 8, ...
-    const int tg = tid % kGroupThreads;        // 0..63
+    const int tg = tid % kGroupThreads;
     const uint2* grid_s = reinterpret_cast<const uint2*>(smem + C::kOffGrid);
     bool ok = true;
     int n = 0;                                 // running count of reduction steps of this CTA
@@ -538,11 +560,12 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
         const uint8_t* pk = smem + C::kOffP + sp * C::kPStage;
         uint8_t* bstage = smem + C::kOffB + sb * kBStage;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          // four (row, half) items per thread: forward 128 rows x 2 halves, dgrad 64 rows x 2 column quarters x 2 halves
-          const int half = j >> 1;
-          const int drow = MODE == kFwd ? tg + 64 * (j & 1) : tg;
-          const int sub = MODE == kFwd ? 0 : (j & 1);                 // dgrad: which 64 of this CTA's 128 columns
+        for (int j = 0; j < kItemsPerThread; ++j) {
+          // 256 (row, half) items per step: forward 128 rows x 2 halves, dgrad 64 rows x 2 column quarters x 2 halves
+          const int idx = tg + kGroupThreads * j;
+          const int half = idx >> 7;                                  // uniform across a warp
+          const int drow = MODE == kFwd ? (idx & 127) : (idx & 63);
+          const int sub = MODE == kFwd ? 0 : ((idx >> 6) & 1);        // dgrad: which 64 of this CTA's 128 columns
           const int quarter = 2 * static_cast<int>(rank) + sub;       // ... = which 64 of the tile's 256 columns
           uint32_t out[16];
           unpack_half<QT, MODE>(pk, drow, MODE == kFwd ? (it & 3) : quarter, half, it, ct, grid_s, out);

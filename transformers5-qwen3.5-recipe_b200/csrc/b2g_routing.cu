@@ -170,13 +170,29 @@ __global__ void __launch_bounds__(256) plan_scatter_kernel(const void* __restric
 // ---------------------------------------------------------------------------------------------
 // Permute / un-permute.  Rows are H bf16 wide; a thread moves 8 values (16 bytes) at a time.
 // ---------------------------------------------------------------------------------------------
+// One warp per destination row, up to eight 16-byte loads in flight per lane.
 __global__ void __launch_bounds__(256) gather_kernel(const uint4* __restrict__ hidden, const int64_t* __restrict__ perm,
                                                      uint4* __restrict__ sel, int64_t R, int top_k, int vec_per_row) {
-  for (int64_t s = blockIdx.x; s < R; s += gridDim.x) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t s = warp; s < R; s += nwarps) {
     const int64_t tok = perm[s] / top_k;
     const uint4* src = hidden + tok * vec_per_row;
     uint4* dst = sel + s * vec_per_row;
-    for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) dst[v] = src[v];
+    for (int v0 = 0; v0 < vec_per_row; v0 += 256) {
+      uint4 buf[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int v = v0 + lane + 32 * i;
+        if (v < vec_per_row) buf[i] = src[v];
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int v = v0 + lane + 32 * i;
+        if (v < vec_per_row) dst[v] = buf[i];
+      }
+    }
   }
 }
 
@@ -254,18 +270,21 @@ __global__ void __launch_bounds__(256) combine_kernel(const uint4* __restrict__ 
   }
 }
 
+// One warp per routed row: no block-wide barrier, eight independent rows in flight per block.
 template <bool kW32>
 __global__ void __launch_bounds__(256) combine_bwd_kernel(const uint4* __restrict__ expert_out, const void* __restrict__ weights,
                                                           const int64_t* __restrict__ perm, const uint4* __restrict__ grad_final,
                                                           uint4* __restrict__ grad_out, void* __restrict__ grad_w, int64_t R,
                                                           int top_k, int vec_per_row) {
-  __shared__ float red[8];
-  for (int64_t s = blockIdx.x; s < R; s += gridDim.x) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t s = warp; s < R; s += nwarps) {
     const int64_t route = perm[s];
     const int64_t tok = route / top_k;
     const float w = load_weight_bf16<kW32>(weights, route);
     float dot = 0.f;
-    for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
+    for (int v = lane; v < vec_per_row; v += 32) {
       const uint4 g = grad_final[tok * vec_per_row + v];
       const uint4 y = expert_out[s * vec_per_row + v];
       const uint32_t gq[4] = {g.x, g.y, g.z, g.w}, yq[4] = {y.x, y.y, y.z, y.w};
@@ -281,15 +300,10 @@ __global__ void __launch_bounds__(256) combine_bwd_kernel(const uint4* __restric
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xFFFFFFFFu, dot, off);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = dot;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      float total = 0.f;
-      for (int i = 0; i < (int)(blockDim.x >> 5); ++i) total += red[i];
-      if (kW32) static_cast<float*>(grad_w)[route] = total;
-      else static_cast<__nv_bfloat16*>(grad_w)[route] = __float2bfloat16_rn(total);
+    if (lane == 0) {
+      if (kW32) static_cast<float*>(grad_w)[route] = dot;
+      else static_cast<__nv_bfloat16*>(grad_w)[route] = __float2bfloat16_rn(dot);
     }
-    __syncthreads();
   }
 }
 
@@ -422,7 +436,7 @@ extern "C" int b2g_route_gather(const void* hidden, const int64_t* perm, void* s
   const int64_t R = T * top_k;
   if (R == 0) return 0;
   B2G_REQUIRE(hidden && perm && selected && aligned16(hidden) && aligned16(selected), "null or misaligned pointer");
-  gather_kernel<<<row_grid(R), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint4*>(hidden), perm,
+  gather_kernel<<<row_grid((R + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint4*>(hidden), perm,
                                                                             static_cast<uint4*>(selected), R, top_k, H / 8);
   B2G_CUDA_OK(cudaGetLastError());
   return 0;
@@ -465,10 +479,10 @@ extern "C" int b2g_route_combine_bwd(const void* expert_out, const void* weights
   B2G_REQUIRE(expert_out && weights && perm && grad_final && grad_expert_out && grad_weights, "null pointer");
   B2G_REQUIRE(aligned16(expert_out) && aligned16(grad_final) && aligned16(grad_expert_out), "misaligned pointer");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (w_dtype) combine_bwd_kernel<true><<<row_grid(R), 256, 0, s>>>(static_cast<const uint4*>(expert_out), weights, perm,
+  if (w_dtype) combine_bwd_kernel<true><<<row_grid((R + 7) / 8), 256, 0, s>>>(static_cast<const uint4*>(expert_out), weights, perm,
                                                                     static_cast<const uint4*>(grad_final),
                                                                     static_cast<uint4*>(grad_expert_out), grad_weights, R, top_k, H / 8);
-  else combine_bwd_kernel<false><<<row_grid(R), 256, 0, s>>>(static_cast<const uint4*>(expert_out), weights, perm,
+  else combine_bwd_kernel<false><<<row_grid((R + 7) / 8), 256, 0, s>>>(static_cast<const uint4*>(expert_out), weights, perm,
                                                              static_cast<const uint4*>(grad_final),
                                                              static_cast<uint4*>(grad_expert_out), grad_weights, R, top_k, H / 8);
   B2G_CUDA_OK(cudaGetLastError());
