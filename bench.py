@@ -177,7 +177,7 @@ def run_moe(args) -> int:
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29531")
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
-    from b2g import _lib, ep, gguf_quant, ops
+    from b2g import _lib, ep, ep_peer, gguf_quant, ops
 
     E, H, I, TOPK, R_LORA = 256, 2048, 512, 8, 16
     t_total = args.tokens if args.tokens != 32768 else (16384 if world == 1 else 65536)
@@ -207,13 +207,19 @@ def run_moe(args) -> int:
         bias = torch.randn(E, generator=torch.Generator(device=dev).manual_seed(SEED + 4), device=dev) * 0.5   # same on every rank
         logits = logits + bias
 
+    use_peer = world > 1 and args.ep == "peer"
+    xchg = ep_peer.PeerExchange(t_local * TOPK, H, E, device=dev) if use_peer else None
+
     def step():
         h = hidden.detach().requires_grad_(True)
         for v in lora.values():
             v.grad = None
         idx = ops.router_topk(logits, TOPK, None, False)
         wts = torch.softmax(logits.gather(1, idx), dim=-1)
-        out = ep.cuda_moe_layer(h, idx, wts, gate_p, up_p, down_p, Q4_K, I, E, lora, SCALING)
+        if use_peer:
+            out = ep_peer.peer_moe_layer(xchg, h, idx, wts, gate_p, up_p, down_p, Q4_K, I, lora, SCALING)
+        else:
+            out = ep.cuda_moe_layer(h, idx, wts, gate_p, up_p, down_p, Q4_K, I, E, lora, SCALING)
         out.backward(g_out)
         return out, h.grad
 
@@ -258,7 +264,8 @@ def run_moe(args) -> int:
             "scaling": "strong" if world > 1 or t_total == 65536 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "grouped MoE Q4_K LoRA, 256 experts top-8, hidden 2048, intermediate 512 (BASELINE configs[%d])" % (4 if skew else 2),
                        "tokens_total": t_total, "experts_per_gpu": e_local, "skewed_router": skew,
-                       "parallelism": f"ep{world} (experts sharded, NCCL all-to-all dispatch/combine)" if world > 1 else "1 GPU",
+                       "parallelism": (f"ep{world} (experts sharded, " + ("peer-store dispatch/combine over NVLink)" if use_peer else "NCCL all-to-all dispatch/combine)"))
+                       if world > 1 else "1 GPU",
                        "l2": "routed rows 2 GiB, larger than L2"},
             "step_tflops": flops / (ms_step * 1e-3) / 1e12, "step_frac_of_tensor_peak_all_gpus": flops / (ms_step * 1e-3) / 1e12 / (peak_tf * world),
             "peak_source": peak_src, "clocks": clocks, "gpu_launches": launches}))
@@ -274,6 +281,8 @@ def main() -> int:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--tokens", type=int, default=32768, help="M: tokens per step and per GPU")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ep", default="peer", choices=["peer", "nccl"],
+                    help="MoE workload at N>1: row exchange by peer stores over NVLink (default) or by NCCL all-to-all")
     ap.add_argument("--workload", default="dense", choices=["dense", "moe"],
                     help="dense: BASELINE configs[1] (default, replicas at N>1); moe: grouped Q4_K experts, expert-parallel at N>1")
     args = ap.parse_args()
@@ -418,7 +427,10 @@ def main() -> int:
             achieved = 2.0 * m * n_big * K_DIM / (kernel_ms * 1e-3) / 1e12
             roof = {"bound": "tensor", "kernel": "qgemm_kernel<Q4_K, forward> M=%d N=%d K=%d" % (m, n_big, K_DIM),
                     "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
-                    "peak_source": f"{peak_src} burst cuBLAS bf16", "kernel_ms": kernel_ms, "traffic": None}
+                    "peak_source": f"{peak_src} burst cuBLAS bf16", "kernel_ms": kernel_ms,
+                    # dram__bytes_read + dram__bytes_write of this kernel: 161.3 MB per launch in the ncu capture at M=16384
+                    # (profiles/qgemm_q4k_forward_M16384_N4096_K2048.md); traffic is activations in and out, proportional to M
+                    "traffic": 161.3e6 * m / 16384, "traffic_unit": "bytes/launch"}
         line = {"metric": "quantized LoRA-linear fwd+bwd tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world,
                 "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,

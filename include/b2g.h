@@ -188,6 +188,26 @@ B2G_API int b2g_grouped_lora_wgrad(const void* s, const void* t, float scale, co
 B2G_API int b2g_grouped_lora_up(const void* p, int64_t ldp, const void* w, int w_is_nr, const int32_t* offsets_full, void* y,
                         int64_t R, int64_t N, int r, int num_experts, void* stream);
 
+/* ---- expert-parallel row exchange over peer memory (new design: the reference is single-GPU,
+ *      docs/plan_qwen3.5.md:23) -------------------------------------------------------------------------- */
+
+/* Source side.  For every routed row s (rows sorted by global expert id, sorted_expert[R]) copy the row into the
+ * receive buffer of the expert's owner rank: peer_ptrs[owner] (device array of one base address per rank, NVLink
+ * peer pointers of a symmetric allocation) at row dest_base[e] + (s - my_start[e]).  With perm != NULL the row is
+ * gathered from the token matrix (row perm[s] / top_k of src): the token permute of _route_gather_forward_kernel
+ * (fast_moe_routing.py:101-123) and the inter-GPU dispatch in one pass; with perm == NULL row s of src is sent.
+ * A slot at or beyond capacity_rows is never written; the status word is set to 901 instead. */
+B2G_API int b2g_ep_scatter_rows(const void* src, const int64_t* perm, int top_k, const int64_t* sorted_expert,
+                        const int32_t* my_start, const int32_t* dest_base, const uint64_t* peer_ptrs, int experts_per_rank,
+                        int64_t R, int H, int64_t capacity_rows, int* status, void* stream);
+
+/* Owner side, the inverse: rows of the grouped buffer (blocks ordered by (local expert, source rank), block b
+ * spanning rows [blk_start[b], blk_start[b+1]), source rank b % world) go back to their source rank at row
+ * src_pos[b] + offset inside the block.  Pairs with the weighted un-permute of fast_moe_routing.py:162-194 on the
+ * source rank. */
+B2G_API int b2g_ep_return_rows(const void* rows, const int32_t* blk_start, const int32_t* src_pos, const uint64_t* peer_ptrs,
+                       int world, int num_blocks, int H, int64_t capacity_rows, void* stream);
+
 /* SwiGLU between the two grouped products: z = silu(g) * u (optionally clamped as the DeepSeek
  * experts do: g <= limit, |u| <= limit; limit <= 0 disables).  Replaces GGUFExperts._apply_split_gate
  * (called at fast_moe_lora.py:747; clamp semantics at test_deepseek_v4_moe_lora.py:194-196). */

@@ -144,3 +144,40 @@ def test_a_missing_rank_surfaces_as_an_error_not_a_hang(tmp_path):
     mp.spawn(_timeout_worker, args=(2, _free_port(), path), nprocs=2, join=True)
     res = torch.load(f"{path}.0")
     assert res["raised"], res
+
+
+def test_peer_exchange_plan_places_every_row_once_and_returns_it():
+    """The slot arithmetic of the peer-memory exchange (b2g/ep_peer.py), simulated for 4 ranks on the CPU:
+    every routed row lands in exactly one slot of its owner, slots are grouped by (local expert, source rank),
+    and the return mapping sends each slot back to the sorted position it came from."""
+    from b2g import ep_peer
+    from oracle import moe_ref
+
+    g_ranks, e_total, k, tokens = 4, 16, 3, 37
+    gen = torch.Generator().manual_seed(0)
+    idx = [torch.randint(0, e_total, (tokens, k), generator=gen) for _ in range(g_ranks)]
+    idx[2][:, :] = idx[2] % 5                                   # a rank that never uses most experts
+    plans = [moe_ref.route_plan(i, e_total) for i in idx]
+    counts = torch.stack([p["group_sizes"] for p in plans])
+    per = e_total // g_ranks
+    cap = int(counts.sum())
+    recv = [torch.full((cap, 2), -1) for _ in range(g_ranks)]
+    pp = [ep_peer.build_peer_plan(counts, r) for r in range(g_ranks)]
+    for r in range(g_ranks):
+        se = plans[r]["expert_indices"]
+        for s in range(se.numel()):
+            e = int(se[s])
+            slot = int(pp[r].dest_base[e]) + (s - int(pp[r].my_start[e]))
+            assert recv[e // per][slot, 0] == -1
+            recv[e // per][slot] = torch.tensor([r, s])
+    for o in range(g_ranks):
+        total = int(pp[o].local_sizes.sum())
+        assert (recv[o][:total, 0] >= 0).all() and (recv[o][total:, 0] == -1).all()
+        bs, sp = pp[o].blk_start.tolist(), pp[o].src_pos.tolist()
+        assert bs[-1] == total
+        for b in range(per * g_ranks):
+            for j in range(bs[b], bs[b + 1]):
+                src, pos = b % g_ranks, sp[b] + (j - bs[b])
+                assert recv[o][j].tolist() == [src, pos]
+                assert int(plans[src]["expert_indices"][pos]) == o * per + b // g_ranks
+        assert pp[o].local_offsets.tolist() == torch.cumsum(pp[o].local_sizes, 0).tolist()

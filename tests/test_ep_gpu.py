@@ -49,5 +49,18 @@ def test_single_rank_expert_parallel_equals_local_layer(cuda):
         assert torch.equal(out1, out2) and torch.equal(h1.grad, h2.grad)
         for n in lora:
             assert torch.equal(l1[n].grad, l2[n].grad), n
+
+        # the peer-store exchange (symmetric memory; with one rank every peer pointer is the rank's own buffer)
+        from b2g import ep_peer
+
+        xchg = ep_peer.PeerExchange(t * k, h, e, device=cuda)
+        for _ in range(2):                                   # twice: the second call reuses the buffers
+            h3 = hidden.clone().requires_grad_(True)
+            l3 = {n: v.clone().requires_grad_(True) for n, v in lora.items()}
+            out3 = ep_peer.peer_moe_layer(xchg, h3, idx, wts, *pk, go.Q4_K, i, l3, 2.0)
+            out3.backward(gout)
+            assert torch.equal(out3, out2) and torch.equal(h3.grad, h2.grad)
+            for n in lora:
+                assert torch.equal(l3[n].grad, l2[n].grad), n
     finally:
         dist.destroy_process_group()

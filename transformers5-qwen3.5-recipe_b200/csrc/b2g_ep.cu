@@ -1,0 +1,119 @@
+// Expert-parallel row exchange over peer memory: the token permute and the inter-GPU transfer are one pass.
+//
+// Every rank maps the receive buffers of all ranks (NVLink peer pointers of a symmetric allocation).
+//   scatter: for each routed row, sorted by global expert id on the SOURCE rank, copy the token's row straight
+//            into the OWNER rank's receive buffer, at the slot that groups rows by (local expert, source rank).
+//            With `perm` the source row is gathered from the token matrix on the fly (dispatch of activations);
+//            without it rows are taken in order (dispatch of output gradients).
+//   return : the inverse on the OWNER rank: each row of the grouped buffer goes back to its source rank, to the
+//            position it has in that rank's sorted order (combine of expert outputs / of input gradients).
+// Slots come from the all-gathered count matrix, so no split size ever visits the host.  Plain 16-byte peer
+// stores only: no multicast, no waits inside the kernels (ranks synchronise between the two phases on the
+// stream, outside these kernels).
+#include "b2g_common.cuh"
+
+namespace b2g {
+namespace ep {
+
+__global__ void __launch_bounds__(256) scatter_rows_kernel(const uint4* __restrict__ src, const int64_t* __restrict__ perm, int top_k,
+                                                           const int64_t* __restrict__ sorted_expert, const int32_t* __restrict__ my_start,
+                                                           const int32_t* __restrict__ dest_base, const unsigned long long* __restrict__ peers,
+                                                           int experts_per_rank, int64_t R, int vec_per_row, int64_t capacity, int* status) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t s = warp; s < R; s += nwarps) {
+    const int e = static_cast<int>(sorted_expert[s]);
+    const int owner = e / experts_per_rank;
+    const int64_t slot = static_cast<int64_t>(dest_base[e]) + (s - my_start[e]);
+    if (slot >= capacity) {
+      if (lane == 0 && status) atomicCAS(status, 0, 901);   // receive buffer too small: report, never write past it
+      continue;
+    }
+    const int64_t from = perm ? perm[s] / top_k : s;
+    const uint4* in = src + from * vec_per_row;
+    uint4* out = reinterpret_cast<uint4*>(peers[owner]) + slot * vec_per_row;
+    for (int v0 = 0; v0 < vec_per_row; v0 += 256) {
+      uint4 buf[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int v = v0 + lane + 32 * i;
+        if (v < vec_per_row) buf[i] = in[v];
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int v = v0 + lane + 32 * i;
+        if (v < vec_per_row) out[v] = buf[i];
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) return_rows_kernel(const uint4* __restrict__ rows, const int32_t* __restrict__ blk_start,
+                                                          const int32_t* __restrict__ src_pos, const unsigned long long* __restrict__ peers,
+                                                          int world, int num_blocks, int vec_per_row, int64_t capacity) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int64_t total = blk_start[num_blocks];
+  const int64_t live = total < capacity ? total : capacity;
+  for (int64_t j = warp; j < live; j += nwarps) {
+    // block (local expert, source rank) that holds row j: last b with blk_start[b] <= j
+    int lo = 0, hi = num_blocks - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (blk_start[mid] <= j) lo = mid; else hi = mid - 1;
+    }
+    const int64_t pos = static_cast<int64_t>(src_pos[lo]) + (j - blk_start[lo]);
+    const uint4* in = rows + j * vec_per_row;
+    uint4* out = reinterpret_cast<uint4*>(peers[lo % world]) + pos * vec_per_row;
+    for (int v0 = 0; v0 < vec_per_row; v0 += 256) {
+      uint4 buf[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int v = v0 + lane + 32 * i;
+        if (v < vec_per_row) buf[i] = in[v];
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int v = v0 + lane + 32 * i;
+        if (v < vec_per_row) out[v] = buf[i];
+      }
+    }
+  }
+}
+
+}  // namespace ep
+}  // namespace b2g
+
+using namespace b2g;
+
+extern "C" int b2g_ep_scatter_rows(const void* src, const int64_t* perm, int top_k, const int64_t* sorted_expert, const int32_t* my_start,
+                                   const int32_t* dest_base, const uint64_t* peer_ptrs, int experts_per_rank, int64_t R, int H,
+                                   int64_t capacity_rows, int* status, void* stream) {
+  B2G_REQUIRE(H > 0 && H % 8 == 0, "ep_scatter_rows: row width %d must be a positive multiple of 8", H);
+  B2G_REQUIRE(experts_per_rank >= 1 && capacity_rows >= 0 && R >= 0, "ep_scatter_rows: bad sizes");
+  B2G_REQUIRE(perm == nullptr || top_k >= 1, "ep_scatter_rows: top_k must be positive when rows are gathered");
+  if (R == 0) return 0;
+  B2G_REQUIRE(src && sorted_expert && my_start && dest_base && peer_ptrs && aligned16(src), "ep_scatter_rows: null or misaligned pointer");
+  const int64_t want = (R + 7) / 8, cap = (int64_t)sm_count() * 8;
+  ep::scatter_rows_kernel<<<(int)(want < cap ? want : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), perm, top_k, sorted_expert, my_start, dest_base, reinterpret_cast<const unsigned long long*>(peer_ptrs),
+      experts_per_rank, R, H / 8, capacity_rows, status);
+  B2G_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int b2g_ep_return_rows(const void* rows, const int32_t* blk_start, const int32_t* src_pos, const uint64_t* peer_ptrs, int world,
+                                  int num_blocks, int H, int64_t capacity_rows, void* stream) {
+  B2G_REQUIRE(H > 0 && H % 8 == 0, "ep_return_rows: row width %d must be a positive multiple of 8", H);
+  B2G_REQUIRE(world >= 1 && num_blocks >= 1 && num_blocks % world == 0, "ep_return_rows: %d blocks do not split over %d ranks", num_blocks, world);
+  if (capacity_rows == 0) return 0;
+  B2G_REQUIRE(rows && blk_start && src_pos && peer_ptrs && aligned16(rows), "ep_return_rows: null or misaligned pointer");
+  const int64_t want = (capacity_rows + 7) / 8, cap = (int64_t)sm_count() * 8;
+  ep::return_rows_kernel<<<(int)(want < cap ? want : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(rows), blk_start, src_pos, reinterpret_cast<const unsigned long long*>(peer_ptrs), world, num_blocks, H / 8,
+      capacity_rows);
+  B2G_CUDA_OK(cudaGetLastError());
+  return 0;
+}
