@@ -27,7 +27,6 @@
 // barriers that release buffers are signalled in both CTAs by tcgen05.commit.  No TMA multicast is used:
 // every CTA loads its own tiles.  All mbarrier waits are bounded.
 #include "b2g_formats.cuh"
-#include <cstdlib>
 
 namespace b2g {
 int iq2xxs_grid(const uint2** out);
@@ -54,8 +53,8 @@ constexpr int kThreads = 32 * (7 + kUnpackWarps);  // + A producer, MMA, 4 epilo
 constexpr int kLoraATile = kBM * 32;        // [128 x 16] bf16
 constexpr int kLoraBTile = kBNh * 32;       // 4096 either way
 constexpr int kTmemCols = 512;
-constexpr int kEpiRowBytes = 80;            // 32 bf16 + 16 B pad: conflict-free 16-byte row writes
-constexpr int kEpiWarpBytes = 32 * kEpiRowBytes;
+constexpr int kEpiRowBytes = 64;            // 32 bf16: the dense [32 rows x 32 columns] box of a bulk tensor store
+constexpr int kEpiBufBytes = 32 * kEpiRowBytes;
 
 // Packed-stage geometry: what one reduction step needs of the packed weight in ONE CTA, as TMA boxes over
 // the payload viewed as uint32 [rows, pitch/4].  x coordinates are always multiples of 4 words (16 bytes).
@@ -91,8 +90,9 @@ struct Cfg {
   static constexpr int kOffP = kOffB + kBStages * kBStage;
   static constexpr int kOffLA = kOffP + kPStages * kPStage;
   static constexpr int kOffLB = kOffLA + kMT * kLoraATile;
-  static constexpr int kOffEpi = kOffLB + kLoraBTile;                       // 4 epilogue warps x [32 rows x 80 B] staging
-  static constexpr int kOffGrid = kOffEpi + 4 * kEpiWarpBytes;              // IQ2_XXS table (2 KB)
+  static constexpr int kEpiBufs = P::kBytes <= 9216 ? 2 : 1;                // staging buffers per epilogue warp
+  static constexpr int kOffEpi = kOffLB + kLoraBTile;                       // 4 epilogue warps x kEpiBufs x [32 rows x 64 B]
+  static constexpr int kOffGrid = kOffEpi + 4 * kEpiBufs * kEpiBufBytes;    // IQ2_XXS table (2 KB)
   static constexpr int kOffBar = kOffGrid + (QT == B2G_IQ2_XXS ? 2048 : 0);
   static constexpr int kNumBars = 2 * kAStages + 2 * kBStages + 2 * kPStages + 2 + 2;
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;                   // tmem slot, abort flag
@@ -119,7 +119,6 @@ struct Params {
   const __nv_bfloat16* bias;
   const uint2* grid;  // IQ2_XXS table in global memory
   int* status;
-  int debug;          // timing experiments only (0 = normal)
 };
 
 struct Tile { int expert, row0, rows, ct; };
@@ -283,7 +282,8 @@ template <int QT, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_a1,
              const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1,
-             const __grid_constant__ CUtensorMap tm_la, const __grid_constant__ CUtensorMap tm_lb) {
+             const __grid_constant__ CUtensorMap tm_la, const __grid_constant__ CUtensorMap tm_lb,
+             const __grid_constant__ CUtensorMap tm_o0, const __grid_constant__ CUtensorMap tm_o1) {
   using C = Cfg<QT, MODE>;
   using P = Packed<QT, MODE>;
   extern __shared__ uint8_t smem_raw[];
@@ -400,7 +400,7 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
                                                 : dev::make_smem_desc(b_base + k16 * 2048, 8192, 1024, 2);
             for (int m = 0; m < nmt; ++m) {
               const uint64_t adesc = dev::make_smem_desc(a_base + m * kATile + k16 * 32, 16, 1024, 2);
-              if (p.debug != 3) dev::umma_bf16_pair(tmem_base + m * kBN, adesc, bdesc, idesc, (it | k16) != 0 ? 1u : 0u);
+              dev::umma_bf16_pair(tmem_base + m * kBN, adesc, bdesc, idesc, (it | k16) != 0 ? 1u : 0u);
             }
           }
           dev::umma_commit_pair(bar(kEmptyA + sa));
@@ -429,6 +429,7 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
     // ============================== epilogue ==============================
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     int pacc = 0;
+    int nstore = 0;          // bulk stores issued by this warp (selects the staging buffer)
     bool ok = true;
     for (int item = pair; item < total_items && ok; item += num_pairs) {
       const Tile t = get_tile(p, item);
@@ -443,9 +444,11 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
       dev::tc_fence_after();
       const uint32_t acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
       const bool vec_ok = (p.ldc & 7) == 0;
-      uint8_t* stage = smem + C::kOffEpi + q * kEpiWarpBytes;
+      const CUtensorMap* om = seg ? &tm_o1 : &tm_o0;
       for (int m = 0; m < nmt; ++m) {
-        const int row_local = m * kPairRows + static_cast<int>(rank) * kBM + q * 32 + lane;
+        const int row_first = m * kPairRows + static_cast<int>(rank) * kBM + q * 32;   // first of this warp's 32 rows
+        const int rows_here = t.rows - row_first;                                      // how many of them exist
+        const int row_local = row_first + lane;
         const bool row_ok = row_local < t.rows;
         __nv_bfloat16* orow = outp + static_cast<int64_t>(t.row0 + row_local) * p.ldc;
 #pragma unroll 1
@@ -454,41 +457,60 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
           dev::tmem_ld_32x32(acc + m * kBN + c * 32, r);
           dev::tmem_ld_wait();
           const int cbase = col0 + c * 32;
-          const bool fast = vec_ok && cbase + 32 <= ncols;   // uniform across the warp
-          if (row_ok && cbase < ncols && p.debug != 4) {
-            if (MODE == kFwd && p.bias) {
+          if (cbase >= ncols || rows_here <= 0) continue;      // uniform across the warp
+          if (MODE == kFwd && p.bias) {
 #pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (cbase + i < ncols) r[i] = __float_as_uint(__uint_as_float(r[i]) + __bfloat162float(p.bias[cbase + i]));
-            }
-            if (fast) {
-              // own row -> staging buffer (lane = row); written out below with four lanes per row so that every
-              // store instruction fills whole 32-byte sectors
-#pragma unroll
-              for (int v = 0; v < 4; ++v) {
-                uint4 o;
-                o.x = dev::pack_bf16(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
-                o.y = dev::pack_bf16(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-                o.z = dev::pack_bf16(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-                o.w = dev::pack_bf16(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-                *reinterpret_cast<uint4*>(stage + lane * kEpiRowBytes + 16 * v) = o;
-              }
-            } else {
+            for (int i = 0; i < 32; ++i)
+              if (cbase + i < ncols) r[i] = __float_as_uint(__uint_as_float(r[i]) + __bfloat162float(p.bias[cbase + i]));
+          }
+          if (!vec_ok) {                                       // odd row pitch: element stores
+            if (row_ok) {
 #pragma unroll
               for (int i = 0; i < 32; ++i)
                 if (cbase + i < ncols) orow[cbase + i] = __float2bfloat16_rn(__uint_as_float(r[i]));
             }
+            continue;
           }
-          if (fast && p.debug != 4) {
+          // own row -> staging buffer (lane = row).  The buffer was last read by the bulk store issued kEpiBufs chunks ago.
+          uint8_t* stage = smem + C::kOffEpi + (q * C::kEpiBufs + (nstore % C::kEpiBufs)) * kEpiBufBytes;
+          if (lane == 0) dev::bulk_wait_read<C::kEpiBufs - 1>();
+          __syncwarp();
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 o;
+            o.x = dev::pack_bf16(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+            o.y = dev::pack_bf16(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+            o.z = dev::pack_bf16(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+            o.w = dev::pack_bf16(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+            *reinterpret_cast<uint4*>(stage + lane * kEpiRowBytes + 16 * v) = o;
+          }
+          if (rows_here >= 32) {
+            // all 32 rows belong to this tile: one asynchronous bulk store (columns past the tensor edge are clipped),
+            // which drains while the next chunks and the next tile proceed
+            dev::fence_proxy_async_smem();
             __syncwarp();
-            const int rows_here = t.rows - (m * kPairRows + static_cast<int>(rank) * kBM + q * 32);   // valid rows of this warp's 32
+            if (lane == 0) {
+              dev::tma_store_2d(om, dev::smem_u32(stage), cbase, t.row0 + row_first);
+              dev::bulk_commit();
+            }
+            ++nstore;
+          } else {
+            // ragged end of an expert segment: rows past it belong to someone else, store the valid ones by hand
+            __syncwarp();
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               const int rr = (lane >> 2) + 8 * i;
-              if (rr < rows_here) {
+              const int cc = cbase + 8 * (lane & 3);
+              if (rr < rows_here && cc < ncols) {
                 const uint4 o = *reinterpret_cast<const uint4*>(stage + rr * kEpiRowBytes + 16 * (lane & 3));
-                *reinterpret_cast<uint4*>(outp + static_cast<int64_t>(t.row0 + m * kPairRows + static_cast<int>(rank) * kBM + q * 32 + rr) * p.ldc +
-                                          cbase + 8 * (lane & 3)) = o;
+                if (cc + 8 <= ncols) {
+                  *reinterpret_cast<uint4*>(outp + static_cast<int64_t>(t.row0 + row_first + rr) * p.ldc + cc) = o;
+                } else {
+                  const uint32_t w[4] = {o.x, o.y, o.z, o.w};
+                  __nv_bfloat16* dst = outp + static_cast<int64_t>(t.row0 + row_first + rr) * p.ldc + cc;
+                  for (int e2 = 0; e2 < 8 && cc + e2 < ncols; ++e2)
+                    dst[e2] = __ushort_as_bfloat16(static_cast<unsigned short>((w[e2 >> 1] >> (16 * (e2 & 1))) & 0xFFFFu));
+                }
               }
             }
             __syncwarp();
@@ -500,6 +522,7 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
       if (lane == 0) dev::mbar_arrive_cluster(lead_acc_empty);
       pacc ^= 1;
     }
+    if (lane == 0) dev::bulk_wait_all();   // staging buffers are read until the last bulk store completes
   } else if (warp == 6 + kUnpackWarps) {
     // ============================== packed-weight producer ==============================
     if (lane == 0) {
@@ -644,7 +667,6 @@ int launch_impl(const Launch& L) {
   p.bias = static_cast<const __nv_bfloat16*>(L.bias);
   p.status = L.status;
   p.grid = nullptr;
-  { const char* e = getenv("B2G_QGEMM_DEBUG"); p.debug = e ? atoi(e) : 0; }
   if (QT == B2G_IQ2_XXS) {
     int rc = iq2xxs_grid(&p.grid);
     if (rc) return rc;
@@ -678,6 +700,15 @@ int launch_impl(const Launch& L) {
     }
   }
 
+  CUtensorMap tm_o0 = tm_a0, tm_o1 = tm_a0;
+  if ((p.ldc & 7) == 0) {   // bulk stores need a 16-byte row pitch; odd widths take the element-store path
+    const uint64_t ocols = MODE == kFwd ? (uint64_t)p.n : (uint64_t)p.k;
+    if ((rc = make_tmap_2d(&tm_o0, L.out0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ocols, L.m_total, (uint64_t)p.ldc * 2, 32, 32,
+                           CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
+    tm_o1 = tm_o0;
+    if (L.out1 && (rc = make_tmap_2d(&tm_o1, L.out1, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ocols, L.m_total, (uint64_t)p.ldc * 2, 32, 32,
+                                     CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
+  }
   auto kern = qgemm_kernel<QT, MODE>;
   B2G_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
   int pairs = sm_count() / 2;
@@ -698,7 +729,7 @@ int launch_impl(const Launch& L) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  B2G_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p, tm_a0, tm_a1, tm_w0, tm_w1, tm_la, tm_lb));
+  B2G_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p, tm_a0, tm_a1, tm_w0, tm_w1, tm_la, tm_lb, tm_o0, tm_o1));
   return 0;
 }
 
