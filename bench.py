@@ -135,14 +135,14 @@ def cpu_step_fn(layers_cpu):
 def run_cpu(steps: int, warmup: int, budget_s: float, m_full: int) -> dict:
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
-    layers, x, dys = make_inputs(2048, "cpu")
+    layers, x, dys = make_inputs(m_full, "cpu")
     step = cpu_step_fn(layers)
     step(x[:64], [d[:64] for d in dys])                      # first-call overheads
     t0 = time.perf_counter()
-    step(x[:256], [d[:256] for d in dys])
-    per_row = (time.perf_counter() - t0) / 256
+    step(x[:512], [d[:512] for d in dys])
+    per_row = (time.perf_counter() - t0) / 512
     per_step_budget = max(0.05, budget_s / max(1, steps + warmup))
-    m = int(min(2048, max(64, per_step_budget / per_row)))
+    m = int(min(m_full, max(64, per_step_budget / per_row)))   # the whole workload when the budget allows, else a prefix of it
     m = max(64, m // 64 * 64)
     xs, ds = x[:m].contiguous(), [d[:m].contiguous() for d in dys]
     for _ in range(warmup):
@@ -440,7 +440,7 @@ def main() -> int:
                 "e2e": {"value": world * m / (ms_e2e / e2e_steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                         "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / e2e_steps}}
         if world == 1 and not args.no_cpu_baseline:
-            res = run_cpu(3, 1, budget_s=20.0, m_full=m)
+            res = run_cpu(3, 1, budget_s=24.0, m_full=m)
             line["cpu_baseline"] = {"value": res["tokens_per_s"], "unit": "tokens/s", "cores": res["cores"], "kind": "port", "sample": res["sample"]}
         print(json.dumps(line))
     if dist is not None:

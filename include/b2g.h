@@ -166,7 +166,7 @@ B2G_API int b2g_grouped_dgrad(int qtype, const void* dy0, const void* dy1, const
 
 /* Per-expert skinny projection P[rows_g, r] = X[rows_g, C] . W[e_g]^T, W given per expert as [r,C]
  * (w_is_cr = 0) or [C,r] (w_is_cr = 1); with x1 != NULL the reduction runs over [x | x1] (two
- * [R,C] halves against a [2C,r] factor: dGate|dUp against gate_up_b).  Outputs as b2g_lora_down.
+ * [R,C] halves against a [r,2C] or [2C,r] factor: dGate|dUp against gate_up_b).  Outputs as b2g_lora_down.
  * Replaces the first AITER gmm of _lora_grouped_linear (fast_moe_lora.py:675-682) and gmm's use in
  * _AiterGroupedMM.backward (:126-131). */
 B2G_API int b2g_grouped_lora_down(const void* x, const void* x1, const void* w, int w_is_cr, float scale, const int32_t* tiles,

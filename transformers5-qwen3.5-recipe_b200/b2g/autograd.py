@@ -130,11 +130,12 @@ class _LoraQLinear(torch.autograd.Function):
                 pad = (n + 7) // 8 * 8
                 dy_p = dy.new_zeros(dy.shape[0], pad)
                 dy_p[:, :n] = dy
-                b_p = b.new_zeros(pad, r)
-                b_p[:n] = b
-                dyb, dybs = ops.lora_down(dy_p, b_p, True, scaling, r)
+                b_p = b.new_zeros(r, pad)
+                b_p[:, :n] = b.t()
+                dyb, dybs = ops.lora_down(dy_p, b_p, False, scaling, r)
             else:
-                dyb, dybs = ops.lora_down(dy, b, True, scaling, r)
+                # B is tiny: transposing it once lets the projection stream it with the [r, C] layout
+                dyb, dybs = ops.lora_down(dy, b.t().contiguous(), False, scaling, r)
         dx = da = db = None
         if need_x:
             dx = ops.qlinear_dgrad(dy, payload.reshape(-1), quant_type, x2.shape[1], dybs, ops.pad_rank_rows(a)).reshape(xshape)
@@ -292,7 +293,7 @@ class _GroupedLoraExperts(torch.autograd.Function):
         d_gu_a = d_gu_b = d_down_a = d_down_b = None
         if has_lora:
             # down projection: dZ = dOut.deq(Wd) + s.(dOut.Bd).Ad ; dAd = s.(dOut.Bd)^T.Z ; dBd = s.dOut^T.(Z.Ad^T)
-            dob, dobs = ops.grouped_lora_down(d_out, None, down_b.contiguous(), True, scaling, r, tiles)
+            dob, dobs = ops.grouped_lora_down(d_out, None, down_b.transpose(1, 2).contiguous(), False, scaling, r, tiles)
             dz = ops.grouped_dgrad(d_out, None, down_p.reshape(-1), None, quant_down, inter_dim, e, tiles, dobs,
                                    ops.pad_rank_rows(down_a))
             d_down_a = torch.empty_like(down_a)
@@ -304,7 +305,7 @@ class _GroupedLoraExperts(torch.autograd.Function):
         d_gate, d_up = ops.swiglu_bwd(gate, up, dz, limit)
         if has_lora:
             # gate|up: dX = dG.deq(Wg) + dU.deq(Wu) + s.([dG|dU].Bgu).Agu
-            dgb, dgbs = ops.grouped_lora_down(d_gate, d_up, gu_b.contiguous(), True, scaling, r, tiles)
+            dgb, dgbs = ops.grouped_lora_down(d_gate, d_up, gu_b.transpose(1, 2).contiguous(), False, scaling, r, tiles)
             d_sel = ops.grouped_dgrad(d_gate, d_up, gate_p.reshape(-1), up_p.reshape(-1), quant_gu, hidden, e, tiles, dgbs,
                                       ops.pad_rank_rows(gu_a))
             d_gu_a = torch.empty_like(gu_a)

@@ -40,7 +40,7 @@ struct Seg { int expert, row0, rows; };
 // Projection: P[rows,16] = X[rows,C] . W_e^T  (r <= 16 columns live, the rest zero)
 // CTA = 4 warps x 16 rows; reduction in chunks of 128 columns, 3-stage cp.async ring.
 // ------------------------------------------------------------------------------------------------
-constexpr int kDownRows = 64, kDownBK = 128, kDownStages = 3, kDownStride = kDownBK * 2 + 16;  // 272-byte rows
+constexpr int kDownRows = 64, kDownBK = 128, kDownStages = 4, kDownStride = kDownBK * 2 + 16;  // 272-byte rows
 constexpr int kDownXBytes = kDownRows * kDownStride, kDownWBytes = kRankPad * kDownStride;
 constexpr int kDownStageBytes = kDownXBytes + kDownWBytes;
 
@@ -123,8 +123,16 @@ __global__ void __launch_bounds__(128) lora_down_kernel(const __nv_bfloat16* __r
       const int seg = ch / chunks, k = (ch - seg * chunks) * kDownBK + threadIdx.x;
       const unsigned short* src = reinterpret_cast<const unsigned short*>(we) + ((int64_t)seg * C + k) * r;
       const bool ok = k < C;
+      if (r == kRankPad && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {   // full rank: the 32-byte row in two vector loads
+        uint4 q0 = make_uint4(0, 0, 0, 0), q1 = q0;
+        if (ok) { q0 = reinterpret_cast<const uint4*>(src)[0]; q1 = reinterpret_cast<const uint4*>(src)[1]; }
+        const uint32_t w32[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
-      for (int n = 0; n < kRankPad; ++n) wv[n] = (ok && n < r) ? src[n] : (unsigned short)0;
+        for (int n = 0; n < kRankPad; ++n) wv[n] = static_cast<unsigned short>((w32[n >> 1] >> (16 * (n & 1))) & 0xFFFFu);
+      } else {
+#pragma unroll
+        for (int n = 0; n < kRankPad; ++n) wv[n] = (ok && n < r) ? src[n] : (unsigned short)0;
+      }
     };
     auto store_w = [&](int ch) {
       uint8_t* dst = sm + (ch % kDownStages) * kDownStageBytes + kDownXBytes + threadIdx.x * 2;
@@ -189,7 +197,7 @@ __global__ void __launch_bounds__(128) lora_down_kernel(const __nv_bfloat16* __r
 //   kPartial = true : dense path, segment = one split of M, fp32 partial to the workspace
 //   kPartial = false: grouped path, segment = one expert, scaled bf16 straight to the output
 // ------------------------------------------------------------------------------------------------
-constexpr int kWgCols = 128, kWgRows = 64, kWgStages = 3, kWgTStride = kWgCols * 2 + 16, kWgSStride = 48;
+constexpr int kWgCols = 128, kWgRows = 64, kWgStages = 4, kWgTStride = kWgCols * 2 + 16, kWgSStride = 48;
 constexpr int kWgStageBytes = kWgRows * kWgTStride + kWgRows * kWgSStride;
 
 template <bool kPartial>
@@ -366,7 +374,7 @@ static int lora_down_launch(const void* x, const void* x1, const void* w, int w_
   B2G_REQUIRE(w_is_cr || (reinterpret_cast<uintptr_t>(w) & 3) == 0, "%s: weight must be 4-byte aligned", what);
   const size_t smem = (size_t)lora::kDownStages * lora::kDownStageBytes;
   const int dense_items = (int)((M + lora::kDownRows - 1) / lora::kDownRows);
-  int grid = sm_count() * 3;
+  int grid = sm_count() * 2;
   if (!tiles && dense_items < grid) grid = dense_items;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   auto* xb = static_cast<const __nv_bfloat16*>(x);
@@ -394,7 +402,6 @@ extern "C" int b2g_lora_down(const void* x, const void* w, int w_is_cr, float sc
 extern "C" int b2g_grouped_lora_down(const void* x, const void* x1, const void* w, int w_is_cr, float scale, const int32_t* tiles,
                                      void* out_plain, void* out_scaled, int64_t R, int64_t C, int r, int num_experts, void* stream) {
   B2G_REQUIRE(tiles != nullptr && num_experts >= 1, "grouped_lora_down: tile table missing");
-  B2G_REQUIRE(x1 == nullptr || w_is_cr, "grouped_lora_down: a two-part input needs the [2C, r] weight layout");
   return lora_down_launch(x, x1, w, w_is_cr, scale, tiles, out_plain, out_scaled, R, C, r, stream, "grouped_lora_down");
 }
 
