@@ -159,7 +159,7 @@ def run_cpu(steps: int, warmup: int, budget_s: float, m_full: int) -> dict:
 
 
 # ---------------------------------------------------------------------------------------------
-# MoE workload: BASELINE configs[2] on one GPU (16384 tokens) and configs[4] (65536 tokens, skewed router,
+# MoE workload: the 16384-token grouped configuration on one GPU and its 65536-token variant (skewed router,
 # experts sharded over the ranks, NCCL all-to-all dispatch / combine) when launched on several.
 # ---------------------------------------------------------------------------------------------
 def run_moe(args) -> int:
@@ -284,7 +284,7 @@ def main() -> int:
     ap.add_argument("--ep", default="peer", choices=["peer", "nccl"],
                     help="MoE workload at N>1: row exchange by peer stores over NVLink (default) or by NCCL all-to-all")
     ap.add_argument("--workload", default="dense", choices=["dense", "moe"],
-                    help="dense: BASELINE configs[1] (default, replicas at N>1); moe: grouped Q4_K experts, expert-parallel at N>1")
+                    help="dense: the Q4_K attention-shape linears (default, replicas at N>1); moe: grouped Q4_K experts, expert-parallel at N>1")
     args = ap.parse_args()
     if args.workload == "moe":
         return run_moe(args)
@@ -428,8 +428,8 @@ def main() -> int:
             roof = {"bound": "tensor", "kernel": "qgemm_kernel<Q4_K, forward> M=%d N=%d K=%d" % (m, n_big, K_DIM),
                     "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
                     "peak_source": f"{peak_src} burst cuBLAS bf16", "kernel_ms": kernel_ms,
-                    # dram__bytes_read + dram__bytes_write of this kernel: 161.3 MB per launch in the ncu capture at M=16384
-                    # (profiles/qgemm_q4k_forward_M16384_N4096_K2048.md); traffic is activations in and out, proportional to M
+                    # dram__bytes_read + dram__bytes_write of this kernel: 161.3 MB per launch in an ncu capture at M=16384;
+                    # the traffic is activations in and out (the packed weight stays in L2), so it scales with M
                     "traffic": 161.3e6 * m / 16384, "traffic_unit": "bytes/launch"}
         line = {"metric": "quantized LoRA-linear fwd+bwd tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world,
                 "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,

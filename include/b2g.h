@@ -15,7 +15,7 @@
  *
  * Each entry names the reference interface it stands in for (file:line in
  * woct0rdho/transformers5-qwen3.5-recipe).  The reference reaches these through the third-party
- * torch_ggml_ops / AITER ops; the mapping to those ops is in INTEGRATION.md.
+ * torch_ggml_ops / AITER ops, named at each entry below.
  */
 #ifndef B2G_H_
 #define B2G_H_

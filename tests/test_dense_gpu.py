@@ -52,7 +52,7 @@ def test_fused_lora_linear_forward_backward(cuda, qtype, m, n, k, r):
 
 
 def test_config0_q8_lora_linear(cuda):
-    """BASELINE configs[0]: Q8_0 2048x2048, r=16, alpha=32, 4096 tokens; also the bf16 oracle itself
+    """The CPU-runnable benchmark configuration: Q8_0 2048x2048, r=16, alpha=32, 4096 tokens; also the bf16 oracle itself
     must sit inside the same tolerance of the fp32 oracle."""
     from b2g import autograd as ag
 

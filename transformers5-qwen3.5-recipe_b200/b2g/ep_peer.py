@@ -9,7 +9,7 @@ the device, so no split size is read on the host and nothing is regrouped afterw
 Buffers are symmetric allocations (one per rank, same size, mapped into every rank): two receive buffers of
 ``capacity`` rows (activations forward, output gradients backward) and two return buffers of the rank's own
 routed-row count.  A layer object owns them; its outputs alias them until the next call of the same layer.
-Ranks synchronise on the stream around each exchange with a one-element NCCL all-reduce (no device-side spin
+Ranks synchronise on the stream after each exchange with a one-element NCCL all-reduce (no device-side spin
 loops of our own); multicast is not used.
 """
 from __future__ import annotations
@@ -91,7 +91,8 @@ class PeerExchange:
 
     def scatter(self, src: torch.Tensor, perm: Optional[torch.Tensor], top_k: int, sorted_expert: torch.Tensor, plan: PeerPlan, which: int):
         rows = sorted_expert.numel()
-        self.sync()          # owners are done with the previous contents of their receive buffers
+        # No synchronisation is needed before writing: the last reads of this receive buffer (expert forward / backward of
+        # the previous call) were enqueued before that call's final sync(), which every rank has passed to get here.
         with torch.cuda.device(self.device):
             _lib.call("b2g_ep_scatter_rows", C.c_void_p(src.data_ptr()), None if perm is None else C.c_void_p(perm.data_ptr()), int(top_k),
                       C.c_void_p(sorted_expert.data_ptr()), C.c_void_p(plan.my_start.data_ptr()), C.c_void_p(plan.dest_base.data_ptr()),
@@ -101,7 +102,8 @@ class PeerExchange:
         return self.recv[which]
 
     def give_back(self, rows: torch.Tensor, plan: PeerPlan, which: int):
-        self.sync()
+        # Same argument as in scatter(): every earlier read of the return buffers is separated from this write by at
+        # least one sync() that both ranks took part in.
         with torch.cuda.device(self.device):
             _lib.call("b2g_ep_return_rows", C.c_void_p(rows.data_ptr()), C.c_void_p(plan.blk_start.data_ptr()), C.c_void_p(plan.src_pos.data_ptr()),
                       C.c_void_p(self._ret_ptrs[which].data_ptr()), self.world, self.experts_per_rank * self.world, self.hidden, self.capacity,
