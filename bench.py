@@ -71,24 +71,58 @@ def make_inputs(m: int, device, with_payload=True):
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    """nvidia-smi clocks / throttle reasons, one sample every 100 ms, each stamped on arrival.
+
+    The sampler is started before the warm-up so that it is already delivering when the timed region begins;
+    ``begin()`` / ``end()`` mark the timed region and only samples that arrived while the load was running are
+    summarised.  A timed region shorter than a few sampling periods is followed by ``extend(step)``: the same step
+    keeps running, untimed, until at least ``MIN_SAMPLES`` samples have been taken under that load."""
 
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    MIN_SAMPLES = 3
 
     def __init__(self, gpu_index: int):
         self.gpu_index = gpu_index
         self.proc = None
-        self.path = None
+        self.rows = []                  # (arrival time, fields)
+        self.t_begin = self.t_end = None
+        self.extra_steps = 0
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            fields = [f.strip() for f in line.split(",")]
+            if len(fields) >= 9:
+                self.rows.append((time.monotonic(), fields))
 
     def start(self):
         try:
-            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
-            self.path = f.name
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.gpu_index), "-lms", "200"], stdout=f, stderr=subprocess.DEVNULL)
+                                          "-i", str(self.gpu_index), "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
         except Exception:
             self.proc = None
+
+    def begin(self):
+        self.t_begin = time.monotonic()
+
+    def end(self):
+        self.t_end = time.monotonic()
+
+    def _under_load(self):
+        return [f for (t, f) in self.rows if self.t_begin is not None and t >= self.t_begin and (self.t_end is None or t <= self.t_end)]
+
+    def extend(self, step, sync, limit_s: float = 4.0):
+        """Keep the load of the timed region running (untimed) until enough samples were taken under it."""
+        if self.proc is None or len(self._under_load()) >= self.MIN_SAMPLES:
+            return
+        self.t_end = None
+        t0 = time.monotonic()
+        while len(self._under_load()) < self.MIN_SAMPLES and time.monotonic() - t0 < limit_s:
+            step()
+            sync()
+            self.extra_steps += 1
+        self.t_end = time.monotonic()
 
     def stop(self) -> dict:
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
@@ -99,19 +133,19 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             pass
+        rows = self._under_load()
         try:
-            rows = [r.split(",") for r in Path(self.path).read_text().strip().splitlines() if r.strip()]
-            sm = [float(r[1]) for r in rows if len(r) >= 9]
+            sm = [float(r[1]) for r in rows]
             names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
             reasons = set()
             for r in rows:
-                if len(r) >= 9:
-                    for name, val in zip(names, r[5:9]):
-                        if val.strip().lower().startswith("active"):
-                            reasons.add(name)
+                for name, val in zip(names, r[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
             if sm:
-                out.update(sm_mhz=statistics.median(sm), sm_max_mhz=float(rows[0][2]), reasons=sorted(reasons), samples=len(sm))
-            os.unlink(self.path)
+                out.update(sm_mhz=statistics.median(sm), sm_max_mhz=float(rows[0][2]), reasons=sorted(reasons), samples=len(sm),
+                           power_w=statistics.median(float(r[3]) for r in rows),
+                           window="timed region" + (f" + {self.extra_steps} identical untimed steps run directly after it" if self.extra_steps else ""))
         except Exception:
             pass
         return out
@@ -227,16 +261,16 @@ def run_moe(args) -> int:
         dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     for _ in range(max(3, args.warmup)):
         step()
     barrier()
     ops.check_status()
     _lib.COUNT_LAUNCHES, _lib.LAUNCHES = True, 0
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-        time.sleep(0.25)
     barrier()
+    sampler.begin()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     torch.cuda.profiler.start()                   # `ncu --profile-from-start off` then sees only the timed steps (all threads)
@@ -246,10 +280,13 @@ def run_moe(args) -> int:
     torch.cuda.profiler.stop()
     e1.record()
     barrier()
+    sampler.end()
     ms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     launches = _lib.LAUNCHES
     _lib.COUNT_LAUNCHES = False
+    if world == 1:
+        sampler.extend(step, torch.cuda.synchronize)        # (a multi-rank step holds collectives: never run it on one rank alone)
     clocks = sampler.stop() if rank == 0 else {}
     ops.check_status()
     if rank == 0:
@@ -346,6 +383,9 @@ def main() -> int:
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     for _ in range(max(3, args.warmup)):
         step(x_dev, dys_dev)
     torch.cuda.synchronize()
@@ -356,11 +396,8 @@ def main() -> int:
     _lib.LAUNCHES = 0
     _lib.TIMED = {"b2g_qlinear_fwd"}
     _lib.EVENTS.clear()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-        time.sleep(0.25)
     barrier()
+    sampler.begin()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     torch.cuda.profiler.start()                   # `ncu --profile-from-start off` then sees only the timed steps (all threads)
@@ -370,10 +407,13 @@ def main() -> int:
     torch.cuda.profiler.stop()
     e1.record()
     barrier()
+    sampler.end()
     ms_total = e0.elapsed_time(e1)
     launches = _lib.LAUNCHES
     _lib.COUNT_LAUNCHES = False
     _lib.TIMED = set()
+    if rank == 0:
+        sampler.extend(lambda: step(x_dev, dys_dev), torch.cuda.synchronize)    # replicas are independent: rank 0 may run on alone
     clocks = sampler.stop() if rank == 0 else {}
     ops.check_status()
 

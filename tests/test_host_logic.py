@@ -97,3 +97,29 @@ def test_oracle_routing_reference_is_stable_and_consistent():
     assert plan["group_sizes"].tolist() == [1, 3, 0, 2] and plan["offsets"].tolist() == [1, 4, 4, 6]
     logits = torch.zeros(2, 256)
     assert moe_ref.router_topk(logits, 8).tolist() == [list(range(8))] * 2  # ties -> smaller id
+
+
+def test_bench_clock_sampler_reads_samples_under_load(tmp_path, monkeypatch):
+    """The bench's clock sampler against a fake `nvidia-smi` (a script printing one CSV row every 20 ms): only rows that
+    arrive while the load runs are summarised, and a too-short timed region is extended by untimed steps."""
+    import os
+    import stat
+    import time
+
+    import bench
+
+    fake = tmp_path / "nvidia-smi"
+    fake.write_text("#!/bin/sh\nwhile true; do echo '0, 1905, 1965, 801.5, 0x4, Not Active, Not Active, Not Active, Active'; sleep 0.02; done\n")
+    fake.chmod(fake.stat().st_mode | stat.S_IEXEC)
+    monkeypatch.setenv("PATH", f"{tmp_path}{os.pathsep}{os.environ['PATH']}")
+    s = bench.ClockSampler(0)
+    s.start()
+    time.sleep(0.1)
+    s.begin()
+    s.end()                                             # a timed region too short for any sample
+    steps = []
+    s.extend(lambda: (steps.append(1), time.sleep(0.01)), lambda: None)
+    out = s.stop()
+    assert out["samples"] >= bench.ClockSampler.MIN_SAMPLES and steps
+    assert out["sm_mhz"] == 1905 and out["sm_max_mhz"] == 1965 and out["reasons"] == ["sw_power_cap"]
+    assert "untimed" in out["window"]
