@@ -21,7 +21,7 @@
 // shared memory.  The LoRA up-projection is one extra K=16 MMA per row block on 32-byte-swizzled tiles.
 //
 // Warp roles (736 threads per CTA): 0 = activation / LoRA tile producer (TMA), 1 = MMA issuer (first CTA of the
-// pair only) + TMEM owner, 2-5 = epilogue (TMEM -> registers -> global), 6-21 = unpack in four groups that take
+// pair only) + TMEM owner, 2-5 = epilogue (TMEM -> registers -> 32-byte global stores), 6-21 = unpack in four groups that take
 // reduction steps round-robin (four steps in flight), 22 = packed-weight producer (TMA).  Barriers that gate the MMA
 // (A / B / LoRA tiles ready, accumulator drained) live in the first CTA and collect arrivals from both;
 // barriers that release buffers are signalled in both CTAs by tcgen05.commit.  No TMA multicast is used:
@@ -53,8 +53,6 @@ constexpr int kThreads = 32 * (7 + kUnpackWarps);  // + A producer, MMA, 4 epilo
 constexpr int kLoraATile = kBM * 32;        // [128 x 16] bf16
 constexpr int kLoraBTile = kBNh * 32;       // 4096 either way
 constexpr int kTmemCols = 512;
-constexpr int kEpiRowBytes = 64;            // 32 bf16: the dense [32 rows x 32 columns] box of a bulk tensor store
-constexpr int kEpiBufBytes = 32 * kEpiRowBytes;
 
 // Packed-stage geometry: what one reduction step needs of the packed weight in ONE CTA, as TMA boxes over
 // the payload viewed as uint32 [rows, pitch/4].  x coordinates are always multiples of 4 words (16 bytes).
@@ -90,9 +88,7 @@ struct Cfg {
   static constexpr int kOffP = kOffB + kBStages * kBStage;
   static constexpr int kOffLA = kOffP + kPStages * kPStage;
   static constexpr int kOffLB = kOffLA + kMT * kLoraATile;
-  static constexpr int kEpiBufs = P::kBytes <= 9216 ? 2 : 1;                // staging buffers per epilogue warp
-  static constexpr int kOffEpi = kOffLB + kLoraBTile;                       // 4 epilogue warps x kEpiBufs x [32 rows x 64 B]
-  static constexpr int kOffGrid = kOffEpi + 4 * kEpiBufs * kEpiBufBytes;    // IQ2_XXS table (2 KB)
+  static constexpr int kOffGrid = kOffLB + kLoraBTile;                      // IQ2_XXS table (2 KB)
   static constexpr int kOffBar = kOffGrid + (QT == B2G_IQ2_XXS ? 2048 : 0);
   static constexpr int kNumBars = 2 * kAStages + 2 * kBStages + 2 * kPStages + 2 + 2;
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;                   // tmem slot, abort flag
@@ -119,6 +115,7 @@ struct Params {
   const __nv_bfloat16* bias;
   const uint2* grid;  // IQ2_XXS table in global memory
   int* status;
+  int wide_ok;        // output rows and row segments start on 32-byte boundaries
 };
 
 struct Tile { int expert, row0, rows, ct; };
@@ -278,12 +275,64 @@ __device__ __forceinline__ void unpack_half(const uint8_t* pk, int row, int pair
   }
 }
 
+__device__ __forceinline__ void st_global_v8(void* dst, const uint32_t (&w)[16], int o) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(w[o]), "r"(w[o + 1]), "r"(w[o + 2]), "r"(w[o + 3]),
+               "r"(w[o + 4]), "r"(w[o + 5]), "r"(w[o + 6]), "r"(w[o + 7])
+               : "memory");
+}
+
+// Drain one TMEM lane quarter (32 rows per row block of this CTA) of a finished tile.  A TMEM load gives each lane 32
+// consecutive accumulators of ONE output row: (+ bias) -> bf16 -> two 32-byte stores, whole sectors, straight from
+// registers.  (Staging through shared memory for wider row segments, by hand or by bulk tensor stores, and keeping the
+// next chunk's TMEM load in flight in a second register set all measured slower here.)
+template <int MODE>
+__device__ __forceinline__ void drain_tile(const Params& p, const Tile& t, uint32_t tmem_base, int rank, int q, int lane) {
+  const int nmt = t.rows > kPairRows ? 2 : 1;
+  int seg = 0, col0;
+  if (MODE == kFwd) { seg = t.ct / p.ct_per_seg; col0 = (t.ct - seg * p.ct_per_seg) * kBN; }
+  else col0 = t.ct * kBN;
+  const int ncols = MODE == kFwd ? p.n : p.k;
+  __nv_bfloat16* outp = seg ? p.out1 : p.out0;
+  const uint32_t acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+  for (int m = 0; m < nmt; ++m) {
+    const int row_first = m * kPairRows + rank * kBM + q * 32;
+    if (row_first >= t.rows) break;              // uniform across the warp
+    const bool row_ok = row_first + lane < t.rows;   // rows past a ragged expert segment belong to someone else
+    __nv_bfloat16* orow = outp + static_cast<int64_t>(t.row0 + row_first + lane) * p.ldc;
+#pragma unroll 1
+    for (int c = 0; c < kBN / 32; ++c) {
+      const int cbase = col0 + c * 32;
+      if (cbase >= ncols) break;
+      uint32_t r[32];
+      dev::tmem_ld_32x32(acc + m * kBN + c * 32, r);
+      dev::tmem_ld_wait();
+      if (MODE == kFwd && p.bias) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (cbase + i < ncols) r[i] = __float_as_uint(__uint_as_float(r[i]) + __bfloat162float(p.bias[cbase + i]));
+      }
+      if (!row_ok) continue;
+      __nv_bfloat16* dst = orow + cbase;
+      if (p.wide_ok && cbase + 32 <= ncols) {
+        uint32_t w[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) w[i] = dev::pack_bf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+        st_global_v8(dst, w, 0);
+        st_global_v8(dst + 16, w, 8);
+      } else {                                   // odd row pitch or the ragged last columns: element stores
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (cbase + i < ncols) dst[i] = __float2bfloat16_rn(__uint_as_float(r[i]));
+      }
+    }
+  }
+}
+
 template <int QT, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_a1,
              const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1,
-             const __grid_constant__ CUtensorMap tm_la, const __grid_constant__ CUtensorMap tm_lb,
-             const __grid_constant__ CUtensorMap tm_o0, const __grid_constant__ CUtensorMap tm_o1) {
+             const __grid_constant__ CUtensorMap tm_la, const __grid_constant__ CUtensorMap tm_lb) {
   using C = Cfg<QT, MODE>;
   using P = Packed<QT, MODE>;
   extern __shared__ uint8_t smem_raw[];
@@ -429,100 +478,18 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
     // ============================== epilogue ==============================
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     int pacc = 0;
-    int nstore = 0;          // bulk stores issued by this warp (selects the staging buffer)
     bool ok = true;
     for (int item = pair; item < total_items && ok; item += num_pairs) {
       const Tile t = get_tile(p, item);
-      const int nmt = t.rows > kPairRows ? 2 : 1;
-      int seg = 0, col0;
-      if (MODE == kFwd) { seg = t.ct / p.ct_per_seg; col0 = (t.ct - seg * p.ct_per_seg) * kBN; }
-      else col0 = t.ct * kBN;
-      const int ncols = MODE == kFwd ? p.n : p.k;
-      __nv_bfloat16* outp = seg ? p.out1 : p.out0;
       ok = dev::mbar_wait(bar(kAccFull), pacc, abort_flag, p.status, 301);
       if (!ok) break;
       dev::tc_fence_after();
-      const uint32_t acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-      const bool vec_ok = (p.ldc & 7) == 0;
-      const CUtensorMap* om = seg ? &tm_o1 : &tm_o0;
-      for (int m = 0; m < nmt; ++m) {
-        const int row_first = m * kPairRows + static_cast<int>(rank) * kBM + q * 32;   // first of this warp's 32 rows
-        const int rows_here = t.rows - row_first;                                      // how many of them exist
-        const int row_local = row_first + lane;
-        const bool row_ok = row_local < t.rows;
-        __nv_bfloat16* orow = outp + static_cast<int64_t>(t.row0 + row_local) * p.ldc;
-#pragma unroll 1
-        for (int c = 0; c < kBN / 32; ++c) {
-          uint32_t r[32];
-          dev::tmem_ld_32x32(acc + m * kBN + c * 32, r);
-          dev::tmem_ld_wait();
-          const int cbase = col0 + c * 32;
-          if (cbase >= ncols || rows_here <= 0) continue;      // uniform across the warp
-          if (MODE == kFwd && p.bias) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (cbase + i < ncols) r[i] = __float_as_uint(__uint_as_float(r[i]) + __bfloat162float(p.bias[cbase + i]));
-          }
-          if (!vec_ok) {                                       // odd row pitch: element stores
-            if (row_ok) {
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (cbase + i < ncols) orow[cbase + i] = __float2bfloat16_rn(__uint_as_float(r[i]));
-            }
-            continue;
-          }
-          // own row -> staging buffer (lane = row).  The buffer was last read by the bulk store issued kEpiBufs chunks ago.
-          uint8_t* stage = smem + C::kOffEpi + (q * C::kEpiBufs + (nstore % C::kEpiBufs)) * kEpiBufBytes;
-          if (lane == 0) dev::bulk_wait_read<C::kEpiBufs - 1>();
-          __syncwarp();
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint4 o;
-            o.x = dev::pack_bf16(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
-            o.y = dev::pack_bf16(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-            o.z = dev::pack_bf16(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-            o.w = dev::pack_bf16(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-            *reinterpret_cast<uint4*>(stage + lane * kEpiRowBytes + 16 * v) = o;
-          }
-          if (rows_here >= 32) {
-            // all 32 rows belong to this tile: one asynchronous bulk store (columns past the tensor edge are clipped),
-            // which drains while the next chunks and the next tile proceed
-            dev::fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              dev::tma_store_2d(om, dev::smem_u32(stage), cbase, t.row0 + row_first);
-              dev::bulk_commit();
-            }
-            ++nstore;
-          } else {
-            // ragged end of an expert segment: rows past it belong to someone else, store the valid ones by hand
-            __syncwarp();
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int rr = (lane >> 2) + 8 * i;
-              const int cc = cbase + 8 * (lane & 3);
-              if (rr < rows_here && cc < ncols) {
-                const uint4 o = *reinterpret_cast<const uint4*>(stage + rr * kEpiRowBytes + 16 * (lane & 3));
-                if (cc + 8 <= ncols) {
-                  *reinterpret_cast<uint4*>(outp + static_cast<int64_t>(t.row0 + row_first + rr) * p.ldc + cc) = o;
-                } else {
-                  const uint32_t w[4] = {o.x, o.y, o.z, o.w};
-                  __nv_bfloat16* dst = outp + static_cast<int64_t>(t.row0 + row_first + rr) * p.ldc + cc;
-                  for (int e2 = 0; e2 < 8 && cc + e2 < ncols; ++e2)
-                    dst[e2] = __ushort_as_bfloat16(static_cast<unsigned short>((w[e2 >> 1] >> (16 * (e2 & 1))) & 0xFFFFu));
-                }
-              }
-            }
-            __syncwarp();
-          }
-        }
-      }
+      drain_tile<MODE>(p, t, tmem_base, static_cast<int>(rank), q, lane);
       dev::tc_fence_before();
       __syncwarp();
       if (lane == 0) dev::mbar_arrive_cluster(lead_acc_empty);
       pacc ^= 1;
     }
-    if (lane == 0) dev::bulk_wait_all();   // staging buffers are read until the last bulk store completes
   } else if (warp == 6 + kUnpackWarps) {
     // ============================== packed-weight producer ==============================
     if (lane == 0) {
@@ -666,6 +633,7 @@ int launch_impl(const Launch& L) {
   p.out1 = static_cast<__nv_bfloat16*>(L.out1);
   p.bias = static_cast<const __nv_bfloat16*>(L.bias);
   p.status = L.status;
+  p.wide_ok = (p.ldc % 16 == 0) && (reinterpret_cast<uintptr_t>(L.out0) % 32 == 0) && (reinterpret_cast<uintptr_t>(L.out1) % 32 == 0);
   p.grid = nullptr;
   if (QT == B2G_IQ2_XXS) {
     int rc = iq2xxs_grid(&p.grid);
@@ -700,15 +668,6 @@ int launch_impl(const Launch& L) {
     }
   }
 
-  CUtensorMap tm_o0 = tm_a0, tm_o1 = tm_a0;
-  if ((p.ldc & 7) == 0) {   // bulk stores need a 16-byte row pitch; odd widths take the element-store path
-    const uint64_t ocols = MODE == kFwd ? (uint64_t)p.n : (uint64_t)p.k;
-    if ((rc = make_tmap_2d(&tm_o0, L.out0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ocols, L.m_total, (uint64_t)p.ldc * 2, 32, 32,
-                           CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
-    tm_o1 = tm_o0;
-    if (L.out1 && (rc = make_tmap_2d(&tm_o1, L.out1, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ocols, L.m_total, (uint64_t)p.ldc * 2, 32, 32,
-                                     CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
-  }
   auto kern = qgemm_kernel<QT, MODE>;
   B2G_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
   int pairs = sm_count() / 2;
@@ -729,7 +688,7 @@ int launch_impl(const Launch& L) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  B2G_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p, tm_a0, tm_a1, tm_w0, tm_w1, tm_la, tm_lb, tm_o0, tm_o1));
+  B2G_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p, tm_a0, tm_a1, tm_w0, tm_w1, tm_la, tm_lb));
   return 0;
 }
 
