@@ -140,6 +140,27 @@ def test_linearity_at_full_width(cuda):
     del exact_sum
 
 
+def test_full_width_every_element_repeated(cuda):
+    """Every output element of a config-sized product (M=8192, N=4096, K=2048) against the product with the exactly
+    dequantised weight, three runs in a row, forward and input gradient.  A norm hides a few hundred wrong elements;
+    a hand-off race between the warp roles of the kernel shows up exactly so: in some runs, in some tiles."""
+    from b2g import gguf_quant, ops
+
+    g = torch.Generator(device=cuda).manual_seed(3)
+    n, k, m = 4096, 2048, 8192
+    payload = gguf_quant.random_payload(12, (n, k), 4, device=cuda).reshape(-1)
+    w = ops.dequantize(payload, 12, (n, k)).float()
+    x = torch.randn(m, k, generator=g, device=cuda).bfloat16()
+    dy = torch.randn(m, n, generator=g, device=cuda).bfloat16()
+    ref_y, ref_dx = x.float() @ w.t(), dy.float() @ w
+    for _ in range(3):
+        y = ops.qlinear_fwd(x, payload, 12, n).float()
+        dx = ops.qlinear_dgrad(dy, payload, 12, k).float()
+        for got, ref in ((y, ref_y), (dx, ref_dx)):
+            bad = (got - ref).abs() > 0.02 * ref.abs() + 0.02 * float(ref.abs().mean())
+            assert int(bad.sum()) == 0, f"{int(bad.sum())} elements off, first at {bad.nonzero()[0].tolist()}"
+
+
 def test_fail_closed_arguments(cuda):
     from b2g import autograd as ag, ops
 

@@ -47,8 +47,8 @@ constexpr int kBStages = 4;
 constexpr int kUnpackWarps = 16;
 constexpr int kUnpackGroups = 4;            // groups take reduction steps round-robin, so four steps are unpacked concurrently
 constexpr int kGroupWarps = kUnpackWarps / kUnpackGroups;
-constexpr int kGroupThreads = 32 * kGroupWarps;   // 128 threads x 2 items = 256 (row, half) items of one step
-constexpr int kItemsPerThread = 256 / kGroupThreads;
+constexpr int kGroupThreads = 32 * kGroupWarps;   // 128 threads: one 64-value slice of a W row each
+static_assert(kGroupThreads == 128, "the unpack mapping assumes 128 threads per group");
 constexpr int kThreads = 32 * (7 + kUnpackWarps);  // + A producer, MMA, 4 epilogue, packed-weight producer
 constexpr int kLoraATile = kBM * 32;        // [128 x 16] bf16
 constexpr int kLoraBTile = kBNh * 32;       // 4096 either way
@@ -191,12 +191,12 @@ __device__ __forceinline__ void q8_half(const uint32_t (&w)[17], int half, uint3
 
 // Read `N` words starting at byte offset `off` (a multiple of 4, < 16) of a 16-byte aligned row.
 template <int N>
-__device__ __forceinline__ void load_words_shifted(const uint8_t* row16, int off, uint32_t (&w)[N]) {
+__device__ __forceinline__ void load_words_shifted(uint32_t row16, int off, uint32_t (&w)[N]) {
   constexpr int kVec = (N + 3 + 3) / 4;  // enough 16-byte vectors for any shift
   uint32_t raw[kVec * 4];
 #pragma unroll
   for (int v = 0; v < kVec; ++v) {
-    const uint4 q = *reinterpret_cast<const uint4*>(row16 + 16 * v);
+    const uint4 q = dev::lds128(row16 + 16 * v);
     raw[4 * v] = q.x; raw[4 * v + 1] = q.y; raw[4 * v + 2] = q.z; raw[4 * v + 3] = q.w;
   }
   const int s = off >> 2;  // warp-uniform
@@ -216,11 +216,11 @@ __device__ __forceinline__ void load_words_shifted(const uint8_t* row16, int off
 }
 
 // IQ2_XXS: one 8-byte group (32 values): four grid-row indices and the sign/scale word.
-__device__ __forceinline__ void iq2_half(float d, uint32_t idx4, uint32_t word, const uint2* __restrict__ grid_s, uint32_t (&out)[16]) {
+__device__ __forceinline__ void iq2_half(float d, uint32_t idx4, uint32_t word, uint32_t grid_s, uint32_t (&out)[16]) {
   const float db = __fmul_rn(__fmul_rn(d, 0.5f + static_cast<float>(word >> 28)), 0.25f);
 #pragma unroll
   for (int s = 0; s < 4; ++s) {
-    const uint2 mag = grid_s[(idx4 >> (8 * s)) & 255u];
+    const uint2 mag = dev::lds64(grid_s + (((idx4 >> (8 * s)) & 255u) << 3));
     const uint32_t sg = fmt::iq2_sign_byte((word >> (7 * s)) & 127u);
     float v[8];
 #pragma unroll
@@ -235,44 +235,54 @@ __device__ __forceinline__ void iq2_half(float d, uint32_t idx4, uint32_t word, 
   }
 }
 
-// Unpack the 32 values this thread owns for reduction step `it` from packed stage `pk`.
-//   forward: thread = (one of this CTA's 128 W rows, half); the step selects which 64 of the row's values
-//   dgrad  : thread = (W row 0..63, 64-value quarter `pair` (0..3) of the 256-value column tile `ct`, half)
+// What one unpack thread needs of a packed stage, held in registers: both 32-value halves of its 64-value slice of
+// one W row come from the same packed bytes, so they are read from shared memory once.
+//   forward: thread = one of this CTA's 128 W rows; the step selects which 64 of the row's values
+//   dgrad  : thread = (W row 0..63, which 64 (`pair`, 0..3) of the 256-value column tile `ct`)
+template <int QT> struct RowData;
+template <> struct RowData<B2G_Q4_K> { uint4 hdr, qa, qb; };
+template <> struct RowData<B2G_Q8_0> { uint32_t w[17]; };
+template <> struct RowData<B2G_IQ2_XXS> { float d; uint32_t idx4[2], word[2]; };
+
 template <int QT, int MODE>
-__device__ __forceinline__ void unpack_half(const uint8_t* pk, int row, int pair, int half, int it, int ct, const uint2* grid_s,
-                                            uint32_t (&out)[16]) {
+__device__ __forceinline__ void load_row(uint32_t pk, int row, int pair, int it, int ct, RowData<QT>& rd) {
   if constexpr (QT == B2G_Q4_K) {
     if constexpr (MODE == kFwd) {
-      const uint4 hdr = *reinterpret_cast<const uint4*>(pk + row * 16);
-      const uint4 qa = *reinterpret_cast<const uint4*>(pk + 2048 + row * 16);
-      const uint4 qb = *reinterpret_cast<const uint4*>(pk + 4096 + row * 16);
-      q4k_half(hdr, qa, qb, pair, half, out);
+      rd.hdr = dev::lds128(pk + row * 16);
+      rd.qa = dev::lds128(pk + 2048 + row * 16);
+      rd.qb = dev::lds128(pk + 4096 + row * 16);
     } else {
-      const uint8_t* r = pk + row * 144;
-      const uint4 hdr = *reinterpret_cast<const uint4*>(r);
-      const uint4 qa = *reinterpret_cast<const uint4*>(r + 16 + 32 * pair);
-      const uint4 qb = *reinterpret_cast<const uint4*>(r + 32 + 32 * pair);
-      q4k_half(hdr, qa, qb, pair, half, out);
+      const uint32_t r = pk + row * 144;
+      rd.hdr = dev::lds128(r);
+      rd.qa = dev::lds128(r + 16 + 32 * pair);
+      rd.qb = dev::lds128(r + 32 + 32 * pair);
     }
   } else if constexpr (QT == B2G_Q8_0) {
-    uint32_t w[17];
-    if constexpr (MODE == kFwd) load_words_shifted<17>(pk + row * 80, (68 * it) & 15, w);
+    if constexpr (MODE == kFwd) load_words_shifted<17>(pk + row * 80, (68 * it) & 15, rd.w);
     else {
       const int byte0 = ((136 * (pair >> 1)) & 15) + 68 * (pair & 1);  // two blocks of column quarter `pair` inside the 144-byte window
-      load_words_shifted<17>(pk + row * 144 + (byte0 & ~15), byte0 & 15, w);
+      load_words_shifted<17>(pk + row * 144 + (byte0 & ~15), byte0 & 15, rd.w);
     }
-    q8_half(w, half, out);
   } else {
     // 66-byte super-block inside an 80-byte window; `off` (even) is where it starts.
     const int sb = MODE == kFwd ? (it >> 2) : ct;
     const int off = (66 * sb) & 15;
-    const unsigned short* h = reinterpret_cast<const unsigned short*>(pk + row * 80 + off);
-    const float d = dev::half_bits_to_float(h[0]);
-    const unsigned short* q = h + 1 + 8 * pair + 4 * half;  // this thread's 8-byte group
-    const uint32_t idx4 = static_cast<uint32_t>(q[0]) | (static_cast<uint32_t>(q[1]) << 16);
-    const uint32_t word = static_cast<uint32_t>(q[2]) | (static_cast<uint32_t>(q[3]) << 16);
-    iq2_half(d, idx4, word, grid_s, out);
+    const uint32_t h = pk + row * 80 + off;
+    rd.d = dev::half_bits_to_float(dev::lds16(h));
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const uint32_t q = h + 2 + 16 * pair + 8 * half;  // 8-byte group of this half (2-byte aligned)
+      rd.idx4[half] = dev::lds16(q) | (dev::lds16(q + 2) << 16);
+      rd.word[half] = dev::lds16(q + 4) | (dev::lds16(q + 6) << 16);
+    }
   }
+}
+
+template <int QT>
+__device__ __forceinline__ void decode_half(const RowData<QT>& rd, int pair, int half, uint32_t grid_s, uint32_t (&out)[16]) {
+  if constexpr (QT == B2G_Q4_K) q4k_half(rd.hdr, rd.qa, rd.qb, pair, half, out);
+  else if constexpr (QT == B2G_Q8_0) q8_half(rd.w, half, out);
+  else iq2_half(rd.d, rd.idx4[half], rd.word[half], grid_s, out);
 }
 
 __device__ __forceinline__ void st_global_v8(void* dst, const uint32_t (&w)[16], int o) {
@@ -535,7 +545,7 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
     const int tid = threadIdx.x - 6 * 32;
     const int group = tid / kGroupThreads;     // this group unpacks steps group, group + 4, group + 8, ...
     const int tg = tid % kGroupThreads;
-    const uint2* grid_s = reinterpret_cast<const uint2*>(smem + C::kOffGrid);
+    const uint32_t grid_s = sbase + C::kOffGrid;
     bool ok = true;
     int n = 0;                                 // running count of reduction steps of this CTA
     for (int item = pair; item < total_items && ok; item += num_pairs) {
@@ -544,30 +554,31 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
         if ((n % kUnpackGroups) != group) continue;
         const int sp = n % C::kPStages, pp = (n / C::kPStages) & 1;
         const int sb = n % kBStages, pb = (n / kBStages) & 1;
-        ok = dev::mbar_wait(bar(kFullP + sp), pp, abort_flag, p.status, 401) &&
-             dev::mbar_wait(bar(kEmptyB + sb), pb ^ 1, abort_flag, p.status, 402);
+        ok = dev::mbar_wait(bar(kFullP + sp), pp, abort_flag, p.status, 401);
         if (!ok) break;
-        const uint8_t* pk = smem + C::kOffP + sp * C::kPStage;
-        uint8_t* bstage = smem + C::kOffB + sb * kBStage;
+        // one (row, column group) per thread: forward 128 rows, dgrad 64 rows x the two 64-column groups of this CTA
+        const int drow = MODE == kFwd ? tg : (tg & 63);
+        const int sub = MODE == kFwd ? 0 : (tg >> 6);                 // dgrad: which 64 of this CTA's 128 columns
+        const int pairsel = MODE == kFwd ? (it & 3) : (2 * static_cast<int>(rank) + sub);   // ... of the tile's 256
+        RowData<QT> rd;
+        load_row<QT, MODE>(sP + sp * C::kPStage, drow, pairsel, it, ct, rd);
+        ok = dev::mbar_wait(bar(kEmptyB + sb), pb ^ 1, abort_flag, p.status, 402);
+        if (!ok) break;
+        const uint32_t dst = sB + sb * kBStage + static_cast<uint32_t>(sub) * 8192u + static_cast<uint32_t>(drow) * 128u;
+        const uint32_t sw = static_cast<uint32_t>(drow & 7);
 #pragma unroll
-        for (int j = 0; j < kItemsPerThread; ++j) {
-          // 256 (row, half) items per step: forward 128 rows x 2 halves, dgrad 64 rows x 2 column quarters x 2 halves
-          const int idx = tg + kGroupThreads * j;
-          const int half = idx >> 7;                                  // uniform across a warp
-          const int drow = MODE == kFwd ? (idx & 127) : (idx & 63);
-          const int sub = MODE == kFwd ? 0 : ((idx >> 6) & 1);        // dgrad: which 64 of this CTA's 128 columns
-          const int quarter = 2 * static_cast<int>(rank) + sub;       // ... = which 64 of the tile's 256 columns
+        for (int half = 0; half < 2; ++half) {
           uint32_t out[16];
-          unpack_half<QT, MODE>(pk, drow, MODE == kFwd ? (it & 3) : quarter, half, it, ct, grid_s, out);
-          uint8_t* dst = bstage + static_cast<uint32_t>(sub) * 8192u + static_cast<uint32_t>(drow) * 128u;
-          const uint32_t sw = static_cast<uint32_t>(drow & 7);
+          decode_half<QT>(rd, pairsel, half, grid_s, out);
 #pragma unroll
           for (int c = 0; c < 4; ++c)
-            *reinterpret_cast<uint4*>(dst + ((static_cast<uint32_t>(4 * half + c) ^ sw) << 4)) =
-                make_uint4(out[4 * c], out[4 * c + 1], out[4 * c + 2], out[4 * c + 3]);
+            dev::sts128(dst + ((static_cast<uint32_t>(4 * half + c) ^ sw) << 4), out[4 * c], out[4 * c + 1], out[4 * c + 2], out[4 * c + 3]);
         }
         dev::fence_proxy_async_smem();
         __syncwarp();
+        // The proxy fence above also covers the packed slot: its bytes were read through the generic proxy and the refill
+        // is a TMA (async proxy) write.  Handing the slot back right after the loads, without a fence in between, let the
+        // refill overtake the reads.
         if (lane == 0) {
           dev::mbar_arrive(bar(kEmptyP + sp));
           dev::mbar_arrive_cluster(lead_full_b + 8u * sb);
