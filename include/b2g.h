@@ -71,6 +71,20 @@ B2G_API int b2g_qlinear_fwd(int qtype, const void* x, const void* payload, const
 B2G_API int b2g_qlinear_dgrad(int qtype, const void* dy, const void* payload, const void* dybs, const void* lora_a16,
                       void* dx, int64_t M, int64_t N, int64_t K, int* status, void* stream);
 
+/* Fixed groups: Y[M,g,:] = X[M,g,:] . deq(W_g[N,K])^T for g < groups, with X [M, groups, K], the payload
+ * [groups, N, row bytes] and Y [M, groups, N] all contiguous: `groups` independent dense products that read and write
+ * column blocks of the shared tensors in place (no per-group copies), each the same kernel and the same arithmetic as
+ * b2g_qlinear_fwd on a contiguous slice.  Replaces torch_ggml_ops.fixed_grouped_mmq(input[...,8,4096],
+ * payload[8,1024,.]) of DeepSeek's frozen eight-group Q8_0 o_a_proj (deepseek_v4_lora.py:123); the group count, widths
+ * and quant type are not fixed here (any type of this library, widths multiples of 16). */
+B2G_API int b2g_fixed_grouped_fwd(int qtype, const void* x, const void* payload, void* y, int64_t M, int groups, int64_t N,
+                          int64_t K, int* status, void* stream);
+
+/* dX[M,g,:] = dY[M,g,:] . deq(W_g[N,K]): the registered autograd of fixed_grouped_mmq (the reference checks it
+ * against per-group mmq_grad_input, test_deepseek_v4_lora.py:101-152). */
+B2G_API int b2g_fixed_grouped_dgrad(int qtype, const void* dy, const void* payload, void* dx, int64_t M, int groups, int64_t N,
+                            int64_t K, int* status, void* stream);
+
 /* Skinny projection onto the LoRA rank: P[M,r] = X[M,C] . W^T with W given as [r,C] (w_is_cr = 0,
  * lora_A for X.A^T) or as [C,r] (w_is_cr = 1, lora_B for dY.B); r <= 16.
  * Writes out_plain[M,16] = bf16(P) and out_scaled[M,16] = bf16(scale*P), zero in columns >= r

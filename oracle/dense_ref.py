@@ -57,3 +57,19 @@ def rel_l2(actual: torch.Tensor, expected: torch.Tensor) -> float:
     e = expected.detach().double().cpu()
     den = float(e.norm())
     return float((a - e).norm()) / (den if den > 0 else 1.0)
+
+
+def fixed_grouped(x: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+    """Oracle of the fixed-group projection: ``x [..., G, K]``, dequantised ``weights [G, N, K]`` -> ``[..., G, N]`` in
+    fp32, each group an independent ``F.linear`` on its slice -- the expression the reference's own check builds from
+    per-group ``mmq`` calls (``test_deepseek_v4_lora.py:128-141``)."""
+    groups = weights.shape[0]
+    cols = [torch.nn.functional.linear(x[..., g, :].float(), weights[g].float()) for g in range(groups)]
+    return torch.stack(cols, dim=-2)
+
+
+def fixed_grouped_grad_input(dy: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+    """Input gradient of ``fixed_grouped``: ``dy [..., G, N]`` -> ``[..., G, K]``."""
+    groups = weights.shape[0]
+    cols = [dy[..., g, :].float() @ weights[g].float() for g in range(groups)]
+    return torch.stack(cols, dim=-2)

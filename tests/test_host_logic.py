@@ -123,3 +123,49 @@ def test_bench_clock_sampler_reads_samples_under_load(tmp_path, monkeypatch):
     assert out["samples"] >= bench.ClockSampler.MIN_SAMPLES and steps
     assert out["sm_mhz"] == 1905 and out["sm_max_mhz"] == 1965 and out["reasons"] == ["sw_power_cap"]
     assert "untimed" in out["window"]
+
+
+def test_deepseek_fixed_group_module_contract():
+    """configure_deepseek_v4_grouped_mmq (deepseek_v4_lora.py:128-162): patches matching frozen grouped projections, fails
+    closed on anything else, refuses grouped adapters; the operator has a Meta kernel with the reference's shapes."""
+    import deepseek_v4_lora as dsl
+    from b2g.gguf_types import GGUFGroupedLinear, GGUFQuantizedTensor
+
+    good = GGUFGroupedLinear(4096, 8192, 8)
+    good.weight = GGUFQuantizedTensor(torch.zeros(8192, 4352, dtype=torch.uint8), quant_type=8, logical_shape=(8192, 4096))
+    holder = torch.nn.Sequential(good)
+    assert dsl.configure_deepseek_v4_grouped_mmq(holder) == {"enabled": 1, "paths": ["0"]}
+    assert good._deepseek_v4_grouped_mmq_enabled and dsl.configure_deepseek_v4_grouped_mmq(holder)["enabled"] == 1
+    with pytest.raises(RuntimeError, match="contiguous|CUDA|cuda"):          # no CPU route behind the patched forward
+        good(torch.zeros(2, 8, 4096, dtype=torch.bfloat16))
+
+    small = GGUFGroupedLinear(32, 24, 4)
+    small.weight = GGUFQuantizedTensor(torch.zeros(24, 34, dtype=torch.uint8), quant_type=8, logical_shape=(24, 32))
+    with pytest.raises(RuntimeError, match="fixed eight-group"):
+        dsl.configure_deepseek_v4_grouped_mmq(small)
+    plain = GGUFGroupedLinear(4096, 8192, 8)
+    plain.weight = torch.zeros(8192, 4352, dtype=torch.uint8)
+    with pytest.raises(TypeError, match="not GGUF-quantized"):
+        dsl.configure_deepseek_v4_grouped_mmq(plain)
+    with pytest.raises(RuntimeError, match="grouped o_a_proj LoRA is unsupported"):
+        dsl._RejectedDeepseekV4GroupedLora(good, "default")
+
+    y = torch.ops.b2g.fixed_grouped_mmq(torch.empty(3, 2, 8, 4096, device="meta", dtype=torch.bfloat16),
+                                        torch.empty(8, 1024, 4352, device="meta", dtype=torch.uint8), 8)
+    assert tuple(y.shape) == (3, 2, 8, 1024)
+    dx = torch.ops.b2g.fixed_grouped_mmq_grad_input(torch.empty(5, 8, 1024, device="meta", dtype=torch.bfloat16),
+                                                    torch.empty(8, 1024, 4352, device="meta", dtype=torch.uint8), 8)
+    assert tuple(dx.shape) == (5, 8, 4096)
+
+
+def test_oracle_fixed_groups_equal_per_group_linear():
+    from oracle import dense_ref
+
+    g = torch.Generator().manual_seed(7)
+    x, w, dy = torch.randn(3, 4, 64, generator=g), torch.randn(4, 24, 64, generator=g), torch.randn(3, 4, 24, generator=g)
+    y = dense_ref.fixed_grouped(x, w)
+    for k in range(4):
+        assert torch.equal(y[:, k], x[:, k] @ w[k].t())
+    xr = x.clone().requires_grad_(True)
+    dense_ref.fixed_grouped(xr, w).backward(dy)
+    assert torch.allclose(xr.grad, dense_ref.fixed_grouped_grad_input(dy, w), atol=1e-5)

@@ -24,6 +24,8 @@ from . import ops
 _LIB = torch.library.Library("b2g", "DEF")
 _LIB.define("mmq(Tensor x, Tensor payload, int quant_type, int out_features) -> Tensor")
 _LIB.define("mmq_grad_input(Tensor grad_output, Tensor payload, int quant_type, int in_features) -> Tensor")
+_LIB.define("fixed_grouped_mmq(Tensor x, Tensor packed_groups, int quant_type) -> Tensor")
+_LIB.define("fixed_grouped_mmq_grad_input(Tensor grad_output, Tensor packed_groups, int quant_type) -> Tensor")
 _LIB.define("grouped_mmq(Tensor x, Tensor payload, Tensor expert_indices, Tensor expert_offsets, int quant_type, "
             "int out_features) -> Tensor")
 _LIB.define("grouped_mmq_grad_input(Tensor grad_output, Tensor payload, Tensor expert_indices, Tensor expert_offsets, "
@@ -101,6 +103,40 @@ def mmq(x: torch.Tensor, payload: torch.Tensor, quant_type: int, out_features: i
 
 def mmq_grad_input(grad_output: torch.Tensor, payload: torch.Tensor, quant_type: int, in_features: int) -> torch.Tensor:
     return torch.ops.b2g.mmq_grad_input(grad_output, payload, int(quant_type), int(in_features))
+
+
+# ---- fixed groups (DeepSeek's frozen eight-group o_a_proj) ------------------------------------------
+def _fixed_k(packed_groups, quant_type):
+    blk, nbytes = ops._BLOCK[int(quant_type)]
+    return packed_groups.shape[-1] // nbytes * blk
+
+
+_LIB.impl("fixed_grouped_mmq", lambda x, pg, q: ops.fixed_grouped_fwd(x, pg, q), "CUDA")
+_LIB.impl("fixed_grouped_mmq_grad_input", lambda g, pg, q: ops.fixed_grouped_dgrad(g, pg, q), "CUDA")
+_LIB.impl("fixed_grouped_mmq", lambda x, pg, q: x.new_empty(*x.shape[:-1], pg.shape[1]), "Meta")
+_LIB.impl("fixed_grouped_mmq_grad_input", lambda g, pg, q: g.new_empty(*g.shape[:-1], _fixed_k(pg, q)), "Meta")
+
+
+def _fixed_setup(ctx, inputs, output):
+    _, packed_groups, quant_type = inputs
+    ctx.save_for_backward(packed_groups)
+    ctx.quant_type = quant_type
+
+
+def _fixed_backward(ctx, grad):
+    (packed_groups,) = ctx.saved_tensors
+    return torch.ops.b2g.fixed_grouped_mmq_grad_input(grad.contiguous(), packed_groups, ctx.quant_type), None, None
+
+
+torch.library.register_autograd("b2g::fixed_grouped_mmq", _fixed_backward, setup_context=_fixed_setup)
+torch.library.register_autograd("b2g::fixed_grouped_mmq_grad_input", _no_double_backward)
+
+
+def fixed_grouped_mmq(x: torch.Tensor, packed_groups: torch.Tensor, quant_type: int = 8) -> torch.Tensor:
+    """``Y[..., g, :] = X[..., g, :] . deq(W_g)^T`` for a payload ``[G, N, row bytes]``: the operator behind DeepSeek's
+    frozen grouped projection (``torch_ggml_ops.fixed_grouped_mmq(input, packed_groups)``, ``deepseek_v4_lora.py:123``,
+    which fixes Q8_0; the type is a third, optional argument here).  Autograd gives the input gradient only."""
+    return torch.ops.b2g.fixed_grouped_mmq(x, packed_groups, int(quant_type))
 
 
 class _LoraQLinear(torch.autograd.Function):

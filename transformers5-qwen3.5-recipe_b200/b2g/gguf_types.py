@@ -19,7 +19,7 @@ from . import autograd as ag
 from . import ops
 
 try:  # the fork, when present
-    from transformers.integrations.gguf import ALL_GGUF_EXPERTS_FUNCTIONS, GGUFExperts, GGUFLinear  # type: ignore
+    from transformers.integrations.gguf import ALL_GGUF_EXPERTS_FUNCTIONS, GGUFExperts, GGUFGroupedLinear, GGUFLinear  # type: ignore
     from transformers.integrations.gguf_dequant import GGUFQuantizedTensor, dequantize_gguf_tensor  # type: ignore
 
     HAVE_FORK = True
@@ -73,6 +73,29 @@ except Exception:  # stock transformers, or none
             w = self.weight
             y = ag.mmq(x.to(self.compute_dtype), w.as_subclass(torch.Tensor), int(w.quant_type), self.out_features)
             return y if self.bias is None else y + self.bias.to(y.dtype)
+
+    class GGUFGroupedLinear(torch.nn.Module):
+        """Frozen packed projection in ``n_groups`` independent groups: ``[..., n_groups, in_features]`` ->
+        ``[..., n_groups, out_features / n_groups]``; ``weight`` is a GGUFQuantizedTensor holding the groups' rows one
+        after the other (``[out_features, row bytes]``).  The stock forward materialises every group's logical weight;
+        ``deepseek_v4_lora.configure_deepseek_v4_grouped_mmq`` replaces it with the native fixed-group product."""
+
+        def __init__(self, in_features: int, out_features: int, n_groups: int, device=None, dtype=None,
+                     compute_dtype: torch.dtype = torch.bfloat16) -> None:
+            super().__init__()
+            if out_features % n_groups:
+                raise ValueError(f"{out_features} output features do not divide into {n_groups} groups")
+            self.in_features, self.out_features, self.n_groups = in_features, out_features, n_groups
+            self.compute_dtype = compute_dtype
+            self.weight: Any = None
+            self.input_permutation = None
+            self.output_permutation = None
+
+        def forward(self, x: torch.Tensor) -> torch.Tensor:
+            w = self.weight
+            logical = dequantize_gguf_tensor(w, int(w.quant_type), self.compute_dtype)
+            grouped = logical.reshape(self.n_groups, self.out_features // self.n_groups, self.in_features)
+            return torch.einsum("...gk,gnk->...gn", x.to(self.compute_dtype), grouped).to(x.dtype)
 
     ALL_GGUF_EXPERTS_FUNCTIONS: dict[str, Callable[..., torch.Tensor]] = {}
 

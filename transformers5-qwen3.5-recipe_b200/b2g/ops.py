@@ -202,6 +202,50 @@ def qlinear_fwd(x: torch.Tensor, payload: torch.Tensor, qtype: int, n: int, bias
     return y
 
 
+def _fixed_group_geometry(a: torch.Tensor, payload: torch.Tensor, qtype: int, forward: bool):
+    """Shapes of the fixed-group product: activations [..., G, width] (contiguous), payload [G, N, row bytes]."""
+    _need(a, torch.bfloat16, "activation")
+    _need(payload, torch.uint8, "packed_groups")
+    if a.dim() < 2 or payload.dim() != 3:
+        raise ValueError("fixed groups need activations [..., G, width] and a payload [G, N, row bytes]")
+    if not a.is_contiguous():
+        raise RuntimeError("fixed-group products need a contiguous activation (no hidden copy is made)")
+    groups, n, row_bytes = payload.shape
+    if a.shape[-2] != groups:
+        raise ValueError(f"activation has {a.shape[-2]} groups, the payload {groups}")
+    block_values, block_bytes = _BLOCK[int(qtype)] if int(qtype) in NATIVE_QUANT_TYPES else (0, 0)
+    if not block_values:
+        raise ValueError(f"GGML type {qtype} is not supported natively (supported: 8 Q8_0, 12 Q4_K, 16 IQ2_XXS)")
+    if row_bytes % block_bytes:
+        raise ValueError(f"payload rows of {row_bytes} bytes are not whole blocks of type {qtype}")
+    k = row_bytes // block_bytes * block_values
+    width = a.shape[-1]
+    if width != (k if forward else n):
+        raise ValueError(f"activation width {width} does not match the payload ({k if forward else n} expected)")
+    _check_payload(payload, qtype, groups * n, k, "packed_groups")
+    m = a.numel() // (groups * width)
+    return m, groups, n, k
+
+
+def fixed_grouped_fwd(x: torch.Tensor, packed_groups: torch.Tensor, qtype: int) -> torch.Tensor:
+    """Y[..., g, :] = X[..., g, :] . deq(W_g)^T for every group, in place on column blocks (no per-group copies)."""
+    m, groups, n, k = _fixed_group_geometry(x, packed_groups, qtype, True)
+    y = torch.empty(*x.shape[:-1], n, dtype=torch.bfloat16, device=x.device)
+    with _DeviceCtx(x):
+        _lib.call("b2g_fixed_grouped_fwd", int(qtype), _p(x), _p(packed_groups), _p(y), m, groups, n, k, _p(status_word(x.device)), _stream(x))
+    return y
+
+
+def fixed_grouped_dgrad(dy: torch.Tensor, packed_groups: torch.Tensor, qtype: int) -> torch.Tensor:
+    """dX[..., g, :] = dY[..., g, :] . deq(W_g) for every group."""
+    m, groups, n, k = _fixed_group_geometry(dy, packed_groups, qtype, False)
+    dx = torch.empty(*dy.shape[:-1], k, dtype=torch.bfloat16, device=dy.device)
+    with _DeviceCtx(dy):
+        _lib.call("b2g_fixed_grouped_dgrad", int(qtype), _p(dy), _p(packed_groups), _p(dx), m, groups, n, k, _p(status_word(dy.device)),
+                  _stream(dy))
+    return dx
+
+
 def qlinear_dgrad(dy: torch.Tensor, payload: torch.Tensor, qtype: int, k: int,
                   dybs: Optional[torch.Tensor] = None, lora_a16: Optional[torch.Tensor] = None) -> torch.Tensor:
     _need(dy, torch.bfloat16, "dy")

@@ -606,6 +606,7 @@ struct Launch {
   const void *w0, *w1;        // payloads
   const void *la, *lb;        // LoRA operands
   int64_t m_total, n, k;
+  int64_t lda, ldc;           // row pitch (elements) of the activation operand / the output; 0 = contiguous
   int num_experts;
   const int32_t* tiles;       // nullptr = dense
   int64_t lora_rows;
@@ -628,13 +629,13 @@ int launch_impl(const Launch& L) {
     p.num_ct = p.nseg * p.ct_per_seg;
     p.num_iters = p.k / kBK;
     p.iters_per_seg = p.num_iters;
-    p.ldc = p.n;
+    p.ldc = L.ldc ? (int)L.ldc : p.n;
   } else {
     p.ct_per_seg = p.k / kBN;
     p.num_ct = p.k / kBN;
     p.iters_per_seg = (p.n + kBK - 1) / kBK;
     p.num_iters = p.nseg * p.iters_per_seg;
-    p.ldc = p.k;
+    p.ldc = L.ldc ? (int)L.ldc : p.k;
   }
   p.dense_m_tiles = (int)((L.m_total + kTileRows - 1) / kTileRows);
   p.has_lora = L.la != nullptr;
@@ -651,9 +652,14 @@ int launch_impl(const Launch& L) {
     if (rc) return rc;
   }
 
+  // First a runtime call: it binds the device's primary context to this thread.  The tensor-map encoder below is a driver
+  // entry point and fails with CUDA_ERROR_INVALID_CONTEXT on a thread that has made no runtime call yet (an autograd
+  // worker whose first CUDA work is this launch).
+  auto kern = qgemm_kernel<QT, MODE>;
+  B2G_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
   CUtensorMap tm_a0, tm_a1, tm_w0, tm_w1, tm_la, tm_lb;
   int rc;
-  const uint64_t a_pitch = (uint64_t)red_cols * 2;
+  const uint64_t a_pitch = (uint64_t)(L.lda ? L.lda : red_cols) * 2;
   if ((rc = make_tmap_2d(&tm_a0, L.a0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, red_cols, L.m_total, a_pitch, kBK, kBM,
                          CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   tm_a1 = tm_a0;
@@ -679,8 +685,6 @@ int launch_impl(const Launch& L) {
     }
   }
 
-  auto kern = qgemm_kernel<QT, MODE>;
-  B2G_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
   int pairs = sm_count() / 2;
   if (!L.tiles) {
     const int64_t items = (int64_t)p.dense_m_tiles * p.num_ct;
@@ -842,4 +846,41 @@ extern "C" int b2g_grouped_dgrad(int qtype, const void* dy0, const void* dy1, co
   B2G_REQUIRE(N % 64 == 0, "grouped_dgrad: N=%lld must be a multiple of 64", (long long)N);
   if (R == 0) return 0;
   return qg::launch_mode<qg::kDgrad>(L);
+}
+
+// ---- fixed groups: G independent dense products on column blocks of one activation tensor ----------------------
+static int fixed_grouped(int mode, int qtype, const void* a, const void* payload, void* out, int64_t M, int groups, int64_t N, int64_t K,
+                         int* status, void* stream, const char* what) {
+  B2G_REQUIRE(groups >= 1 && groups <= 64, "%s: group count %d outside 1..64", what, groups);
+  const int64_t in_w = mode == qg::kFwd ? K : N, out_w = mode == qg::kFwd ? N : K;
+  B2G_REQUIRE(in_w % 8 == 0 && out_w % 16 == 0, "%s: group widths %lld -> %lld must be multiples of 8 / 16", what, (long long)in_w,
+              (long long)out_w);
+  const int64_t row_bytes = fmt::row_bytes(qtype, K);
+  for (int g = 0; g < groups; ++g) {
+    qg::Launch L{};
+    L.qtype = qtype; L.mode = mode;
+    L.a0 = static_cast<const __nv_bfloat16*>(a) + g * in_w;
+    L.w0 = static_cast<const uint8_t*>(payload) + (int64_t)g * N * row_bytes;
+    L.out0 = static_cast<__nv_bfloat16*>(out) + g * out_w;
+    L.lda = groups * in_w; L.ldc = groups * out_w;
+    L.m_total = M; L.n = N; L.k = K; L.num_experts = 1; L.lora_rows = mode == qg::kFwd ? N : 16; L.status = status;
+    L.stream = static_cast<cudaStream_t>(stream);
+    int rc = qg::check_common(L, what);
+    if (rc) return rc;
+    if (M == 0) return 0;
+    rc = mode == qg::kFwd ? qg::launch_mode<qg::kFwd>(L) : qg::launch_mode<qg::kDgrad>(L);
+    if (rc) return rc;
+  }
+  return 0;
+}
+
+extern "C" int b2g_fixed_grouped_fwd(int qtype, const void* x, const void* payload, void* y, int64_t M, int groups, int64_t N, int64_t K,
+                                     int* status, void* stream) {
+  return fixed_grouped(qg::kFwd, qtype, x, payload, y, M, groups, N, K, status, stream, "fixed_grouped_fwd");
+}
+
+extern "C" int b2g_fixed_grouped_dgrad(int qtype, const void* dy, const void* payload, void* dx, int64_t M, int groups, int64_t N,
+                                       int64_t K, int* status, void* stream) {
+  B2G_REQUIRE(N % 8 == 0, "fixed_grouped_dgrad: N=%lld must be a multiple of 8", (long long)N);
+  return fixed_grouped(qg::kDgrad, qtype, dy, payload, dx, M, groups, N, K, status, stream, "fixed_grouped_dgrad");
 }
