@@ -85,6 +85,17 @@ B2G_API int b2g_fixed_grouped_fwd(int qtype, const void* x, const void* payload,
 B2G_API int b2g_fixed_grouped_dgrad(int qtype, const void* dy, const void* payload, void* dx, int64_t M, int groups, int64_t N,
                             int64_t K, int* status, void* stream);
 
+/* Cross-entropy of a chunk of bf16 logits [rows, V] (row pitch ld elements), IN PLACE: loss[row] = (logsumexp - logit
+ * of the target) * scale and the logits are overwritten by (softmax - onehot) * scale in bf16, scale = 1 / *count for
+ * mean (count: device scalar, the number of non-ignored targets of the WHOLE batch) or 1 for sum.  Rows whose target
+ * is ignore_index give zero loss and zero gradient; predicted[row] (argmax, -1 when ignored) and correct[row] (0/1) are
+ * optional.  Replaces the Liger Triton cross-entropy kernel that the packed LM-head loss runs between mmq and
+ * mmq_grad_input (gguf_liger_loss.py:138-170, deepseek_v4_liger_loss.py:129-158).  A target outside [0, V) sets status
+ * 902 and is treated as ignored. */
+B2G_API int b2g_cross_entropy_inplace(void* logits, int64_t ld, const int64_t* target, float* loss, int64_t* predicted, float* correct,
+                              int64_t rows, int64_t V, int64_t ignore_index, const int64_t* count, int mean, int* status,
+                              void* stream);
+
 /* Skinny projection onto the LoRA rank: P[M,r] = X[M,C] . W^T with W given as [r,C] (w_is_cr = 0,
  * lora_A for X.A^T) or as [C,r] (w_is_cr = 1, lora_B for dY.B); r <= 16.
  * Writes out_plain[M,16] = bf16(P) and out_scaled[M,16] = bf16(scale*P), zero in columns >= r

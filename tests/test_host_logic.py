@@ -169,3 +169,56 @@ def test_oracle_fixed_groups_equal_per_group_linear():
     xr = x.clone().requires_grad_(True)
     dense_ref.fixed_grouped(xr, w).backward(dy)
     assert torch.allclose(xr.grad, dense_ref.fixed_grouped_grad_input(dy, w), atol=1e-5)
+
+
+def test_packed_lm_head_loss_argument_contract():
+    """Argument checks of the packed LM-head loss run before anything touches a device (gguf_liger_loss.py:60-86,
+    deepseek_v4_liger_loss.py:235-272)."""
+    import deepseek_v4_liger_loss as dl
+    from b2g.gguf_types import GGUFLinear, GGUFQuantizedTensor
+
+    fwd = dl._packed_q8_linear_cross_entropy_forward
+    h, p, t = torch.zeros(4, 256, dtype=torch.bfloat16), torch.zeros(37 * 272, dtype=torch.uint8), torch.zeros(4, dtype=torch.long)
+    with pytest.raises(ValueError, match="two-dimensional"):
+        fwd(h[None], p, t, 8, 37, 512, -100, 0.0, 0.0, "mean", None)
+    with pytest.raises(TypeError, match="BF16"):
+        fwd(h.float(), p, t, 8, 37, 512, -100, 0.0, 0.0, "mean", None)
+    with pytest.raises(ValueError, match="match the hidden-state row count"):
+        fwd(h, p, t[:3], 8, 37, 512, -100, 0.0, 0.0, "mean", None)
+    with pytest.raises(TypeError, match="torch.long"):
+        fwd(h, p, t.int(), 8, 37, 512, -100, 0.0, 0.0, "mean", None)
+    with pytest.raises(ValueError, match="mean or sum"):
+        fwd(h, p, t, 8, 37, 512, -100, 0.0, 0.0, "none", None)
+    with pytest.raises(ValueError, match="chunk_size"):
+        fwd(h, p, t, 8, 37, 0, -100, 0.0, 0.0, "mean", None)
+
+    head = GGUFLinear(256, 37)
+    head.weight = GGUFQuantizedTensor(torch.zeros(37, 272, dtype=torch.uint8), quant_type=8, logical_shape=(37, 256))
+    labels = torch.zeros(1, 4, dtype=torch.long)
+    for kw, msg in (({"label_smoothing": 0.1}, "label_smoothing"), ({"return_z_loss": True}, "return_z_loss"),
+                    ({"accum_dtype": torch.bfloat16}, "FP32 internal accumulation")):
+        with pytest.raises(RuntimeError, match=msg):
+            dl.deepseek_v4_packed_liger_causal_lm_loss(h[None], head, labels, hidden_size=256, loss_kwargs=kw)
+    with pytest.raises(RuntimeError, match="hidden size does not match"):
+        dl.deepseek_v4_packed_liger_causal_lm_loss(h[None], head, labels, hidden_size=128)
+    head.weight = GGUFQuantizedTensor(torch.zeros(37, 210, dtype=torch.uint8), quant_type=14, logical_shape=(37, 256))
+    with pytest.raises(RuntimeError, match="validated only for Q8_0"):
+        dl.deepseek_v4_packed_liger_causal_lm_loss(h[None], head, labels, hidden_size=256)
+
+
+def test_oracle_lm_head_loss_matches_autograd_of_plain_torch():
+    from oracle import loss_ref
+
+    g = torch.Generator().manual_seed(11)
+    h = torch.randn(19, 64, generator=g).bfloat16()
+    w = (torch.randn(37, 64, generator=g) * 0.3).bfloat16()
+    t = torch.randint(0, 37, (19,), generator=g)
+    t[5] = -100
+    for reduction in ("mean", "sum"):
+        o = loss_ref.packed_linear_cross_entropy(h, w, t, -100, reduction)
+        logits = o["logits"].clone().requires_grad_(True)
+        ref = torch.nn.functional.cross_entropy(logits, t, ignore_index=-100, reduction=reduction)
+        ref.backward()
+        assert torch.allclose(o["loss"], ref, rtol=1e-6, atol=1e-6)
+        assert torch.allclose(o["grad_input"], logits.grad.bfloat16().float() @ w.float(), rtol=1e-5, atol=1e-6)
+        assert int(o["predicted"][5]) == -1

@@ -1,0 +1,103 @@
+"""GPU: packed LM-head chunked cross-entropy against the CPU oracle.
+
+Tolerances: the loss within rtol = atol = 1e-3 (the reference's own bar between its packed and logical losses,
+test_deepseek_v4_liger_loss.py:134); the input gradient within relative L2 <= 1e-2; predicted tokens exact wherever the
+top two logits differ.
+"""
+import numpy as np
+import pytest
+import torch
+from torch.utils._python_dispatch import TorchDispatchMode
+
+from oracle import dense_ref, gguf_oracle as go, loss_ref
+
+pytestmark = pytest.mark.gpu
+
+
+def _head(vocab, hidden, qtype, seed):
+    rng = np.random.default_rng(seed)
+    payload = go.quantize((rng.standard_normal((vocab, hidden)) * 0.08).astype(np.float32), qtype)
+    return payload, dense_ref.dequant_bf16(payload, qtype)
+
+
+@pytest.mark.parametrize("qtype,vocab,hidden,rows,chunk,reduction", [
+    (go.Q8_0, 37, 256, 34, 512, "mean"),          # the reference's toy shape: odd vocabulary -> element path of the kernel
+    (go.Q8_0, 4096, 512, 700, 256, "mean"),       # several chunks, ragged last one
+    (go.Q4_K, 2048, 1024, 300, 128, "sum"),
+])
+def test_loss_and_input_gradient(cuda, qtype, vocab, hidden, rows, chunk, reduction):
+    import deepseek_v4_liger_loss as dl
+
+    payload, w = _head(vocab, hidden, qtype, 100 + vocab)
+    g = torch.Generator().manual_seed(vocab)
+    h = torch.randn(rows, hidden, generator=g).bfloat16()
+    t = torch.randint(0, vocab, (rows,), generator=g)
+    t[::7] = -100
+    ref = loss_ref.packed_linear_cross_entropy(h, w, t, -100, reduction)
+
+    hc = h.to(cuda).requires_grad_(True)
+    loss, acc, pred = dl._PackedQ8LigerLinearCrossEntropyFunction.apply(
+        hc, torch.from_numpy(payload).to(cuda), t.to(cuda), qtype, vocab, chunk, -100, 0.0, 0.0, reduction, None, True, True)
+    (loss * 3.0).backward()
+    torch.testing.assert_close(loss.cpu(), ref["loss"], rtol=1e-3, atol=1e-3)
+    assert dense_ref.rel_l2(hc.grad, 3.0 * ref["grad_input"]) < 1e-2
+    top2 = ref["logits"].topk(2, dim=-1).values
+    clear = (top2[:, 0] - top2[:, 1]) > 0
+    assert torch.equal(pred.cpu()[clear], ref["predicted"][clear])
+    assert abs(float(acc) - float(ref["accuracy"])) < 2.0 / rows
+
+
+def test_module_surface_dispatches_packed_products(cuda):
+    """deepseek_v4_packed_liger_causal_lm_loss on a packed head: shifted labels, no logical weight, the two packed operators
+    in the dispatch trace (test_deepseek_v4_liger_loss.py:90-138)."""
+    import deepseek_v4_liger_loss as dl
+    from b2g.gguf_types import GGUFLinear, GGUFQuantizedTensor
+
+    payload, w = _head(37, 256, go.Q8_0, 9753)
+    head = GGUFLinear(256, 37)
+    head.weight = GGUFQuantizedTensor(torch.from_numpy(payload).to(cuda), quant_type=go.Q8_0, logical_shape=(37, 256))
+    g = torch.Generator().manual_seed(9753)
+    hidden = torch.randn(2, 17, 256, generator=g).bfloat16()
+    labels = torch.randint(0, 37, (2, 17), generator=g)
+    labels[1, 4] = -100
+    shifted = torch.nn.functional.pad(labels, (0, 1), value=-100)[..., 1:].reshape(-1)
+    ref = loss_ref.packed_linear_cross_entropy(hidden.reshape(-1, 256), w, shifted, -100, "mean")
+
+    seen = []
+
+    class Rec(TorchDispatchMode):
+        def __torch_dispatch__(self, func, types, args=(), kwargs=None):
+            seen.append(str(func))
+            return func(*args, **(kwargs or {}))
+
+    hc = hidden.to(cuda).requires_grad_(True)
+    with Rec():
+        loss = dl.deepseek_v4_packed_liger_causal_lm_loss(hc, head, labels.to(cuda), hidden_size=256)
+        loss.backward()
+    torch.testing.assert_close(loss.cpu(), ref["loss"], rtol=1e-3, atol=1e-3)
+    assert dense_ref.rel_l2(hc.grad.reshape(-1, 256), ref["grad_input"]) < 1e-2
+    assert "b2g.mmq.default" in seen and "b2g.mmq_grad_input.default" in seen
+    assert head.weight.grad is None and torch.isfinite(hc.grad).all()
+
+    # gradient accumulation: sum reduction divided by the caller's count
+    hc2 = hidden.to(cuda).requires_grad_(True)
+    n = int((shifted != -100).sum())
+    loss2 = dl.deepseek_v4_packed_liger_causal_lm_loss(hc2, head, labels.to(cuda), hidden_size=256, loss_kwargs={"num_items_in_batch": n})
+    torch.testing.assert_close(loss2.cpu(), ref["loss"], rtol=1e-3, atol=1e-3)
+
+
+def test_all_targets_ignored_and_bad_label(cuda):
+    from b2g import ops
+
+    logits = torch.randn(5, 64, device=cuda).bfloat16()
+    target = torch.full((5,), -100, dtype=torch.long, device=cuda)
+    loss = torch.empty(5, device=cuda)
+    count = (target != -100).sum().reshape(1)
+    ops.cross_entropy_inplace(logits, target, loss, count, True)
+    assert float(loss.abs().sum()) == 0.0 and float(logits.float().abs().sum()) == 0.0
+    ops.check_status()
+    logits = torch.randn(2, 64, device=cuda).bfloat16()
+    target = torch.tensor([3, 64], dtype=torch.long, device=cuda)      # 64 is outside the vocabulary
+    ops.cross_entropy_inplace(logits, target, torch.empty(2, device=cuda), (target != -100).sum().reshape(1), True)
+    with pytest.raises(Exception, match="902"):
+        ops.check_status()

@@ -21,6 +21,7 @@ SIGNATURES = {
     "b2g_qlinear_dgrad": (_i32, [_i32, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp]),
     "b2g_fixed_grouped_fwd": (_i32, [_i32, _vp, _vp, _vp, _i64, _i32, _i64, _i64, _vp, _vp]),
     "b2g_fixed_grouped_dgrad": (_i32, [_i32, _vp, _vp, _vp, _i64, _i32, _i64, _i64, _vp, _vp]),
+    "b2g_cross_entropy_inplace": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i32, _vp, _vp]),
     "b2g_lora_down": (_i32, [_vp, _vp, _i32, _f32, _vp, _vp, _i64, _i64, _i32, _vp]),
     "b2g_lora_wgrad_workspace_bytes": (_i64, [_i64, _i64]),
     "b2g_lora_wgrad": (_i32, [_vp, _vp, _f32, _vp, _i32, _vp, _i64, _i64, _i64, _i32, _vp]),
@@ -80,7 +81,7 @@ KERNELS_PER_CALL = {
     "b2g_router_topk": 1, "b2g_route_plan": 4, "b2g_route_gather": 1, "b2g_route_gather_bwd": 1, "b2g_route_combine": 1,
     "b2g_route_combine_bwd": 1, "b2g_grouped_schedule": 1, "b2g_grouped_fwd": 1, "b2g_grouped_dgrad": 1,
     "b2g_grouped_lora_down": 1, "b2g_grouped_lora_wgrad": 1, "b2g_grouped_lora_up": 1, "b2g_ep_scatter_rows": 1, "b2g_ep_return_rows": 1, "b2g_swiglu_fwd": 1, "b2g_swiglu_bwd": 1,
-    "b2g_fixed_grouped_fwd": 8, "b2g_fixed_grouped_dgrad": 8,      # one launch per group (eight in the DeepSeek layout)
+    "b2g_cross_entropy_inplace": 1, "b2g_fixed_grouped_fwd": 8, "b2g_fixed_grouped_dgrad": 8,      # one launch per group (eight in the DeepSeek layout)
 }
 COUNT_LAUNCHES = False
 LAUNCHES = 0

@@ -72,7 +72,9 @@ def status_word(device: torch.device) -> torch.Tensor:
 
 
 def check_status(device: Optional[torch.device] = None) -> None:
-    """Synchronise and raise if any kernel on the device reported a timed-out wait."""
+    """Synchronise and raise if any kernel on the device reported a problem through the status word: a bounded wait that
+    ran out (sites 1xx-4xx), a receive buffer too small for an expert-parallel exchange (901), a label outside the
+    vocabulary in the cross-entropy kernel (902)."""
     devs = [device.index if device is not None and device.index is not None else torch.cuda.current_device()] \
         if device is not None else list(_status)
     for idx in devs:
@@ -80,7 +82,9 @@ def check_status(device: Optional[torch.device] = None) -> None:
             code = int(_status[idx].item())
             if code:
                 _status[idx].zero_()
-                raise _lib.B2GError(f"a libb2g kernel gave up a bounded wait on cuda:{idx} (site {code})")
+                what = {901: "an expert-parallel receive buffer was too small", 902: "a cross-entropy target was outside the vocabulary"}.get(
+                    code, "a libb2g kernel gave up a bounded wait")
+                raise _lib.B2GError(f"{what} on cuda:{idx} (status {code})")
 
 
 def ensure_iq2xxs_grid(device: torch.device) -> None:
@@ -200,6 +204,30 @@ def qlinear_fwd(x: torch.Tensor, payload: torch.Tensor, qtype: int, n: int, bias
         _lib.call("b2g_qlinear_fwd", int(qtype), _p(x), _p(payload), _p(bias), _p(xas), _p(lora_b16), _p(y), m, n, k,
                   _p(status_word(x.device)), _stream(x))
     return y
+
+
+def cross_entropy_inplace(logits: torch.Tensor, target: torch.Tensor, loss: torch.Tensor, count: Optional[torch.Tensor], mean: bool,
+                          ignore_index: int = -100, predicted: Optional[torch.Tensor] = None,
+                          correct: Optional[torch.Tensor] = None) -> None:
+    """Cross-entropy of bf16 ``logits [rows, V]`` against ``target [rows]``: ``loss [rows]`` (fp32) is written and the logits
+    are overwritten by their cotangent (softmax - onehot) / count (mean) or (softmax - onehot) (sum).  ``count`` is a
+    one-element int64 device tensor holding the number of non-ignored targets of the whole batch."""
+    _need(logits, torch.bfloat16, "logits")
+    _need(target, torch.int64, "target")
+    _need(loss, torch.float32, "loss")
+    rows, v = logits.shape
+    if logits.stride(1) != 1 or target.shape != (rows,) or loss.shape != (rows,) or not target.is_contiguous() or not loss.is_contiguous():
+        raise ValueError("cross_entropy_inplace: logits [rows, V] with unit column stride, target and loss [rows], contiguous")
+    if mean:
+        _need(count, torch.int64, "count")
+    for name, t, dt in (("predicted", predicted, torch.int64), ("correct", correct, torch.float32)):
+        if t is not None:
+            _need(t, dt, name)
+            if t.shape != (rows,) or not t.is_contiguous():
+                raise ValueError(f"cross_entropy_inplace: {name} must be a contiguous [rows] tensor")
+    with _DeviceCtx(logits):
+        _lib.call("b2g_cross_entropy_inplace", _p(logits), logits.stride(0), _p(target), _p(loss), _p(predicted), _p(correct), rows, v,
+                  int(ignore_index), _p(count) if mean else None, int(bool(mean)), _p(status_word(logits.device)), _stream(logits))
 
 
 def _fixed_group_geometry(a: torch.Tensor, payload: torch.Tensor, qtype: int, forward: bool):

@@ -8,7 +8,7 @@ from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
-SOURCES = ["b2g_api.cu", "b2g_dequant.cu", "b2g_routing.cu", "b2g_lora.cu", "b2g_qgemm.cu", "b2g_ep.cu"]
+SOURCES = ["b2g_api.cu", "b2g_dequant.cu", "b2g_routing.cu", "b2g_lora.cu", "b2g_qgemm.cu", "b2g_ep.cu", "b2g_loss.cu"]
 HEADERS = ["b2g_common.cuh", "b2g_formats.cuh", "../../include/b2g.h"]
 LIB = HERE / "libb2g.so"
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
