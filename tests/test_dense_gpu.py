@@ -32,6 +32,7 @@ def _case(qtype, m, n, k, r, seed, encoder="quantize"):
     (go.Q4_K, 300, 512, 1024, 16), (go.Q4_K, 33, 37, 256, 4), (go.Q4_K, 1, 8, 256, 1), (go.Q4_K, 513, 768, 2048, 8),
     (go.Q8_0, 300, 512, 1024, 16), (go.Q8_0, 129, 200, 512, 4),
     (go.IQ2_XXS, 260, 512, 2048, 8), (go.IQ2_XXS, 64, 300, 4096, 16),
+    (go.Q6_K, 700, 512, 2048, 16), (go.Q6_K, 130, 264, 4096, 4), (go.Q6_K, 1, 8, 2048, 1),
 ])
 def test_fused_lora_linear_forward_backward(cuda, qtype, m, n, k, r):
     from b2g import autograd as ag

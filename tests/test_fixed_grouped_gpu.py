@@ -52,7 +52,8 @@ def test_deepseek_layout_equals_per_group_mmq_exactly(cuda):
     assert dense_ref.rel_l2(hidden.grad, dense_ref.fixed_grouped_grad_input(dy, w)) < 1e-2
 
 
-@pytest.mark.parametrize("qtype,groups,n,k,rows", [(go.Q4_K, 4, 512, 1024, 700), (go.Q8_0, 2, 48, 256, 33), (go.IQ2_XXS, 3, 256, 2048, 130)])
+@pytest.mark.parametrize("qtype,groups,n,k,rows", [(go.Q4_K, 4, 512, 1024, 700), (go.Q8_0, 2, 48, 256, 33), (go.IQ2_XXS, 3, 256, 2048, 130),
+                                                  (go.Q6_K, 2, 256, 2048, 300)])
 def test_other_types_and_ragged_rows(cuda, qtype, groups, n, k, rows):
     from b2g import autograd as ag
 
@@ -77,6 +78,6 @@ def test_fail_closed(cuda):
     with pytest.raises(RuntimeError, match="contiguous"):
         ag.fixed_grouped_mmq(torch.zeros(2, 8, 8192, dtype=torch.bfloat16, device=cuda)[..., ::2], packed, 8)
     with pytest.raises(ValueError, match="not supported natively"):
-        ag.fixed_grouped_mmq(torch.zeros(2, 8, 4096, dtype=torch.bfloat16, device=cuda), packed, 14)
+        ag.fixed_grouped_mmq(torch.zeros(2, 8, 4096, dtype=torch.bfloat16, device=cuda), packed, 10)
     empty = ag.fixed_grouped_mmq(torch.zeros(0, 8, 4096, dtype=torch.bfloat16, device=cuda), packed, 8)
     assert empty.shape == (0, 8, 1024)

@@ -24,6 +24,7 @@ def _head(vocab, hidden, qtype, seed):
     (go.Q8_0, 37, 256, 34, 512, "mean"),          # the reference's toy shape: odd vocabulary -> element path of the kernel
     (go.Q8_0, 4096, 512, 700, 256, "mean"),       # several chunks, ragged last one
     (go.Q4_K, 2048, 1024, 300, 128, "sum"),
+    (go.Q6_K, 1032, 2048, 520, 256, "mean"),      # the Qwen head's type and hidden size
 ])
 def test_loss_and_input_gradient(cuda, qtype, vocab, hidden, rows, chunk, reduction):
     import deepseek_v4_liger_loss as dl
@@ -101,3 +102,32 @@ def test_all_targets_ignored_and_bad_label(cuda):
     ops.cross_entropy_inplace(logits, target, torch.empty(2, device=cuda), (target != -100).sum().reshape(1), True)
     with pytest.raises(Exception, match="902"):
         ops.check_status()
+
+
+def test_qwen_entry_point_q6k_head(cuda):
+    """gguf_liger_loss._packed_q8_liger_for_causal_lm_loss (gguf_liger_loss.py:268-355): Q6_K head, hidden 2048, with the
+    optional token accuracy and predicted tokens; anything else is refused."""
+    import gguf_liger_loss as gl
+    from b2g.gguf_types import GGUFLinear, GGUFQuantizedTensor
+
+    payload, w = _head(520, 2048, go.Q6_K, 31)
+    head = GGUFLinear(2048, 520)
+    head.weight = GGUFQuantizedTensor(torch.from_numpy(payload).to(cuda), quant_type=go.Q6_K, logical_shape=(520, 2048))
+    g = torch.Generator().manual_seed(5)
+    hidden = torch.randn(3, 40, 2048, generator=g).bfloat16()
+    labels = torch.randint(0, 520, (3, 40), generator=g)
+    labels[0, :5] = -100
+    shifted = torch.nn.functional.pad(labels, (0, 1), value=-100)[..., 1:].reshape(-1)
+    ref = loss_ref.packed_linear_cross_entropy(hidden.reshape(-1, 2048), w, shifted, -100, "mean")
+    hc = hidden.to(cuda).requires_grad_(True)
+    loss, z, acc, pred = gl._packed_q8_liger_for_causal_lm_loss(hc, head, labels.to(cuda), 2048, return_token_accuracy=True,
+                                                                 return_predicted_tokens=True)
+    loss.backward()
+    assert z is None and pred.shape == (120,)
+    torch.testing.assert_close(loss.cpu(), ref["loss"], rtol=1e-3, atol=1e-3)
+    assert dense_ref.rel_l2(hc.grad.reshape(-1, 2048), ref["grad_input"]) < 1e-2
+    assert abs(float(acc) - float(ref["accuracy"])) < 2.0 / 120
+    q8_payload, _ = _head(520, 2048, go.Q8_0, 32)
+    head.weight = GGUFQuantizedTensor(torch.from_numpy(q8_payload).to(cuda), quant_type=go.Q8_0, logical_shape=(520, 2048))
+    with pytest.raises(RuntimeError, match="validated only for Q6_K"):
+        gl._packed_q8_liger_for_causal_lm_loss(hc, head, labels.to(cuda), 2048)

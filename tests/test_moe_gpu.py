@@ -68,6 +68,7 @@ def test_constant_byte_iq2_xxs_payload_like_the_reference_test(cuda):
     (go.Q4_K, 16, 1024, 512, 700, 4, 8, True),
     (go.Q8_0, 8, 512, 256, 300, 2, 16, False),
     (go.IQ2_XXS, 4, 2048, 2048, 300, 2, 8, False),
+    (go.Q6_K, 4, 2048, 2048, 700, 2, 16, False),
 ])
 def test_expert_layer_forward_backward(cuda, qtype, e, h, i, t, k, r, skew):
     from b2g import autograd as ag, routing

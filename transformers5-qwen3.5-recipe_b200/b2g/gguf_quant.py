@@ -67,7 +67,7 @@ def random_payload(qtype: int, shape: tuple[int, ...], seed: int, std: float = 0
     For IQ2_XXS this stands in for an encoder: every index/sign/sub-scale field is uniform and the
     fp16 block scale sets the magnitude.
     """
-    blk, nbytes = {8: (32, 34), 12: (256, 144), 16: (256, 66)}[int(qtype)]
+    blk, nbytes = {8: (32, 34), 12: (256, 144), 14: (256, 210), 16: (256, 66)}[int(qtype)]
     *lead, k = shape
     n = 1
     for v in lead:
@@ -81,6 +81,8 @@ def random_payload(qtype: int, shape: tuple[int, ...], seed: int, std: float = 0
     elif qtype == 12:
         b[:, 0:2] = _f16_bytes(std / 190.0 * jitter)
         b[:, 2:4] = _f16_bytes(std / 25.0 * jitter)
+    elif qtype == 14:
+        b[:, 208:210] = _f16_bytes(std / (74.0 * 18.5) * jitter)
     else:
         b[:, 0:2] = _f16_bytes(std * 4.0 / (85.0 * 600.0) ** 0.5 * jitter)
     return b.reshape(*lead, k // blk * nbytes)

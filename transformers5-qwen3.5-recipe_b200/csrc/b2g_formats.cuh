@@ -1,13 +1,15 @@
-// Device-side decoders for the GGUF block formats on the path: Q8_0, Q4_K, IQ2_XXS.
+// Device-side decoders for the GGUF block formats on the path: Q8_0, Q4_K, Q6_K, IQ2_XXS.
 //
 // The arithmetic reproduces the float32 decode of the public format definition bit for bit
 // after the final bf16 round-to-nearest-even:
 //   Q8_0    q * d                                 (19 significant bits: exact in fp32)
 //   Q4_K    (d*sc)*q - (dmin*m)                   (both products exact; the subtraction rounds once,
 //                                                  so a single fused multiply-add gives the same bits)
+//   Q6_K    (d*scale)*q                           (11 x 7, then x 6 significant bits: both products exact)
 //   IQ2_XXS d*(0.5+s4)*0.25 * grid * sign         (22 significant bits: exact in fp32)
 // Block layouts (bytes): Q8_0 34 = fp16 d | 32 x int8; Q4_K 144 = fp16 d | fp16 dmin | 12 scale bytes
-// | 128 nibble bytes; IQ2_XXS 66 = fp16 d | 8 x (4 grid indices | u32: 4 x 7-bit signs + 4-bit scale).
+// | 128 nibble bytes; Q6_K 210 = 128 low-nibble bytes | 64 high-pair bytes | 16 int8 scales | fp16 d;
+// IQ2_XXS 66 = fp16 d | 8 x (4 grid indices | u32: 4 x 7-bit signs + 4-bit scale).
 #pragma once
 
 #include "b2g_common.cuh"
@@ -19,12 +21,14 @@ template <int QT> struct Block;
 template <> struct Block<B2G_Q8_0> { static constexpr int kValues = 32, kBytes = 34; };
 template <> struct Block<B2G_Q4_K> { static constexpr int kValues = 256, kBytes = 144; };
 template <> struct Block<B2G_IQ2_XXS> { static constexpr int kValues = 256, kBytes = 66; };
+template <> struct Block<B2G_Q6_K> { static constexpr int kValues = 256, kBytes = 210; };
 
 __host__ __device__ inline int64_t row_bytes(int qtype, int64_t k) {
   switch (qtype) {
     case B2G_Q8_0: return k / 32 * 34;
     case B2G_Q4_K: return k / 256 * 144;
     case B2G_IQ2_XXS: return k / 256 * 66;
+    case B2G_Q6_K: return k / 256 * 210;
     default: return -1;
   }
 }
@@ -94,6 +98,35 @@ struct Decode8<B2G_Q4_K> {
     for (int i = 0; i < 4; ++i) {
       v[i] = __fmaf_rn(dsc, byte_to_float(w0, i), -dm);
       v[4 + i] = __fmaf_rn(dsc, byte_to_float(w1, i), -dm);
+    }
+  }
+};
+
+// Six-bit value minus 32 at byte i of `word` (bytes 0..63) -> exact float.
+__device__ __forceinline__ float q6_to_float(uint32_t word, int i) {
+  const uint32_t magic = __byte_perm(word, 0x4B000000u, 0x7540u + i);
+  return __uint_as_float(magic) - 8388640.0f;  // 2^23 + 32
+}
+
+template <>
+struct Decode8<B2G_Q6_K> {
+  __device__ static __forceinline__ void run(const uint8_t* __restrict__ row, int k0, const uint2*, float (&v)[8]) {
+    const uint8_t* b = row + (k0 >> 8) * 210;  // 210-byte blocks are only 2-byte aligned
+    const int within = k0 & 255;
+    const int h = within >> 7, t = (within >> 5) & 3, l = within & 31;   // half, 32-value group, position (multiple of 8)
+    const unsigned short* ql = reinterpret_cast<const unsigned short*>(b + 64 * h + 32 * (t & 1) + l);
+    const unsigned short* qh = reinterpret_cast<const unsigned short*>(b + 128 + 32 * h + l);
+    const float d = dev::half_bits_to_float(*reinterpret_cast<const unsigned short*>(b + 208));
+    const float sc = static_cast<float>(static_cast<int>(static_cast<signed char>(b[192 + (within >> 4)])));
+    const float dsc = __fmul_rn(d, sc);
+    const int lo_shift = (t >> 1) * 4, hi_shift = 2 * t;
+#pragma unroll
+    for (int w2 = 0; w2 < 2; ++w2) {
+      const uint32_t lw = static_cast<uint32_t>(ql[2 * w2]) | (static_cast<uint32_t>(ql[2 * w2 + 1]) << 16);
+      const uint32_t hw = static_cast<uint32_t>(qh[2 * w2]) | (static_cast<uint32_t>(qh[2 * w2 + 1]) << 16);
+      const uint32_t q = ((lw >> lo_shift) & 0x0F0F0F0Fu) | (((hw >> hi_shift) & 0x03030303u) << 4);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[4 * w2 + i] = __fmul_rn(dsc, q6_to_float(q, i));
     }
   }
 };

@@ -59,27 +59,36 @@ constexpr int kTmemCols = 512;
 template <int QT, int MODE> struct Packed;
 // Q4_K forward: header (d, dmin, 12 scale bytes) + the 32 nibble bytes of one 64-value pair, as
 // three [128 rows x 16 B] boxes so that each thread reads its row with conflict-free 16-byte loads.
-template <> struct Packed<B2G_Q4_K, kFwd> { static constexpr int kBoxWords = 4, kBoxRows = 128, kBytes = 3 * 2048; };
+template <> struct Packed<B2G_Q4_K, kFwd> { static constexpr int kBoxWords = 4, kBoxRows = 128, kBytes = 3 * 2048, kSteps = 1; };
 // Q4_K dgrad: whole 144-byte super-blocks of 64 rows (row stride 144 B: conflict-free 16-byte loads);
 // each CTA decodes the two 64-value pairs of its 128 columns.
-template <> struct Packed<B2G_Q4_K, kDgrad> { static constexpr int kBoxWords = 36, kBoxRows = 64, kBytes = 64 * 144; };
+template <> struct Packed<B2G_Q4_K, kDgrad> { static constexpr int kBoxWords = 36, kBoxRows = 64, kBytes = 64 * 144, kSteps = 1; };
 // Q8_0 forward: two 34-byte blocks start at byte 68*step; an 80-byte window from the 16-byte boundary below
 // covers them (the start is at most 12 bytes into the window).
-template <> struct Packed<B2G_Q8_0, kFwd> { static constexpr int kBoxWords = 20, kBoxRows = 128, kBytes = 128 * 80; };
+template <> struct Packed<B2G_Q8_0, kFwd> { static constexpr int kBoxWords = 20, kBoxRows = 128, kBytes = 128 * 80, kSteps = 1; };
 // Q8_0 dgrad: this CTA's 128 columns are four blocks (136 B) starting at byte 272*tile + 136*rank of the row; a
 // 144-byte window from the 16-byte boundary below covers them (the start is 0 or 8 bytes into the window).
-template <> struct Packed<B2G_Q8_0, kDgrad> { static constexpr int kBoxWords = 36, kBoxRows = 64, kBytes = 64 * 144; };
+template <> struct Packed<B2G_Q8_0, kDgrad> { static constexpr int kBoxWords = 36, kBoxRows = 64, kBytes = 64 * 144, kSteps = 1; };
 // IQ2_XXS: 66-byte super-blocks are not 16-byte aligned; an 80-byte window from the boundary below covers one
 // (the start is at most 14 bytes into the window).
-template <> struct Packed<B2G_IQ2_XXS, kFwd> { static constexpr int kBoxWords = 20, kBoxRows = 128, kBytes = 128 * 80; };
-template <> struct Packed<B2G_IQ2_XXS, kDgrad> { static constexpr int kBoxWords = 20, kBoxRows = 64, kBytes = 64 * 80; };
+template <> struct Packed<B2G_IQ2_XXS, kFwd> { static constexpr int kBoxWords = 20, kBoxRows = 128, kBytes = 128 * 80, kSteps = 1; };
+template <> struct Packed<B2G_IQ2_XXS, kDgrad> { static constexpr int kBoxWords = 20, kBoxRows = 64, kBytes = 64 * 80, kSteps = 1; };
+// Q6_K: 210-byte super-blocks start on any even byte of a 16-byte line.  A 64-value step uses, of its super-block, 64 bytes
+// of low nibbles, 32 bytes of high bit pairs, 4 scales and d; with the slack of the alignment that is ten 16-byte pieces
+// per row: five from the line below the nibbles, three below the bit pairs, two below the scales.  Each piece is one
+// [rows x 16 B] box, so threads read their row's pieces without bank conflicts.  Forward: steps 2m and 2m+1 use the SAME
+// bytes (low / high nibbles, bit pairs 0-3 / 4-7), so one slot serves both and the two unpack groups that take them.
+template <> struct Packed<B2G_Q6_K, kFwd> { static constexpr int kBoxWords = 4, kBoxRows = 128, kBytes = 10 * 2048, kSteps = 2; };
+template <> struct Packed<B2G_Q6_K, kDgrad> { static constexpr int kBoxWords = 4, kBoxRows = 64, kBytes = 10 * 1024, kSteps = 1; };
 
 template <int QT, int MODE>
 struct Cfg {
   using P = Packed<QT, MODE>;
   static constexpr int kAStages = 3;
   static constexpr int kAStage = kMT * kATile;
-  static constexpr int kPStages = kUnpackGroups;   // slot s always belongs to unpack group s, so each group sees every phase of its barriers
+  // packed slots: slot s always belongs to the same unpack group(s) (P::kSteps consecutive groups share one), so each group
+  // sees every phase of its barriers
+  static constexpr int kPStages = kUnpackGroups / P::kSteps;
   static_assert(kBStages == kUnpackGroups, "B slots are owned by unpack groups as well");
   static constexpr int kPStage = (P::kBytes + 1023) / 1024 * 1024;
   // shared-memory map (offsets from a 1024-byte aligned base)
@@ -235,6 +244,48 @@ __device__ __forceinline__ void iq2_half(float d, uint32_t idx4, uint32_t word, 
   }
 }
 
+// `N` words that start `sft` bytes (even, < 16, warp-uniform) into the 16-byte aligned words `raw`.
+template <int N, int NRAW>
+__device__ __forceinline__ void extract_words(const uint32_t (&raw)[NRAW], int sft, uint32_t (&w)[N]) {
+  static_assert(N + 3 <= NRAW, "not enough loaded words for the largest shift");
+  const int ws = sft >> 2;
+  const uint32_t bs = static_cast<uint32_t>(sft & 3) * 8u;   // 0 or 16 bits
+  auto at = [&](int i) { return i < NRAW ? raw[i < NRAW ? i : 0] : 0u; };
+  if (ws == 0) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) w[i] = __funnelshift_r(at(i), at(i + 1), bs);
+  } else if (ws == 1) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) w[i] = __funnelshift_r(at(i + 1), at(i + 2), bs);
+  } else if (ws == 2) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) w[i] = __funnelshift_r(at(i + 2), at(i + 3), bs);
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i) w[i] = __funnelshift_r(at(i + 3), at(i + 4), bs);
+  }
+}
+
+// Q6_K: 32 values of a 64-value slice.  `j` = which quarter of the super-block the slice is (its parity picks the low or the
+// high nibbles and the bit pairs 0-3 or 4-7); `half` = first or second 32 values (nibble bytes 0-31 / 32-63, bit pair
+// 2*half of the nibble-parity's four).  value = (d * scale) * (q - 32), both products exact in fp32.
+__device__ __forceinline__ void q6k_half(const uint32_t (&ql)[16], const uint32_t (&qh)[8], uint32_t sc4, float d, int j, int half,
+                                         uint32_t (&out)[16]) {
+  const int s = j & 1;
+  const uint32_t scx = sc4 ^ 0x80808080u;
+  const float dsc0 = __fmul_rn(d, half ? sbyte_to_float(scx, 2) : sbyte_to_float(scx, 0));
+  const float dsc1 = __fmul_rn(d, half ? sbyte_to_float(scx, 3) : sbyte_to_float(scx, 1));
+  const int lo_shift = 4 * s, hi_shift = 4 * s + 2 * half;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t lw = half ? ql[8 + i] : ql[i];
+    const uint32_t q = ((lw >> lo_shift) & 0x0F0F0F0Fu) | (((qh[i] >> hi_shift) & 0x03030303u) << 4);
+    const float dsc = i < 4 ? dsc0 : dsc1;
+    out[2 * i] = dev::pack_bf16(__fmul_rn(dsc, fmt::q6_to_float(q, 0)), __fmul_rn(dsc, fmt::q6_to_float(q, 1)));
+    out[2 * i + 1] = dev::pack_bf16(__fmul_rn(dsc, fmt::q6_to_float(q, 2)), __fmul_rn(dsc, fmt::q6_to_float(q, 3)));
+  }
+}
+
 // What one unpack thread needs of a packed stage, held in registers: both 32-value halves of its 64-value slice of
 // one W row come from the same packed bytes, so they are read from shared memory once.
 //   forward: thread = one of this CTA's 128 W rows; the step selects which 64 of the row's values
@@ -243,6 +294,7 @@ template <int QT> struct RowData;
 template <> struct RowData<B2G_Q4_K> { uint4 hdr, qa, qb; };
 template <> struct RowData<B2G_Q8_0> { uint32_t w[17]; };
 template <> struct RowData<B2G_IQ2_XXS> { float d; uint32_t idx4[2], word[2]; };
+template <> struct RowData<B2G_Q6_K> { uint32_t ql[16], qh[8]; uint32_t sc4; float d; };   // 64 nibble bytes, 32 bit-pair bytes, 4 int8 scales
 
 template <int QT, int MODE>
 __device__ __forceinline__ void load_row(uint32_t pk, int row, int pair, int it, int ct, RowData<QT>& rd) {
@@ -263,6 +315,33 @@ __device__ __forceinline__ void load_row(uint32_t pk, int row, int pair, int it,
       const int byte0 = ((136 * (pair >> 1)) & 15) + 68 * (pair & 1);  // two blocks of column quarter `pair` inside the 144-byte window
       load_words_shifted<17>(pk + row * 144 + (byte0 & ~15), byte0 & 15, rd.w);
     }
+  } else if constexpr (QT == B2G_Q6_K) {
+    // pieces of this row: `piece` bytes apart, 16 bytes each; the super-block starts `sft` (even) bytes into the first line
+    constexpr uint32_t kPiece = (MODE == kFwd ? 128u : 64u) * 16u;
+    const int sb = MODE == kFwd ? (it >> 2) : ct;
+    const int sft = (210 * sb) & 15;
+    const uint32_t base = pk + row * 16;
+    uint32_t raw[20];
+#pragma unroll
+    for (int q = 0; q < 5; ++q) {
+      const uint4 v = dev::lds128(base + q * kPiece);
+      raw[4 * q] = v.x; raw[4 * q + 1] = v.y; raw[4 * q + 2] = v.z; raw[4 * q + 3] = v.w;
+    }
+    extract_words<16, 20>(raw, sft, rd.ql);
+    uint32_t rawh[12];
+#pragma unroll
+    for (int q = 0; q < 3; ++q) {
+      const uint4 v = dev::lds128(base + (5 + q) * kPiece);
+      rawh[4 * q] = v.x; rawh[4 * q + 1] = v.y; rawh[4 * q + 2] = v.z; rawh[4 * q + 3] = v.w;
+    }
+    extract_words<8, 12>(rawh, sft, rd.qh);
+    // the four scales of this 64-value slice (scales[4j .. 4j+3], j = `pair`) and d (two bytes, 16 after the scales): byte
+    // offsets sft + 4j and sft + 16 into the 32-byte scale window, which lies in two pieces
+    auto win = [&](int byte) { return base + (8 + (byte >> 4)) * kPiece + (byte & 15); };
+    const int so = sft + 4 * pair;   // even
+    const uint32_t lo = dev::lds16(win(so)), hi = dev::lds16(win(so + 2));
+    rd.sc4 = lo | (hi << 16);
+    rd.d = dev::half_bits_to_float(dev::lds16(win(sft + 16)));
   } else {
     // 66-byte super-block inside an 80-byte window; `off` (even) is where it starts.
     const int sb = MODE == kFwd ? (it >> 2) : ct;
@@ -282,6 +361,7 @@ template <int QT>
 __device__ __forceinline__ void decode_half(const RowData<QT>& rd, int pair, int half, uint32_t grid_s, uint32_t (&out)[16]) {
   if constexpr (QT == B2G_Q4_K) q4k_half(rd.hdr, rd.qa, rd.qb, pair, half, out);
   else if constexpr (QT == B2G_Q8_0) q8_half(rd.w, half, out);
+  else if constexpr (QT == B2G_Q6_K) q6k_half(rd.ql, rd.qh, rd.sc4, rd.d, pair, half, out);
   else iq2_half(rd.d, rd.idx4[half], rd.word[half], grid_s, out);
 }
 
@@ -366,7 +446,7 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
   if (threadIdx.x == 0) {
     for (int i = 0; i < C::kAStages; ++i) { dev::mbar_init(bar(kFullA + i), 1); dev::mbar_init(bar(kEmptyA + i), 1); }
     for (int i = 0; i < kBStages; ++i) { dev::mbar_init(bar(kFullB + i), 2 * kGroupWarps); dev::mbar_init(bar(kEmptyB + i), 1); }
-    for (int i = 0; i < C::kPStages; ++i) { dev::mbar_init(bar(kFullP + i), 1); dev::mbar_init(bar(kEmptyP + i), kGroupWarps); }
+    for (int i = 0; i < C::kPStages; ++i) { dev::mbar_init(bar(kFullP + i), 1); dev::mbar_init(bar(kEmptyP + i), kGroupWarps * P::kSteps); }
     dev::mbar_init(bar(kFullL), 1);
     dev::mbar_init(bar(kEmptyL), 1);
     dev::mbar_init(bar(kAccFull), 1);
@@ -513,12 +593,22 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
         for (int it = 0; it < p.num_iters; ++it) {
           int seg = fseg, red0 = it * kBK;
           if (MODE == kDgrad) { seg = it / p.iters_per_seg; red0 = (it - seg * p.iters_per_seg) * kBK; }
+          if (P::kSteps > 1 && (it % P::kSteps) != 0) continue;     // this step reads the slot loaded for the previous one
           ok = dev::mbar_wait(bar(kEmptyP + sp), pp ^ 1, abort_flag, p.status, 104);
           if (!ok) break;
           dev::mbar_arrive_expect_tx(bar(kFullP + sp), P::kBytes);
           const CUtensorMap* wm = seg ? &tm_w1 : &tm_w0;
           const uint32_t dst = sP + sp * C::kPStage;
-          if (MODE == kFwd) {
+          if (QT == B2G_Q6_K) {
+            // ten [rows x 16 B] pieces: 5 from the line below the nibbles of half h, 3 below its bit pairs, 2 below the scales
+            const int sb = MODE == kFwd ? (it >> 2) : t.ct, h = MODE == kFwd ? ((it >> 1) & 1) : static_cast<int>(rank);
+            const int x0 = ((210 * sb) & ~15) >> 2;
+            const int y = MODE == kFwd ? t.expert * p.n + col0 + static_cast<int>(rank) * kBNh : t.expert * p.n + red0;
+            constexpr uint32_t kPiece = P::kBoxRows * 16;
+            for (int q = 0; q < 5; ++q) dev::tma_load_2d(dst + q * kPiece, wm, bar(kFullP + sp), x0 + 16 * h + 4 * q, y);
+            for (int q = 0; q < 3; ++q) dev::tma_load_2d(dst + (5 + q) * kPiece, wm, bar(kFullP + sp), x0 + 32 + 8 * h + 4 * q, y);
+            for (int q = 0; q < 2; ++q) dev::tma_load_2d(dst + (8 + q) * kPiece, wm, bar(kFullP + sp), x0 + 48 + 4 * q, y);
+          } else if (MODE == kFwd) {
             const int y = t.expert * p.n + col0 + static_cast<int>(rank) * kBNh;
             if (QT == B2G_Q4_K) {
               const int xb = 36 * (it >> 2), xq = xb + 4 + 8 * (it & 3);
@@ -552,7 +642,8 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
       const int ct = item % p.num_ct;
       for (int it = 0; it < p.num_iters; ++it, ++n) {
         if ((n % kUnpackGroups) != group) continue;
-        const int sp = n % C::kPStages, pp = (n / C::kPStages) & 1;
+        const int ps = n / P::kSteps;                                // packed slots advance once per P::kSteps steps
+        const int sp = ps % C::kPStages, pp = (ps / C::kPStages) & 1;
         const int sb = n % kBStages, pb = (n / kBStages) & 1;
         ok = dev::mbar_wait(bar(kFullP + sp), pp, abort_flag, p.status, 401);
         if (!ok) break;
@@ -713,7 +804,8 @@ int launch_mode(const Launch& L) {
     case B2G_Q4_K: return launch_impl<B2G_Q4_K, MODE>(L);
     case B2G_Q8_0: return launch_impl<B2G_Q8_0, MODE>(L);
     case B2G_IQ2_XXS: return launch_impl<B2G_IQ2_XXS, MODE>(L);
-    default: return fail(B2G_E_ARG, "unsupported GGUF type id %d (supported: 8 Q8_0, 12 Q4_K, 16 IQ2_XXS)", L.qtype);
+    case B2G_Q6_K: return launch_impl<B2G_Q6_K, MODE>(L);
+    default: return fail(B2G_E_ARG, "unsupported GGUF type id %d (supported: 8 Q8_0, 12 Q4_K, 14 Q6_K, 16 IQ2_XXS)", L.qtype);
   }
 }
 
@@ -722,7 +814,7 @@ int check_common(const Launch& L, const char* what) {
               (long long)L.n, (long long)L.k);
   B2G_REQUIRE(L.k % 256 == 0, "%s: K=%lld must be a multiple of 256", what, (long long)L.k);
   B2G_REQUIRE(fmt::row_bytes(L.qtype, L.k) % 16 == 0,
-              "%s: packed rows of %lld bytes are not 16-byte multiples (IQ2_XXS needs K %% 2048 == 0 on this path)", what,
+              "%s: packed rows of %lld bytes are not 16-byte multiples (IQ2_XXS and Q6_K need K %% 2048 == 0 on this path)", what,
               (long long)fmt::row_bytes(L.qtype, L.k));
   B2G_REQUIRE(L.m_total < (1ll << 31) && (int64_t)L.num_experts * L.n < (1ll << 31), "%s: shape too large", what);
   B2G_REQUIRE(L.m_total == 0 || (L.a0 && L.w0 && L.out0), "%s: null pointer", what);

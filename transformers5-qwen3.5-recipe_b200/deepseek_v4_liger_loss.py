@@ -8,8 +8,8 @@ gradient is finished in the forward and only scaled in the backward.
 
 Differences from the reference: the cross-entropy kernel is this library's (``b2g_cross_entropy_inplace``) instead of
 Liger's Triton kernel; the count of non-ignored targets stays on the device (no ``.item()``); chunks are row views of the
-hidden states (the packed product accepts an offset view, so the per-chunk clone is gone).  Q8_0, Q4_K and IQ2_XXS heads
-are accepted (the reference validates Q8_0 here and Q6_K for Qwen; Q6_K is not a native type of this library yet).
+hidden states (the packed product accepts an offset view, so the per-chunk clone is gone).  Every native type of this
+library is accepted as the head's type here (the reference validates Q8_0 here and Q6_K in the Qwen twin, `gguf_liger_loss`).
 The model-forward patching of the reference (``_deepseek_v4_liger_forward``, ``apply_deepseek_v4_liger_loss``) is trainer
 glue and is not part of this path.
 """
@@ -119,7 +119,7 @@ def _packed_q8_liger_for_causal_lm_loss(hidden_states: torch.Tensor, lm_head, la
         raise RuntimeError("Packed DeepSeek Q8_0 LM-head loss hidden size does not match the LM head.")
     quant_type = int(lm_head.weight.quant_type)
     if quant_type not in _ops.NATIVE_QUANT_TYPES:
-        raise RuntimeError("Packed DeepSeek LM-head loss is validated only for Q8_0 weights (Q4_K and IQ2_XXS heads are also native here).")
+        raise RuntimeError("Packed DeepSeek LM-head loss is validated only for Q8_0 weights (the other native types of this library are accepted too).")
     if lm_head.weight.requires_grad:
         raise RuntimeError("Packed DeepSeek LM-head weights must remain frozen.")
 
