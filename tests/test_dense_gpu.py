@@ -33,6 +33,7 @@ def _case(qtype, m, n, k, r, seed, encoder="quantize"):
     (go.Q8_0, 300, 512, 1024, 16), (go.Q8_0, 129, 200, 512, 4),
     (go.IQ2_XXS, 260, 512, 2048, 8), (go.IQ2_XXS, 64, 300, 4096, 16),
     (go.Q6_K, 700, 512, 2048, 16), (go.Q6_K, 130, 264, 4096, 4), (go.Q6_K, 1, 8, 2048, 1),
+    (go.Q5_K, 600, 512, 1024, 16), (go.Q5_K, 77, 200, 256, 3),
 ])
 def test_fused_lora_linear_forward_backward(cuda, qtype, m, n, k, r):
     from b2g import autograd as ag

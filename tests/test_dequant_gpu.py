@@ -29,7 +29,7 @@ def test_golden_vectors_bit_exact(cuda, case):
     assert np.array_equal(_bits(got), want)
 
 
-@pytest.mark.parametrize("qtype", [go.Q8_0, go.Q4_K, go.IQ2_XXS, go.Q6_K])
+@pytest.mark.parametrize("qtype", [go.Q8_0, go.Q4_K, go.IQ2_XXS, go.Q6_K, go.Q5_K])
 @pytest.mark.parametrize("shape", [(1, 256), (37, 2048), (3, 5, 1024)])
 def test_encoded_and_random_payloads_bit_exact(cuda, qtype, shape):
     from b2g import ops

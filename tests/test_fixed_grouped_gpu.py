@@ -53,7 +53,7 @@ def test_deepseek_layout_equals_per_group_mmq_exactly(cuda):
 
 
 @pytest.mark.parametrize("qtype,groups,n,k,rows", [(go.Q4_K, 4, 512, 1024, 700), (go.Q8_0, 2, 48, 256, 33), (go.IQ2_XXS, 3, 256, 2048, 130),
-                                                  (go.Q6_K, 2, 256, 2048, 300)])
+                                                  (go.Q6_K, 2, 256, 2048, 300), (go.Q5_K, 3, 128, 512, 90)])
 def test_other_types_and_ragged_rows(cuda, qtype, groups, n, k, rows):
     from b2g import autograd as ag
 

@@ -21,7 +21,7 @@ def test_torch_encoders_match_oracle_encoders():
     w = torch.randn(32, 1024, generator=torch.Generator().manual_seed(1)) * 0.02
     assert np.array_equal(gguf_quant.quantize_q8_0(w).numpy(), go.quantize(w.numpy(), go.Q8_0))
     assert np.array_equal(gguf_quant.quantize_q4_k(w).numpy(), go.quantize(w.numpy(), go.Q4_K))
-    for qt in (8, 12, 14, 16):
+    for qt in (8, 12, 13, 14, 16):
         p = gguf_quant.random_payload(qt, (3, 2, 2048), 5)
         d = go.dequantize(p.numpy(), qt)
         assert np.isfinite(d).all() and 0.005 < d.std() < 0.06

@@ -16,7 +16,7 @@ def _payload(qtype, shape, seed):
     return go.quantize((np.random.default_rng(seed).standard_normal(shape) * 0.02).astype(np.float32), qtype)
 
 
-@pytest.mark.parametrize("qtype", [go.Q4_K, go.Q8_0])
+@pytest.mark.parametrize("qtype", [go.Q4_K, go.Q8_0, go.Q5_K])
 def test_grouped_ops_with_the_reference_fixture(cuda, qtype):
     """experts [0, 2, 5] with cumulative offsets [2, 5, 6] (test_fast_moe_lora.py:136-137)."""
     from b2g import autograd as ag
@@ -69,6 +69,7 @@ def test_constant_byte_iq2_xxs_payload_like_the_reference_test(cuda):
     (go.Q8_0, 8, 512, 256, 300, 2, 16, False),
     (go.IQ2_XXS, 4, 2048, 2048, 300, 2, 8, False),
     (go.Q6_K, 4, 2048, 2048, 700, 2, 16, False),
+    (go.Q5_K, 8, 512, 256, 300, 2, 8, False),
 ])
 def test_expert_layer_forward_backward(cuda, qtype, e, h, i, t, k, r, skew):
     from b2g import autograd as ag, routing

@@ -1,13 +1,15 @@
-// Device-side decoders for the GGUF block formats on the path: Q8_0, Q4_K, Q6_K, IQ2_XXS.
+// Device-side decoders for the GGUF block formats on the path: Q8_0, Q4_K, Q5_K, Q6_K, IQ2_XXS.
 //
 // The arithmetic reproduces the float32 decode of the public format definition bit for bit
 // after the final bf16 round-to-nearest-even:
 //   Q8_0    q * d                                 (19 significant bits: exact in fp32)
 //   Q4_K    (d*sc)*q - (dmin*m)                   (both products exact; the subtraction rounds once,
 //                                                  so a single fused multiply-add gives the same bits)
+//   Q5_K    as Q4_K with a fifth bit per value    (products of 17 and 22 significant bits: exact)
 //   Q6_K    (d*scale)*q                           (11 x 7, then x 6 significant bits: both products exact)
 //   IQ2_XXS d*(0.5+s4)*0.25 * grid * sign         (22 significant bits: exact in fp32)
 // Block layouts (bytes): Q8_0 34 = fp16 d | 32 x int8; Q4_K 144 = fp16 d | fp16 dmin | 12 scale bytes
+// | 128 nibble bytes; Q5_K 176 = the Q4_K header | 32 bytes of fifth bits (bit j of byte l: value l of sub-block j)
 // | 128 nibble bytes; Q6_K 210 = 128 low-nibble bytes | 64 high-pair bytes | 16 int8 scales | fp16 d;
 // IQ2_XXS 66 = fp16 d | 8 x (4 grid indices | u32: 4 x 7-bit signs + 4-bit scale).
 #pragma once
@@ -22,6 +24,7 @@ template <> struct Block<B2G_Q8_0> { static constexpr int kValues = 32, kBytes =
 template <> struct Block<B2G_Q4_K> { static constexpr int kValues = 256, kBytes = 144; };
 template <> struct Block<B2G_IQ2_XXS> { static constexpr int kValues = 256, kBytes = 66; };
 template <> struct Block<B2G_Q6_K> { static constexpr int kValues = 256, kBytes = 210; };
+template <> struct Block<B2G_Q5_K> { static constexpr int kValues = 256, kBytes = 176; };
 
 __host__ __device__ inline int64_t row_bytes(int qtype, int64_t k) {
   switch (qtype) {
@@ -29,6 +32,7 @@ __host__ __device__ inline int64_t row_bytes(int qtype, int64_t k) {
     case B2G_Q4_K: return k / 256 * 144;
     case B2G_IQ2_XXS: return k / 256 * 66;
     case B2G_Q6_K: return k / 256 * 210;
+    case B2G_Q5_K: return k / 256 * 176;
     default: return -1;
   }
 }
@@ -94,6 +98,30 @@ struct Decode8<B2G_Q4_K> {
     const uint2 w = *reinterpret_cast<const uint2*>(b + 16 + (sub >> 1) * 32 + (within & 31));
     const int shift = (sub & 1) * 4;
     const uint32_t w0 = (w.x >> shift) & 0x0F0F0F0Fu, w1 = (w.y >> shift) & 0x0F0F0F0Fu;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[i] = __fmaf_rn(dsc, byte_to_float(w0, i), -dm);
+      v[4 + i] = __fmaf_rn(dsc, byte_to_float(w1, i), -dm);
+    }
+  }
+};
+
+template <>
+struct Decode8<B2G_Q5_K> {
+  __device__ static __forceinline__ void run(const uint8_t* __restrict__ row, int k0, const uint2*, float (&v)[8]) {
+    const uint8_t* b = row + (k0 >> 8) * 176;  // 176-byte blocks keep 16-byte alignment
+    const uint4 hdr = *reinterpret_cast<const uint4*>(b);
+    const int within = k0 & 255;
+    const int sub = within >> 5;               // sub-block 0..7
+    uint32_t sc, mn;
+    q4k_scale_min(hdr.y, hdr.z, hdr.w, sub, sc, mn);
+    const float dsc = __fmul_rn(dev::half_bits_to_float(hdr.x), static_cast<float>(sc));
+    const float dm = __fmul_rn(dev::half_bits_to_float(hdr.x >> 16), static_cast<float>(mn));
+    const uint2 hb = *reinterpret_cast<const uint2*>(b + 16 + (within & 31));
+    const uint2 w = *reinterpret_cast<const uint2*>(b + 48 + (sub >> 1) * 32 + (within & 31));
+    const int shift = (sub & 1) * 4;
+    const uint32_t w0 = ((w.x >> shift) & 0x0F0F0F0Fu) | (((hb.x >> sub) & 0x01010101u) << 4);
+    const uint32_t w1 = ((w.y >> shift) & 0x0F0F0F0Fu) | (((hb.y >> sub) & 0x01010101u) << 4);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       v[i] = __fmaf_rn(dsc, byte_to_float(w0, i), -dm);

@@ -73,6 +73,11 @@ template <> struct Packed<B2G_Q8_0, kDgrad> { static constexpr int kBoxWords = 3
 // (the start is at most 14 bytes into the window).
 template <> struct Packed<B2G_IQ2_XXS, kFwd> { static constexpr int kBoxWords = 20, kBoxRows = 128, kBytes = 128 * 80, kSteps = 1; };
 template <> struct Packed<B2G_IQ2_XXS, kDgrad> { static constexpr int kBoxWords = 20, kBoxRows = 64, kBytes = 64 * 80, kSteps = 1; };
+// Q5_K: 176-byte super-blocks keep 16-byte alignment like Q4_K.  Forward: header, the 32 bytes of fifth bits (all eight
+// sub-blocks share them) and the 32 nibble bytes of one 64-value pair, as five [128 rows x 16 B] boxes.  Dgrad: whole
+// super-blocks of 64 rows (row stride 176 B = 11 x 16: conflict-free 16-byte loads).
+template <> struct Packed<B2G_Q5_K, kFwd> { static constexpr int kBoxWords = 4, kBoxRows = 128, kBytes = 5 * 2048, kSteps = 1; };
+template <> struct Packed<B2G_Q5_K, kDgrad> { static constexpr int kBoxWords = 44, kBoxRows = 64, kBytes = 64 * 176, kSteps = 1; };
 // Q6_K: 210-byte super-blocks start on any even byte of a 16-byte line.  A 64-value step uses, of its super-block, 64 bytes
 // of low nibbles, 32 bytes of high bit pairs, 4 scales and d; with the slack of the alignment that is ten 16-byte pieces
 // per row: five from the line below the nibbles, three below the bit pairs, two below the scales.  Each piece is one
@@ -161,6 +166,25 @@ __device__ __forceinline__ void q4k_half(const uint4 hdr, const uint4 qa, const 
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const uint32_t q = (w[i] >> shift) & 0x0F0F0F0Fu;  // bytes 4i..4i+3 -> values 4i..4i+3 of the sub-block
+    out[2 * i] = dev::pack_bf16(__fmaf_rn(dsc, fmt::byte_to_float(q, 0), ndm), __fmaf_rn(dsc, fmt::byte_to_float(q, 1), ndm));
+    out[2 * i + 1] = dev::pack_bf16(__fmaf_rn(dsc, fmt::byte_to_float(q, 2), ndm), __fmaf_rn(dsc, fmt::byte_to_float(q, 3), ndm));
+  }
+}
+
+// Q5_K: as q4k_half with the fifth bit of value l of sub-block j taken from bit j of the l-th fifth-bit byte.
+__device__ __forceinline__ void q5k_half(const uint4 hdr, const uint4 qa, const uint4 qb, const uint4 ha, const uint4 hb, int pair, int half,
+                                         uint32_t (&out)[16]) {
+  uint32_t sc, mn;
+  const int sub = 2 * pair + half;
+  fmt::q4k_scale_min(hdr.y, hdr.z, hdr.w, sub, sc, mn);
+  const float dsc = __fmul_rn(dev::half_bits_to_float(hdr.x), static_cast<float>(sc));
+  const float ndm = -__fmul_rn(dev::half_bits_to_float(hdr.x >> 16), static_cast<float>(mn));
+  const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+  const uint32_t h[8] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w};
+  const int shift = 4 * half;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t q = ((w[i] >> shift) & 0x0F0F0F0Fu) | (((h[i] >> sub) & 0x01010101u) << 4);
     out[2 * i] = dev::pack_bf16(__fmaf_rn(dsc, fmt::byte_to_float(q, 0), ndm), __fmaf_rn(dsc, fmt::byte_to_float(q, 1), ndm));
     out[2 * i + 1] = dev::pack_bf16(__fmaf_rn(dsc, fmt::byte_to_float(q, 2), ndm), __fmaf_rn(dsc, fmt::byte_to_float(q, 3), ndm));
   }
@@ -294,6 +318,7 @@ template <int QT> struct RowData;
 template <> struct RowData<B2G_Q4_K> { uint4 hdr, qa, qb; };
 template <> struct RowData<B2G_Q8_0> { uint32_t w[17]; };
 template <> struct RowData<B2G_IQ2_XXS> { float d; uint32_t idx4[2], word[2]; };
+template <> struct RowData<B2G_Q5_K> { uint4 hdr, qa, qb, ha, hb; };
 template <> struct RowData<B2G_Q6_K> { uint32_t ql[16], qh[8]; uint32_t sc4; float d; };   // 64 nibble bytes, 32 bit-pair bytes, 4 int8 scales
 
 template <int QT, int MODE>
@@ -308,6 +333,21 @@ __device__ __forceinline__ void load_row(uint32_t pk, int row, int pair, int it,
       rd.hdr = dev::lds128(r);
       rd.qa = dev::lds128(r + 16 + 32 * pair);
       rd.qb = dev::lds128(r + 32 + 32 * pair);
+    }
+  } else if constexpr (QT == B2G_Q5_K) {
+    if constexpr (MODE == kFwd) {
+      rd.hdr = dev::lds128(pk + row * 16);
+      rd.ha = dev::lds128(pk + 2048 + row * 16);
+      rd.hb = dev::lds128(pk + 4096 + row * 16);
+      rd.qa = dev::lds128(pk + 6144 + row * 16);
+      rd.qb = dev::lds128(pk + 8192 + row * 16);
+    } else {
+      const uint32_t r = pk + row * 176;
+      rd.hdr = dev::lds128(r);
+      rd.ha = dev::lds128(r + 16);
+      rd.hb = dev::lds128(r + 32);
+      rd.qa = dev::lds128(r + 48 + 32 * pair);
+      rd.qb = dev::lds128(r + 64 + 32 * pair);
     }
   } else if constexpr (QT == B2G_Q8_0) {
     if constexpr (MODE == kFwd) load_words_shifted<17>(pk + row * 80, (68 * it) & 15, rd.w);
@@ -361,6 +401,7 @@ template <int QT>
 __device__ __forceinline__ void decode_half(const RowData<QT>& rd, int pair, int half, uint32_t grid_s, uint32_t (&out)[16]) {
   if constexpr (QT == B2G_Q4_K) q4k_half(rd.hdr, rd.qa, rd.qb, pair, half, out);
   else if constexpr (QT == B2G_Q8_0) q8_half(rd.w, half, out);
+  else if constexpr (QT == B2G_Q5_K) q5k_half(rd.hdr, rd.qa, rd.qb, rd.ha, rd.hb, pair, half, out);
   else if constexpr (QT == B2G_Q6_K) q6k_half(rd.ql, rd.qh, rd.sc4, rd.d, pair, half, out);
   else iq2_half(rd.d, rd.idx4[half], rd.word[half], grid_s, out);
 }
@@ -608,6 +649,18 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
             for (int q = 0; q < 5; ++q) dev::tma_load_2d(dst + q * kPiece, wm, bar(kFullP + sp), x0 + 16 * h + 4 * q, y);
             for (int q = 0; q < 3; ++q) dev::tma_load_2d(dst + (5 + q) * kPiece, wm, bar(kFullP + sp), x0 + 32 + 8 * h + 4 * q, y);
             for (int q = 0; q < 2; ++q) dev::tma_load_2d(dst + (8 + q) * kPiece, wm, bar(kFullP + sp), x0 + 48 + 4 * q, y);
+          } else if (QT == B2G_Q5_K) {
+            if (MODE == kFwd) {
+              const int y = t.expert * p.n + col0 + static_cast<int>(rank) * kBNh;
+              const int xb = 44 * (it >> 2), xq = xb + 12 + 8 * (it & 3);
+              dev::tma_load_2d(dst, wm, bar(kFullP + sp), xb, y);                 // d, dmin, scales
+              dev::tma_load_2d(dst + 2048, wm, bar(kFullP + sp), xb + 4, y);      // fifth bits
+              dev::tma_load_2d(dst + 4096, wm, bar(kFullP + sp), xb + 8, y);
+              dev::tma_load_2d(dst + 6144, wm, bar(kFullP + sp), xq, y);          // nibbles of this pair
+              dev::tma_load_2d(dst + 8192, wm, bar(kFullP + sp), xq + 4, y);
+            } else {
+              dev::tma_load_2d(dst, wm, bar(kFullP + sp), 44 * t.ct, t.expert * p.n + red0);
+            }
           } else if (MODE == kFwd) {
             const int y = t.expert * p.n + col0 + static_cast<int>(rank) * kBNh;
             if (QT == B2G_Q4_K) {
@@ -804,8 +857,9 @@ int launch_mode(const Launch& L) {
     case B2G_Q4_K: return launch_impl<B2G_Q4_K, MODE>(L);
     case B2G_Q8_0: return launch_impl<B2G_Q8_0, MODE>(L);
     case B2G_IQ2_XXS: return launch_impl<B2G_IQ2_XXS, MODE>(L);
+    case B2G_Q5_K: return launch_impl<B2G_Q5_K, MODE>(L);
     case B2G_Q6_K: return launch_impl<B2G_Q6_K, MODE>(L);
-    default: return fail(B2G_E_ARG, "unsupported GGUF type id %d (supported: 8 Q8_0, 12 Q4_K, 14 Q6_K, 16 IQ2_XXS)", L.qtype);
+    default: return fail(B2G_E_ARG, "unsupported GGUF type id %d (supported: 8 Q8_0, 12 Q4_K, 13 Q5_K, 14 Q6_K, 16 IQ2_XXS)", L.qtype);
   }
 }
 
