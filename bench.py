@@ -299,7 +299,7 @@ def run_moe(args) -> int:
             "metric": "quantized MoE (grouped Q4_K experts + LoRA) fwd+bwd tokens/s", "value": t_total / (ms_step * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong" if world > 1 or t_total == 65536 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "grouped MoE Q4_K LoRA, 256 experts top-8, hidden 2048, intermediate 512 (BASELINE configs[%d])" % (4 if skew else 2),
+            "config": {"workload": "grouped MoE Q4_K LoRA, 256 experts top-8, hidden 2048, intermediate 512 (configuration %d of the benchmark specification)" % (4 if skew else 2),
                        "tokens_total": t_total, "experts_per_gpu": e_local, "skewed_router": skew,
                        "parallelism": (f"ep{world} (experts sharded, " + ("peer-store dispatch/combine over NVLink)" if use_peer else "NCCL all-to-all dispatch/combine)"))
                        if world > 1 else "1 GPU",
@@ -329,7 +329,7 @@ def main() -> int:
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     m = args.tokens
-    config = {"workload": "dense Q4_K LoRA linears, Qwen3.5-35B-A3B attention shapes (BASELINE configs[1])",
+    config = {"workload": "dense Q4_K LoRA linears, Qwen3.5-35B-A3B attention shapes (configuration 1 of the benchmark specification)",
               "K": K_DIM, "N": list(N_DIMS), "M_tokens_per_gpu": m, "lora_rank": RANK, "lora_alpha": ALPHA,
               "parallelism": f"replicas x{args.gpus} (dense path does not shard)", "l2": "inputs larger than L2 (X 128 MiB, dY up to 256 MiB)"}
 

@@ -35,7 +35,7 @@ def lora_linear_fwd_bwd(
 ) -> dict[str, torch.Tensor]:
     """Y, and with ``dy`` also dX, dA, dB, by the reference test's expressions.
 
-    ``compute_dtype=torch.float32`` gives the high-precision variant used to judge which
+    ``compute_dtype=torch.float32`` gives the high-precision variant used to decide which
     of two bf16 implementations is closer to the exact product.
     """
     xr = x.detach().to(compute_dtype).clone().requires_grad_(dy is not None)
