@@ -1,15 +1,17 @@
-// Device-side decoders for the GGUF block formats on the path: Q8_0, Q4_K, Q5_K, Q6_K, IQ2_XXS.
+// Device-side decoders for the GGUF block formats on the path: Q8_0, Q2_K, Q4_K, Q5_K, Q6_K, IQ2_XXS.
 //
 // The arithmetic reproduces the float32 decode of the public format definition bit for bit
 // after the final bf16 round-to-nearest-even:
 //   Q8_0    q * d                                 (19 significant bits: exact in fp32)
 //   Q4_K    (d*sc)*q - (dmin*m)                   (both products exact; the subtraction rounds once,
 //                                                  so a single fused multiply-add gives the same bits)
+//   Q2_K    (d*s)*q - (dmin*m), s and m 4-bit    (as Q4_K: both products exact, one fused multiply-add)
 //   Q5_K    as Q4_K with a fifth bit per value    (products of 17 and 22 significant bits: exact)
 //   Q6_K    (d*scale)*q                           (11 x 7, then x 6 significant bits: both products exact)
 //   IQ2_XXS d*(0.5+s4)*0.25 * grid * sign         (22 significant bits: exact in fp32)
 // Block layouts (bytes): Q8_0 34 = fp16 d | 32 x int8; Q4_K 144 = fp16 d | fp16 dmin | 12 scale bytes
-// | 128 nibble bytes; Q5_K 176 = the Q4_K header | 32 bytes of fifth bits (bit j of byte l: value l of sub-block j)
+// | 128 nibble bytes; Q2_K 84 = 16 scale bytes (scale | min << 4, one per 16 values) | 64 bytes of 2-bit values
+// | fp16 d | fp16 dmin; Q5_K 176 = the Q4_K header | 32 bytes of fifth bits (bit j of byte l: value l of sub-block j)
 // | 128 nibble bytes; Q6_K 210 = 128 low-nibble bytes | 64 high-pair bytes | 16 int8 scales | fp16 d;
 // IQ2_XXS 66 = fp16 d | 8 x (4 grid indices | u32: 4 x 7-bit signs + 4-bit scale).
 #pragma once
@@ -25,6 +27,7 @@ template <> struct Block<B2G_Q4_K> { static constexpr int kValues = 256, kBytes 
 template <> struct Block<B2G_IQ2_XXS> { static constexpr int kValues = 256, kBytes = 66; };
 template <> struct Block<B2G_Q6_K> { static constexpr int kValues = 256, kBytes = 210; };
 template <> struct Block<B2G_Q5_K> { static constexpr int kValues = 256, kBytes = 176; };
+template <> struct Block<B2G_Q2_K> { static constexpr int kValues = 256, kBytes = 84; };
 
 __host__ __device__ inline int64_t row_bytes(int qtype, int64_t k) {
   switch (qtype) {
@@ -33,6 +36,7 @@ __host__ __device__ inline int64_t row_bytes(int qtype, int64_t k) {
     case B2G_IQ2_XXS: return k / 256 * 66;
     case B2G_Q6_K: return k / 256 * 210;
     case B2G_Q5_K: return k / 256 * 176;
+    case B2G_Q2_K: return k / 256 * 84;
     default: return -1;
   }
 }
@@ -102,6 +106,26 @@ struct Decode8<B2G_Q4_K> {
     for (int i = 0; i < 4; ++i) {
       v[i] = __fmaf_rn(dsc, byte_to_float(w0, i), -dm);
       v[4 + i] = __fmaf_rn(dsc, byte_to_float(w1, i), -dm);
+    }
+  }
+};
+
+template <>
+struct Decode8<B2G_Q2_K> {
+  __device__ static __forceinline__ void run(const uint8_t* __restrict__ row, int k0, const uint2*, float (&v)[8]) {
+    const uint8_t* b = row + (k0 >> 8) * 84;   // 84-byte blocks are 4-byte aligned
+    const int within = k0 & 255;
+    const int h = within >> 7, t = (within >> 5) & 3, l = within & 31;   // half, 32-value group, position (multiple of 8)
+    const uint32_t s = b[within >> 4];
+    const uint32_t dd = *reinterpret_cast<const uint32_t*>(b + 80);
+    const float dl = __fmul_rn(dev::half_bits_to_float(dd), static_cast<float>(s & 15u));
+    const float ml = __fmul_rn(dev::half_bits_to_float(dd >> 16), static_cast<float>(s >> 4));
+    const uint32_t* qs = reinterpret_cast<const uint32_t*>(b + 16 + 32 * h + l);
+#pragma unroll
+    for (int w2 = 0; w2 < 2; ++w2) {
+      const uint32_t q = (qs[w2] >> (2 * t)) & 0x03030303u;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[4 * w2 + i] = __fmaf_rn(dl, byte_to_float(q, i), -ml);
     }
   }
 };

@@ -73,6 +73,12 @@ template <> struct Packed<B2G_Q8_0, kDgrad> { static constexpr int kBoxWords = 3
 // (the start is at most 14 bytes into the window).
 template <> struct Packed<B2G_IQ2_XXS, kFwd> { static constexpr int kBoxWords = 20, kBoxRows = 128, kBytes = 128 * 80, kSteps = 1; };
 template <> struct Packed<B2G_IQ2_XXS, kDgrad> { static constexpr int kBoxWords = 20, kBoxRows = 64, kBytes = 64 * 80, kSteps = 1; };
+// Q2_K: 84-byte super-blocks start on a multiple of 4 bytes of a 16-byte line.  A 64-value step uses 32 bytes of 2-bit values
+// (shared with the other step of the same 128-value half), four scale bytes and d | dmin: six 16-byte pieces per row with
+// the slack of the alignment (two from the line below the scales, three below the values, one holding d | dmin).  As for
+// Q6_K one forward slot serves the two steps that read the same bytes.
+template <> struct Packed<B2G_Q2_K, kFwd> { static constexpr int kBoxWords = 4, kBoxRows = 128, kBytes = 6 * 2048, kSteps = 2; };
+template <> struct Packed<B2G_Q2_K, kDgrad> { static constexpr int kBoxWords = 4, kBoxRows = 64, kBytes = 6 * 1024, kSteps = 1; };
 // Q5_K: 176-byte super-blocks keep 16-byte alignment like Q4_K.  Forward: header, the 32 bytes of fifth bits (all eight
 // sub-blocks share them) and the 32 nibble bytes of one 64-value pair, as five [128 rows x 16 B] boxes.  Dgrad: whole
 // super-blocks of 64 rows (row stride 176 B = 11 x 16: conflict-free 16-byte loads).
@@ -290,6 +296,23 @@ __device__ __forceinline__ void extract_words(const uint32_t (&raw)[NRAW], int s
   }
 }
 
+// Q2_K: 32 values of a 64-value slice; `j` = which quarter of the super-block (its parity picks bit pairs 0-1 or 2-3 of the
+// bytes), `half` = first or second 32 values (the next bit pair).  value = fma(d * scale, q, -(dmin * min)).
+__device__ __forceinline__ void q2k_half(const uint32_t (&qs)[8], uint32_t sc4, uint32_t dd, int j, int half, uint32_t (&out)[16]) {
+  const float d = dev::half_bits_to_float(dd), dmin = dev::half_bits_to_float(dd >> 16);
+  const uint32_t s0 = (sc4 >> (16 * half)) & 0xFFu, s1 = (sc4 >> (16 * half + 8)) & 0xFFu;   // scale bytes of values 0-15, 16-31
+  const float dl0 = __fmul_rn(d, static_cast<float>(s0 & 15u)), nm0 = -__fmul_rn(dmin, static_cast<float>(s0 >> 4));
+  const float dl1 = __fmul_rn(d, static_cast<float>(s1 & 15u)), nm1 = -__fmul_rn(dmin, static_cast<float>(s1 >> 4));
+  const int shift = 4 * (j & 1) + 2 * half;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t q = (qs[i] >> shift) & 0x03030303u;
+    const float dl = i < 4 ? dl0 : dl1, nm = i < 4 ? nm0 : nm1;
+    out[2 * i] = dev::pack_bf16(__fmaf_rn(dl, fmt::byte_to_float(q, 0), nm), __fmaf_rn(dl, fmt::byte_to_float(q, 1), nm));
+    out[2 * i + 1] = dev::pack_bf16(__fmaf_rn(dl, fmt::byte_to_float(q, 2), nm), __fmaf_rn(dl, fmt::byte_to_float(q, 3), nm));
+  }
+}
+
 // Q6_K: 32 values of a 64-value slice.  `j` = which quarter of the super-block the slice is (its parity picks the low or the
 // high nibbles and the bit pairs 0-3 or 4-7); `half` = first or second 32 values (nibble bytes 0-31 / 32-63, bit pair
 // 2*half of the nibble-parity's four).  value = (d * scale) * (q - 32), both products exact in fp32.
@@ -318,6 +341,7 @@ template <int QT> struct RowData;
 template <> struct RowData<B2G_Q4_K> { uint4 hdr, qa, qb; };
 template <> struct RowData<B2G_Q8_0> { uint32_t w[17]; };
 template <> struct RowData<B2G_IQ2_XXS> { float d; uint32_t idx4[2], word[2]; };
+template <> struct RowData<B2G_Q2_K> { uint32_t qs[8]; uint32_t sc4, dd; };   // 32 bytes of 2-bit values, 4 scale bytes, d | dmin
 template <> struct RowData<B2G_Q5_K> { uint4 hdr, qa, qb, ha, hb; };
 template <> struct RowData<B2G_Q6_K> { uint32_t ql[16], qh[8]; uint32_t sc4; float d; };   // 64 nibble bytes, 32 bit-pair bytes, 4 int8 scales
 
@@ -334,6 +358,21 @@ __device__ __forceinline__ void load_row(uint32_t pk, int row, int pair, int it,
       rd.qa = dev::lds128(r + 16 + 32 * pair);
       rd.qb = dev::lds128(r + 32 + 32 * pair);
     }
+  } else if constexpr (QT == B2G_Q2_K) {
+    constexpr uint32_t kPiece = (MODE == kFwd ? 128u : 64u) * 16u;
+    const int sb = MODE == kFwd ? (it >> 2) : ct;
+    const int sft = (84 * sb) & 15;                               // 0, 4, 8 or 12
+    const uint32_t base = pk + row * 16;
+    uint32_t raw[12];
+#pragma unroll
+    for (int q = 0; q < 3; ++q) {
+      const uint4 v = dev::lds128(base + (2 + q) * kPiece);
+      raw[4 * q] = v.x; raw[4 * q + 1] = v.y; raw[4 * q + 2] = v.z; raw[4 * q + 3] = v.w;
+    }
+    extract_words<8, 12>(raw, sft, rd.qs);
+    const int so = sft + 4 * pair;                                 // scales[4j .. 4j+3] inside the 32-byte scale window
+    rd.sc4 = dev::lds32(base + (so >> 4) * kPiece + (so & 15));
+    rd.dd = dev::lds32(base + 5 * kPiece + sft);
   } else if constexpr (QT == B2G_Q5_K) {
     if constexpr (MODE == kFwd) {
       rd.hdr = dev::lds128(pk + row * 16);
@@ -401,6 +440,7 @@ template <int QT>
 __device__ __forceinline__ void decode_half(const RowData<QT>& rd, int pair, int half, uint32_t grid_s, uint32_t (&out)[16]) {
   if constexpr (QT == B2G_Q4_K) q4k_half(rd.hdr, rd.qa, rd.qb, pair, half, out);
   else if constexpr (QT == B2G_Q8_0) q8_half(rd.w, half, out);
+  else if constexpr (QT == B2G_Q2_K) q2k_half(rd.qs, rd.sc4, rd.dd, pair, half, out);
   else if constexpr (QT == B2G_Q5_K) q5k_half(rd.hdr, rd.qa, rd.qb, rd.ha, rd.hb, pair, half, out);
   else if constexpr (QT == B2G_Q6_K) q6k_half(rd.ql, rd.qh, rd.sc4, rd.d, pair, half, out);
   else iq2_half(rd.d, rd.idx4[half], rd.word[half], grid_s, out);
@@ -649,6 +689,14 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
             for (int q = 0; q < 5; ++q) dev::tma_load_2d(dst + q * kPiece, wm, bar(kFullP + sp), x0 + 16 * h + 4 * q, y);
             for (int q = 0; q < 3; ++q) dev::tma_load_2d(dst + (5 + q) * kPiece, wm, bar(kFullP + sp), x0 + 32 + 8 * h + 4 * q, y);
             for (int q = 0; q < 2; ++q) dev::tma_load_2d(dst + (8 + q) * kPiece, wm, bar(kFullP + sp), x0 + 48 + 4 * q, y);
+          } else if (QT == B2G_Q2_K) {
+            const int sb = MODE == kFwd ? (it >> 2) : t.ct, h = MODE == kFwd ? ((it >> 1) & 1) : static_cast<int>(rank);
+            const int x0 = ((84 * sb) & ~15) >> 2;
+            const int y = MODE == kFwd ? t.expert * p.n + col0 + static_cast<int>(rank) * kBNh : t.expert * p.n + red0;
+            constexpr uint32_t kPiece = P::kBoxRows * 16;
+            for (int q = 0; q < 2; ++q) dev::tma_load_2d(dst + q * kPiece, wm, bar(kFullP + sp), x0 + 4 * q, y);                  // scales
+            for (int q = 0; q < 3; ++q) dev::tma_load_2d(dst + (2 + q) * kPiece, wm, bar(kFullP + sp), x0 + 4 + 8 * h + 4 * q, y);  // values of half h
+            dev::tma_load_2d(dst + 5 * kPiece, wm, bar(kFullP + sp), x0 + 20, y);                                                 // d | dmin
           } else if (QT == B2G_Q5_K) {
             if (MODE == kFwd) {
               const int y = t.expert * p.n + col0 + static_cast<int>(rank) * kBNh;
@@ -857,9 +905,10 @@ int launch_mode(const Launch& L) {
     case B2G_Q4_K: return launch_impl<B2G_Q4_K, MODE>(L);
     case B2G_Q8_0: return launch_impl<B2G_Q8_0, MODE>(L);
     case B2G_IQ2_XXS: return launch_impl<B2G_IQ2_XXS, MODE>(L);
+    case B2G_Q2_K: return launch_impl<B2G_Q2_K, MODE>(L);
     case B2G_Q5_K: return launch_impl<B2G_Q5_K, MODE>(L);
     case B2G_Q6_K: return launch_impl<B2G_Q6_K, MODE>(L);
-    default: return fail(B2G_E_ARG, "unsupported GGUF type id %d (supported: 8 Q8_0, 12 Q4_K, 13 Q5_K, 14 Q6_K, 16 IQ2_XXS)", L.qtype);
+    default: return fail(B2G_E_ARG, "unsupported GGUF type id %d (supported: 8 Q8_0, 10 Q2_K, 12 Q4_K, 13 Q5_K, 14 Q6_K, 16 IQ2_XXS)", L.qtype);
   }
 }
 
@@ -868,7 +917,7 @@ int check_common(const Launch& L, const char* what) {
               (long long)L.n, (long long)L.k);
   B2G_REQUIRE(L.k % 256 == 0, "%s: K=%lld must be a multiple of 256", what, (long long)L.k);
   B2G_REQUIRE(fmt::row_bytes(L.qtype, L.k) % 16 == 0,
-              "%s: packed rows of %lld bytes are not 16-byte multiples (IQ2_XXS and Q6_K need K %% 2048 == 0 on this path)", what,
+              "%s: packed rows of %lld bytes are not 16-byte multiples (IQ2_XXS and Q6_K need K %% 2048 == 0, Q2_K K %% 1024 == 0 on this path)", what,
               (long long)fmt::row_bytes(L.qtype, L.k));
   B2G_REQUIRE(L.m_total < (1ll << 31) && (int64_t)L.num_experts * L.n < (1ll << 31), "%s: shape too large", what);
   B2G_REQUIRE(L.m_total == 0 || (L.a0 && L.w0 && L.out0), "%s: null pointer", what);
