@@ -9,7 +9,7 @@
  *     allocates nothing: outputs and workspaces come from the caller.
  *   - bf16 activations / outputs, uint8 GGUF payloads in their on-disk block layout
  *     ([rows, K / block * block_bytes]); quant types use the GGML ids (8 = Q8_0, 10 = Q2_K,
- *     12 = Q4_K, 13 = Q5_K, 14 = Q6_K, 16 = IQ2_XXS).
+ *     11 = Q3_K, 12 = Q4_K, 13 = Q5_K, 14 = Q6_K, 16 = IQ2_XXS).
  *   - `status` (nullable) is a device int32 the kernels write a non-zero code into when a bounded
  *     device-side wait runs out; it is never written on a healthy run.
  *
@@ -42,6 +42,7 @@ extern "C" {
 #define B2G_Q6_K 14
 #define B2G_Q5_K 13
 #define B2G_Q2_K 10
+#define B2G_Q3_K 11
 
 #define B2G_LORA_PAD 16    /* LoRA rank operands are zero-padded to 16 columns / rows */
 

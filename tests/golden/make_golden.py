@@ -5,7 +5,7 @@ GGUF block formats the reference's dequantiser implements):
 
     python tests/golden/make_golden.py
 
-Payload sources: gguf-py's own Q8_0 encoder; this repository's oracle encoders for Q2_K, Q4_K, Q5_K, Q6_K and
+Payload sources: gguf-py's own Q8_0 encoder; this repository's oracle encoders for Q2_K, Q3_K, Q4_K, Q5_K, Q6_K and
 IQ2_XXS (gguf-py has none); uniformly random valid blocks; and the constant-byte payload of the
 reference's own grouped test (test_deepseek_v4_moe_lora.py:55-64: every byte = 32).  The answers
 always come from gguf.quants.dequantize, never from this repository's code.
@@ -40,6 +40,9 @@ def main() -> None:
         "q2_k_oracle_encoder": (go.Q2_K, go.quantize(w, go.Q2_K)),
         "q2_k_random": (go.Q2_K, go.random_payload(go.Q2_K, (6, 512), 6)),
         "q2_k_const32": (go.Q2_K, np.full((4, 84), 32, dtype=np.uint8)),
+        "q3_k_oracle_encoder": (go.Q3_K, go.quantize(w, go.Q3_K)),
+        "q3_k_random": (go.Q3_K, go.random_payload(go.Q3_K, (6, 512), 7)),
+        "q3_k_const32": (go.Q3_K, np.full((4, 110), 32, dtype=np.uint8)),
         "q5_k_oracle_encoder": (go.Q5_K, go.quantize(w, go.Q5_K)),
         "q5_k_random": (go.Q5_K, go.random_payload(go.Q5_K, (6, 512), 5)),
         "q5_k_const32": (go.Q5_K, np.full((4, 176), 32, dtype=np.uint8)),

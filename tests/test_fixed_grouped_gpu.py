@@ -53,7 +53,7 @@ def test_deepseek_layout_equals_per_group_mmq_exactly(cuda):
 
 
 @pytest.mark.parametrize("qtype,groups,n,k,rows", [(go.Q4_K, 4, 512, 1024, 700), (go.Q8_0, 2, 48, 256, 33), (go.IQ2_XXS, 3, 256, 2048, 130),
-                                                  (go.Q6_K, 2, 256, 2048, 300), (go.Q5_K, 3, 128, 512, 90), (go.Q2_K, 2, 128, 1024, 200)])
+                                                  (go.Q6_K, 2, 256, 2048, 300), (go.Q5_K, 3, 128, 512, 90), (go.Q2_K, 2, 128, 1024, 200), (go.Q3_K, 2, 256, 2048, 150)])
 def test_other_types_and_ragged_rows(cuda, qtype, groups, n, k, rows):
     from b2g import autograd as ag
 
@@ -78,6 +78,6 @@ def test_fail_closed(cuda):
     with pytest.raises(RuntimeError, match="contiguous"):
         ag.fixed_grouped_mmq(torch.zeros(2, 8, 8192, dtype=torch.bfloat16, device=cuda)[..., ::2], packed, 8)
     with pytest.raises(ValueError, match="not supported natively"):
-        ag.fixed_grouped_mmq(torch.zeros(2, 8, 4096, dtype=torch.bfloat16, device=cuda), packed, 11)
+        ag.fixed_grouped_mmq(torch.zeros(2, 8, 4096, dtype=torch.bfloat16, device=cuda), packed, 22)
     empty = ag.fixed_grouped_mmq(torch.zeros(0, 8, 4096, dtype=torch.bfloat16, device=cuda), packed, 8)
     assert empty.shape == (0, 8, 1024)

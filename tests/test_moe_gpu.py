@@ -71,6 +71,7 @@ def test_constant_byte_iq2_xxs_payload_like_the_reference_test(cuda):
     (go.Q6_K, 4, 2048, 2048, 700, 2, 16, False),
     (go.Q5_K, 8, 512, 256, 300, 2, 8, False),
     (go.Q2_K, 4, 1024, 1024, 400, 2, 8, False),
+    (go.Q3_K, 4, 2048, 2048, 300, 2, 8, False),
 ])
 def test_expert_layer_forward_backward(cuda, qtype, e, h, i, t, k, r, skew):
     from b2g import autograd as ag, routing

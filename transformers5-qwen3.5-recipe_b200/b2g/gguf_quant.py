@@ -67,7 +67,7 @@ def random_payload(qtype: int, shape: tuple[int, ...], seed: int, std: float = 0
     For IQ2_XXS this stands in for an encoder: every index/sign/sub-scale field is uniform and the
     fp16 block scale sets the magnitude.
     """
-    blk, nbytes = {8: (32, 34), 10: (256, 84), 12: (256, 144), 13: (256, 176), 14: (256, 210), 16: (256, 66)}[int(qtype)]
+    blk, nbytes = {8: (32, 34), 10: (256, 84), 11: (256, 110), 12: (256, 144), 13: (256, 176), 14: (256, 210), 16: (256, 66)}[int(qtype)]
     *lead, k = shape
     n = 1
     for v in lead:
@@ -84,6 +84,8 @@ def random_payload(qtype: int, shape: tuple[int, ...], seed: int, std: float = 0
     elif qtype == 10:
         b[:, 80:82] = _f16_bytes(std / 11.0 * jitter)
         b[:, 82:84] = _f16_bytes(std / 6.5 * jitter)
+    elif qtype == 11:
+        b[:, 108:110] = _f16_bytes(std / (18.5 * 2.3) * jitter)
     elif qtype == 13:
         b[:, 0:2] = _f16_bytes(std / 390.0 * jitter)
         b[:, 2:4] = _f16_bytes(std / 25.0 * jitter)

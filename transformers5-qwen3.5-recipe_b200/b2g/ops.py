@@ -14,9 +14,9 @@ import torch
 
 from . import _lib
 
-Q8_0, Q2_K, Q4_K, Q5_K, Q6_K, IQ2_XXS = 8, 10, 12, 13, 14, 16
-NATIVE_QUANT_TYPES = frozenset({Q8_0, Q2_K, Q4_K, Q5_K, Q6_K, IQ2_XXS})
-_BLOCK = {Q8_0: (32, 34), Q2_K: (256, 84), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210), IQ2_XXS: (256, 66)}
+Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, IQ2_XXS = 8, 10, 11, 12, 13, 14, 16
+NATIVE_QUANT_TYPES = frozenset({Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, IQ2_XXS})
+_BLOCK = {Q8_0: (32, 34), Q2_K: (256, 84), Q3_K: (256, 110), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210), IQ2_XXS: (256, 66)}
 LORA_PAD = 16
 
 
@@ -105,7 +105,7 @@ def ensure_iq2xxs_grid(device: torch.device) -> None:
 def _check_payload(payload: torch.Tensor, qtype: int, rows: int, k: int, what: str) -> None:
     _need(payload, torch.uint8, what)
     if int(qtype) not in NATIVE_QUANT_TYPES:
-        raise ValueError(f"GGML type {qtype} is not supported natively (supported: 8 Q8_0, 10 Q2_K, 12 Q4_K, 13 Q5_K, 14 Q6_K, 16 IQ2_XXS)")
+        raise ValueError(f"GGML type {qtype} is not supported natively (supported: 8 Q8_0, 10 Q2_K, 11 Q3_K, 12 Q4_K, 13 Q5_K, 14 Q6_K, 16 IQ2_XXS)")
     want = rows * payload_row_bytes(qtype, k)
     if payload.numel() != want:
         raise ValueError(f"{what} holds {payload.numel()} bytes, expected {want} for {rows} x {k} of type {qtype}")
@@ -243,7 +243,7 @@ def _fixed_group_geometry(a: torch.Tensor, payload: torch.Tensor, qtype: int, fo
         raise ValueError(f"activation has {a.shape[-2]} groups, the payload {groups}")
     block_values, block_bytes = _BLOCK[int(qtype)] if int(qtype) in NATIVE_QUANT_TYPES else (0, 0)
     if not block_values:
-        raise ValueError(f"GGML type {qtype} is not supported natively (supported: 8 Q8_0, 10 Q2_K, 12 Q4_K, 13 Q5_K, 14 Q6_K, 16 IQ2_XXS)")
+        raise ValueError(f"GGML type {qtype} is not supported natively (supported: 8 Q8_0, 10 Q2_K, 11 Q3_K, 12 Q4_K, 13 Q5_K, 14 Q6_K, 16 IQ2_XXS)")
     if row_bytes % block_bytes:
         raise ValueError(f"payload rows of {row_bytes} bytes are not whole blocks of type {qtype}")
     k = row_bytes // block_bytes * block_values

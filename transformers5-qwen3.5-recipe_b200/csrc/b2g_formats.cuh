@@ -1,4 +1,4 @@
-// Device-side decoders for the GGUF block formats on the path: Q8_0, Q2_K, Q4_K, Q5_K, Q6_K, IQ2_XXS.
+// Device-side decoders for the GGUF block formats on the path: Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, IQ2_XXS.
 //
 // The arithmetic reproduces the float32 decode of the public format definition bit for bit
 // after the final bf16 round-to-nearest-even:
@@ -6,12 +6,14 @@
 //   Q4_K    (d*sc)*q - (dmin*m)                   (both products exact; the subtraction rounds once,
 //                                                  so a single fused multiply-add gives the same bits)
 //   Q2_K    (d*s)*q - (dmin*m), s and m 4-bit    (as Q4_K: both products exact, one fused multiply-add)
+//   Q3_K    (d*scale)*q, 6-bit scales, q in -4..3 (11 x 6, then x 3 significant bits: both products exact)
 //   Q5_K    as Q4_K with a fifth bit per value    (products of 17 and 22 significant bits: exact)
 //   Q6_K    (d*scale)*q                           (11 x 7, then x 6 significant bits: both products exact)
 //   IQ2_XXS d*(0.5+s4)*0.25 * grid * sign         (22 significant bits: exact in fp32)
 // Block layouts (bytes): Q8_0 34 = fp16 d | 32 x int8; Q4_K 144 = fp16 d | fp16 dmin | 12 scale bytes
 // | 128 nibble bytes; Q2_K 84 = 16 scale bytes (scale | min << 4, one per 16 values) | 64 bytes of 2-bit values
-// | fp16 d | fp16 dmin; Q5_K 176 = the Q4_K header | 32 bytes of fifth bits (bit j of byte l: value l of sub-block j)
+// | fp16 d | fp16 dmin; Q3_K 110 = 32 mask bytes (bit g of byte l: group g, value l; CLEAR means minus 4) | 64 bytes of
+// 2-bit values | 12 bytes of packed 6-bit scales | fp16 d; Q5_K 176 = the Q4_K header | 32 bytes of fifth bits (bit j of byte l: value l of sub-block j)
 // | 128 nibble bytes; Q6_K 210 = 128 low-nibble bytes | 64 high-pair bytes | 16 int8 scales | fp16 d;
 // IQ2_XXS 66 = fp16 d | 8 x (4 grid indices | u32: 4 x 7-bit signs + 4-bit scale).
 #pragma once
@@ -28,6 +30,7 @@ template <> struct Block<B2G_IQ2_XXS> { static constexpr int kValues = 256, kByt
 template <> struct Block<B2G_Q6_K> { static constexpr int kValues = 256, kBytes = 210; };
 template <> struct Block<B2G_Q5_K> { static constexpr int kValues = 256, kBytes = 176; };
 template <> struct Block<B2G_Q2_K> { static constexpr int kValues = 256, kBytes = 84; };
+template <> struct Block<B2G_Q3_K> { static constexpr int kValues = 256, kBytes = 110; };
 
 __host__ __device__ inline int64_t row_bytes(int qtype, int64_t k) {
   switch (qtype) {
@@ -37,6 +40,7 @@ __host__ __device__ inline int64_t row_bytes(int qtype, int64_t k) {
     case B2G_Q6_K: return k / 256 * 210;
     case B2G_Q5_K: return k / 256 * 176;
     case B2G_Q2_K: return k / 256 * 84;
+    case B2G_Q3_K: return k / 256 * 110;
     default: return -1;
   }
 }
@@ -130,6 +134,39 @@ struct Decode8<B2G_Q2_K> {
   }
 };
 
+// Three-bit value (0..7) minus 4 / six-bit value minus 32 at byte i of `word` -> exact float.
+__device__ __forceinline__ float q3_to_float(uint32_t word, int i) {
+  const uint32_t magic = __byte_perm(word, 0x4B000000u, 0x7540u + i);
+  return __uint_as_float(magic) - 8388612.0f;  // 2^23 + 4
+}
+__device__ __forceinline__ float q6_to_float(uint32_t word, int i) {
+  const uint32_t magic = __byte_perm(word, 0x4B000000u, 0x7540u + i);
+  return __uint_as_float(magic) - 8388640.0f;  // 2^23 + 32
+}
+
+template <>
+struct Decode8<B2G_Q3_K> {
+  __device__ static __forceinline__ void run(const uint8_t* __restrict__ row, int k0, const uint2*, float (&v)[8]) {
+    const uint8_t* b = row + (k0 >> 8) * 110;  // 110-byte blocks are only 2-byte aligned
+    const int within = k0 & 255;
+    const int h = within >> 7, t = (within >> 5) & 3, l = within & 31, g = 4 * h + t, i = within >> 4;
+    const unsigned short* qs = reinterpret_cast<const unsigned short*>(b + 32 + 32 * h + l);
+    const unsigned short* hm = reinterpret_cast<const unsigned short*>(b + l);
+    const uint32_t s6 = ((static_cast<uint32_t>(b[96 + (i & 7)]) >> (4 * (i >> 3))) & 15u) |
+                        (((static_cast<uint32_t>(b[104 + (i & 3)]) >> (2 * (i >> 2))) & 3u) << 4);
+    const float d = dev::half_bits_to_float(*reinterpret_cast<const unsigned short*>(b + 108));
+    const float dl = __fmul_rn(d, static_cast<float>(static_cast<int>(s6) - 32));
+#pragma unroll
+    for (int w2 = 0; w2 < 2; ++w2) {
+      const uint32_t qw = static_cast<uint32_t>(qs[2 * w2]) | (static_cast<uint32_t>(qs[2 * w2 + 1]) << 16);
+      const uint32_t hw = static_cast<uint32_t>(hm[2 * w2]) | (static_cast<uint32_t>(hm[2 * w2 + 1]) << 16);
+      const uint32_t q = ((qw >> (2 * t)) & 0x03030303u) | (((hw >> g) & 0x01010101u) << 2);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[4 * w2 + e] = __fmul_rn(dl, q3_to_float(q, e));
+    }
+  }
+};
+
 template <>
 struct Decode8<B2G_Q5_K> {
   __device__ static __forceinline__ void run(const uint8_t* __restrict__ row, int k0, const uint2*, float (&v)[8]) {
@@ -153,12 +190,6 @@ struct Decode8<B2G_Q5_K> {
     }
   }
 };
-
-// Six-bit value minus 32 at byte i of `word` (bytes 0..63) -> exact float.
-__device__ __forceinline__ float q6_to_float(uint32_t word, int i) {
-  const uint32_t magic = __byte_perm(word, 0x4B000000u, 0x7540u + i);
-  return __uint_as_float(magic) - 8388640.0f;  // 2^23 + 32
-}
 
 template <>
 struct Decode8<B2G_Q6_K> {

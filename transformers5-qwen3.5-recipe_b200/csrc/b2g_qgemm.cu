@@ -79,6 +79,11 @@ template <> struct Packed<B2G_IQ2_XXS, kDgrad> { static constexpr int kBoxWords 
 // Q6_K one forward slot serves the two steps that read the same bytes.
 template <> struct Packed<B2G_Q2_K, kFwd> { static constexpr int kBoxWords = 4, kBoxRows = 128, kBytes = 6 * 2048, kSteps = 2; };
 template <> struct Packed<B2G_Q2_K, kDgrad> { static constexpr int kBoxWords = 4, kBoxRows = 64, kBytes = 6 * 1024, kSteps = 1; };
+// Q3_K: 110-byte super-blocks start on any even byte.  A step uses the 32 mask bytes, 32 bytes of 2-bit values (shared with
+// the other step of its half), the 12 scale bytes and d: eight pieces per row with the slack (three below the mask, three
+// below the values, two below the scales).  Forward slots serve step pairs as for Q6_K.
+template <> struct Packed<B2G_Q3_K, kFwd> { static constexpr int kBoxWords = 4, kBoxRows = 128, kBytes = 8 * 2048, kSteps = 2; };
+template <> struct Packed<B2G_Q3_K, kDgrad> { static constexpr int kBoxWords = 4, kBoxRows = 64, kBytes = 8 * 1024, kSteps = 1; };
 // Q5_K: 176-byte super-blocks keep 16-byte alignment like Q4_K.  Forward: header, the 32 bytes of fifth bits (all eight
 // sub-blocks share them) and the 32 nibble bytes of one 64-value pair, as five [128 rows x 16 B] boxes.  Dgrad: whole
 // super-blocks of 64 rows (row stride 176 B = 11 x 16: conflict-free 16-byte loads).
@@ -313,6 +318,23 @@ __device__ __forceinline__ void q2k_half(const uint32_t (&qs)[8], uint32_t sc4, 
   }
 }
 
+// Q3_K: 32 values of a 64-value slice; `j` = which quarter of the super-block, `half` = first or second 32 values.  Group
+// number g = 2j + half selects the mask bit, its parity within the half the bit pair of the value bytes.
+__device__ __forceinline__ void q3k_half(const uint32_t (&hm)[8], const uint32_t (&qs)[8], uint32_t sc_lo, uint32_t sc_hi, float d, int j,
+                                         int half, uint32_t (&out)[16]) {
+  const uint32_t s6 = ((sc_lo >> (4 * (j >> 1))) & 0x0F0F0F0Fu) | (((sc_hi >> (2 * j)) & 0x03030303u) << 4);   // scales 4j .. 4j+3, plus 32
+  const float dl0 = __fmul_rn(d, half ? fmt::q6_to_float(s6, 2) : fmt::q6_to_float(s6, 0));
+  const float dl1 = __fmul_rn(d, half ? fmt::q6_to_float(s6, 3) : fmt::q6_to_float(s6, 1));
+  const int g = 2 * j + half, shift = 2 * (g & 3);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t q = ((qs[i] >> shift) & 0x03030303u) | (((hm[i] >> g) & 0x01010101u) << 2);
+    const float dl = i < 4 ? dl0 : dl1;
+    out[2 * i] = dev::pack_bf16(__fmul_rn(dl, fmt::q3_to_float(q, 0)), __fmul_rn(dl, fmt::q3_to_float(q, 1)));
+    out[2 * i + 1] = dev::pack_bf16(__fmul_rn(dl, fmt::q3_to_float(q, 2)), __fmul_rn(dl, fmt::q3_to_float(q, 3)));
+  }
+}
+
 // Q6_K: 32 values of a 64-value slice.  `j` = which quarter of the super-block the slice is (its parity picks the low or the
 // high nibbles and the bit pairs 0-3 or 4-7); `half` = first or second 32 values (nibble bytes 0-31 / 32-63, bit pair
 // 2*half of the nibble-parity's four).  value = (d * scale) * (q - 32), both products exact in fp32.
@@ -342,6 +364,7 @@ template <> struct RowData<B2G_Q4_K> { uint4 hdr, qa, qb; };
 template <> struct RowData<B2G_Q8_0> { uint32_t w[17]; };
 template <> struct RowData<B2G_IQ2_XXS> { float d; uint32_t idx4[2], word[2]; };
 template <> struct RowData<B2G_Q2_K> { uint32_t qs[8]; uint32_t sc4, dd; };   // 32 bytes of 2-bit values, 4 scale bytes, d | dmin
+template <> struct RowData<B2G_Q3_K> { uint32_t hm[8], qs[8]; uint32_t sc_lo, sc_hi; float d; };   // mask, values, scale words
 template <> struct RowData<B2G_Q5_K> { uint4 hdr, qa, qb, ha, hb; };
 template <> struct RowData<B2G_Q6_K> { uint32_t ql[16], qh[8]; uint32_t sc4; float d; };   // 64 nibble bytes, 32 bit-pair bytes, 4 int8 scales
 
@@ -373,6 +396,31 @@ __device__ __forceinline__ void load_row(uint32_t pk, int row, int pair, int it,
     const int so = sft + 4 * pair;                                 // scales[4j .. 4j+3] inside the 32-byte scale window
     rd.sc4 = dev::lds32(base + (so >> 4) * kPiece + (so & 15));
     rd.dd = dev::lds32(base + 5 * kPiece + sft);
+  } else if constexpr (QT == B2G_Q3_K) {
+    constexpr uint32_t kPiece = (MODE == kFwd ? 128u : 64u) * 16u;
+    const int sb = MODE == kFwd ? (it >> 2) : ct;
+    const int sft = (110 * sb) & 15;                              // even
+    const uint32_t base = pk + row * 16;
+    uint32_t raw[12];
+#pragma unroll
+    for (int q = 0; q < 3; ++q) {
+      const uint4 v = dev::lds128(base + q * kPiece);
+      raw[4 * q] = v.x; raw[4 * q + 1] = v.y; raw[4 * q + 2] = v.z; raw[4 * q + 3] = v.w;
+    }
+    extract_words<8, 12>(raw, sft, rd.hm);
+#pragma unroll
+    for (int q = 0; q < 3; ++q) {
+      const uint4 v = dev::lds128(base + (3 + q) * kPiece);
+      raw[4 * q] = v.x; raw[4 * q + 1] = v.y; raw[4 * q + 2] = v.z; raw[4 * q + 3] = v.w;
+    }
+    extract_words<8, 12>(raw, sft, rd.qs);
+    // scale field (12 bytes) + d (2 bytes) start `sft` bytes into the last two pieces: low nibbles of scales 4j..4j+3 in its
+    // word j & 1, their high bit pairs in its word 2
+    auto win = [&](int byte) { return base + (6 + (byte >> 4)) * kPiece + (byte & 15); };
+    auto word_at = [&](int byte) { return dev::lds16(win(byte)) | (dev::lds16(win(byte + 2)) << 16); };
+    rd.sc_lo = word_at(sft + 4 * (pair & 1));
+    rd.sc_hi = word_at(sft + 8);
+    rd.d = dev::half_bits_to_float(dev::lds16(win(sft + 12)));
   } else if constexpr (QT == B2G_Q5_K) {
     if constexpr (MODE == kFwd) {
       rd.hdr = dev::lds128(pk + row * 16);
@@ -441,6 +489,7 @@ __device__ __forceinline__ void decode_half(const RowData<QT>& rd, int pair, int
   if constexpr (QT == B2G_Q4_K) q4k_half(rd.hdr, rd.qa, rd.qb, pair, half, out);
   else if constexpr (QT == B2G_Q8_0) q8_half(rd.w, half, out);
   else if constexpr (QT == B2G_Q2_K) q2k_half(rd.qs, rd.sc4, rd.dd, pair, half, out);
+  else if constexpr (QT == B2G_Q3_K) q3k_half(rd.hm, rd.qs, rd.sc_lo, rd.sc_hi, rd.d, pair, half, out);
   else if constexpr (QT == B2G_Q5_K) q5k_half(rd.hdr, rd.qa, rd.qb, rd.ha, rd.hb, pair, half, out);
   else if constexpr (QT == B2G_Q6_K) q6k_half(rd.ql, rd.qh, rd.sc4, rd.d, pair, half, out);
   else iq2_half(rd.d, rd.idx4[half], rd.word[half], grid_s, out);
@@ -697,6 +746,14 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
             for (int q = 0; q < 2; ++q) dev::tma_load_2d(dst + q * kPiece, wm, bar(kFullP + sp), x0 + 4 * q, y);                  // scales
             for (int q = 0; q < 3; ++q) dev::tma_load_2d(dst + (2 + q) * kPiece, wm, bar(kFullP + sp), x0 + 4 + 8 * h + 4 * q, y);  // values of half h
             dev::tma_load_2d(dst + 5 * kPiece, wm, bar(kFullP + sp), x0 + 20, y);                                                 // d | dmin
+          } else if (QT == B2G_Q3_K) {
+            const int sb = MODE == kFwd ? (it >> 2) : t.ct, h = MODE == kFwd ? ((it >> 1) & 1) : static_cast<int>(rank);
+            const int x0 = ((110 * sb) & ~15) >> 2;
+            const int y = MODE == kFwd ? t.expert * p.n + col0 + static_cast<int>(rank) * kBNh : t.expert * p.n + red0;
+            constexpr uint32_t kPiece = P::kBoxRows * 16;
+            for (int q = 0; q < 3; ++q) dev::tma_load_2d(dst + q * kPiece, wm, bar(kFullP + sp), x0 + 4 * q, y);                  // mask
+            for (int q = 0; q < 3; ++q) dev::tma_load_2d(dst + (3 + q) * kPiece, wm, bar(kFullP + sp), x0 + 8 + 8 * h + 4 * q, y);  // values of half h
+            for (int q = 0; q < 2; ++q) dev::tma_load_2d(dst + (6 + q) * kPiece, wm, bar(kFullP + sp), x0 + 24 + 4 * q, y);       // scales, d
           } else if (QT == B2G_Q5_K) {
             if (MODE == kFwd) {
               const int y = t.expert * p.n + col0 + static_cast<int>(rank) * kBNh;
@@ -906,9 +963,10 @@ int launch_mode(const Launch& L) {
     case B2G_Q8_0: return launch_impl<B2G_Q8_0, MODE>(L);
     case B2G_IQ2_XXS: return launch_impl<B2G_IQ2_XXS, MODE>(L);
     case B2G_Q2_K: return launch_impl<B2G_Q2_K, MODE>(L);
+    case B2G_Q3_K: return launch_impl<B2G_Q3_K, MODE>(L);
     case B2G_Q5_K: return launch_impl<B2G_Q5_K, MODE>(L);
     case B2G_Q6_K: return launch_impl<B2G_Q6_K, MODE>(L);
-    default: return fail(B2G_E_ARG, "unsupported GGUF type id %d (supported: 8 Q8_0, 10 Q2_K, 12 Q4_K, 13 Q5_K, 14 Q6_K, 16 IQ2_XXS)", L.qtype);
+    default: return fail(B2G_E_ARG, "unsupported GGUF type id %d (supported: 8 Q8_0, 10 Q2_K, 11 Q3_K, 12 Q4_K, 13 Q5_K, 14 Q6_K, 16 IQ2_XXS)", L.qtype);
   }
 }
 
@@ -917,7 +975,7 @@ int check_common(const Launch& L, const char* what) {
               (long long)L.n, (long long)L.k);
   B2G_REQUIRE(L.k % 256 == 0, "%s: K=%lld must be a multiple of 256", what, (long long)L.k);
   B2G_REQUIRE(fmt::row_bytes(L.qtype, L.k) % 16 == 0,
-              "%s: packed rows of %lld bytes are not 16-byte multiples (IQ2_XXS and Q6_K need K %% 2048 == 0, Q2_K K %% 1024 == 0 on this path)", what,
+              "%s: packed rows of %lld bytes are not 16-byte multiples (IQ2_XXS, Q3_K and Q6_K need K %% 2048 == 0, Q2_K K %% 1024 == 0 on this path)", what,
               (long long)fmt::row_bytes(L.qtype, L.k));
   B2G_REQUIRE(L.m_total < (1ll << 31) && (int64_t)L.num_experts * L.n < (1ll << 31), "%s: shape too large", what);
   B2G_REQUIRE(L.m_total == 0 || (L.a0 && L.w0 && L.out0), "%s: null pointer", what);
