@@ -9,7 +9,7 @@
  *     allocates nothing: outputs and workspaces come from the caller.
  *   - bf16 activations / outputs, uint8 GGUF payloads in their on-disk block layout
  *     ([rows, K / block * block_bytes]); quant types use the GGML ids (8 = Q8_0, 10 = Q2_K,
- *     11 = Q3_K, 12 = Q4_K, 13 = Q5_K, 14 = Q6_K, 16 = IQ2_XXS).
+ *     11 = Q3_K, 12 = Q4_K, 13 = Q5_K, 14 = Q6_K, 16 = IQ2_XXS, 22 = IQ2_S).
  *   - `status` (nullable) is a device int32 the kernels write a non-zero code into when a bounded
  *     device-side wait runs out; it is never written on a healthy run.
  *
@@ -43,6 +43,7 @@ extern "C" {
 #define B2G_Q5_K 13
 #define B2G_Q2_K 10
 #define B2G_Q3_K 11
+#define B2G_IQ2_S 22
 
 #define B2G_LORA_PAD 16    /* LoRA rank operands are zero-padded to 16 columns / rows */
 
@@ -53,6 +54,10 @@ B2G_API int b2g_abi_version(void);
  * The table is third-party data owned by the gguf package; the caller reads it from there
  * (gguf.quants.IQ2_XXS.grid) and hands it in once per device before any IQ2_XXS call. */
 B2G_API int b2g_set_iq2xxs_grid(const uint8_t* host_grid_256x8);
+
+/* The same for IQ2_S (type 22 of the reference's allow-list, fast_lora.py:24-27): its 1024 rows x 8 bytes table
+ * (gguf.quants.IQ2_S.grid), once per device before any IQ2_S call. */
+B2G_API int b2g_set_iq2s_grid(const uint8_t* host_grid_1024x8);
 
 /* Logical bf16 weight from a packed payload, bit-exact with float32 decode + round-to-nearest-even.
  * Replaces transformers.integrations.gguf_dequant.dequantize_gguf_tensor as used at

@@ -43,6 +43,9 @@ def main() -> None:
         "q3_k_oracle_encoder": (go.Q3_K, go.quantize(w, go.Q3_K)),
         "q3_k_random": (go.Q3_K, go.random_payload(go.Q3_K, (6, 512), 7)),
         "q3_k_const32": (go.Q3_K, np.full((4, 110), 32, dtype=np.uint8)),
+        "iq2_s_oracle_encoder": (go.IQ2_S, go.quantize(w, go.IQ2_S)),
+        "iq2_s_random": (go.IQ2_S, go.random_payload(go.IQ2_S, (6, 512), 8)),
+        "iq2_s_const32": (go.IQ2_S, np.full((4, 82), 32, dtype=np.uint8)),
         "q5_k_oracle_encoder": (go.Q5_K, go.quantize(w, go.Q5_K)),
         "q5_k_random": (go.Q5_K, go.random_payload(go.Q5_K, (6, 512), 5)),
         "q5_k_const32": (go.Q5_K, np.full((4, 176), 32, dtype=np.uint8)),

@@ -36,6 +36,7 @@ def _case(qtype, m, n, k, r, seed, encoder="quantize"):
     (go.Q5_K, 600, 512, 1024, 16), (go.Q5_K, 77, 200, 256, 3),
     (go.Q2_K, 600, 512, 1024, 16), (go.Q2_K, 300, 264, 3072, 5),
     (go.Q3_K, 600, 512, 2048, 16), (go.Q3_K, 70, 136, 4096, 2),
+    (go.IQ2_S, 400, 512, 2048, 16), (go.IQ2_S, 70, 72, 4096, 2),
 ])
 def test_fused_lora_linear_forward_backward(cuda, qtype, m, n, k, r):
     from b2g import autograd as ag

@@ -29,7 +29,7 @@ def test_golden_vectors_bit_exact(cuda, case):
     assert np.array_equal(_bits(got), want)
 
 
-@pytest.mark.parametrize("qtype", [go.Q8_0, go.Q4_K, go.IQ2_XXS, go.Q6_K, go.Q5_K, go.Q2_K, go.Q3_K])
+@pytest.mark.parametrize("qtype", [go.Q8_0, go.Q4_K, go.IQ2_XXS, go.Q6_K, go.Q5_K, go.Q2_K, go.Q3_K, go.IQ2_S])
 @pytest.mark.parametrize("shape", [(1, 256), (37, 2048), (3, 5, 1024)])
 def test_encoded_and_random_payloads_bit_exact(cuda, qtype, shape):
     from b2g import ops
@@ -60,4 +60,4 @@ def test_empty_and_bad_arguments(cuda):
     with pytest.raises(ValueError):
         ops.dequantize(torch.zeros(100, dtype=torch.uint8, device=cuda), go.Q4_K, (1, 256))
     with pytest.raises(ValueError):
-        ops.dequantize(torch.zeros(82, dtype=torch.uint8, device=cuda), 22, (1, 256))  # IQ2_S: not native here
+        ops.dequantize(torch.zeros(144, dtype=torch.uint8, device=cuda), 2, (1, 256))  # Q4_0: not native here

@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 def _grouped_case(m_shape, groups, n, k, qtype, seed, cuda):
     rng = np.random.default_rng(seed)
     logical = (rng.standard_normal((groups * n, k)) * 0.05).astype(np.float32)
-    payload = go.quantize(logical, qtype) if qtype != go.IQ2_XXS else go.random_payload(qtype, (groups * n, k), seed)
+    payload = go.quantize(logical, qtype) if qtype not in (go.IQ2_XXS, go.IQ2_S) else go.random_payload(qtype, (groups * n, k), seed)
     g = torch.Generator().manual_seed(seed)
     x = torch.randn(*m_shape, groups, k, generator=g).bfloat16()
     dy = torch.randn(*m_shape, groups, n, generator=g).bfloat16()
@@ -53,7 +53,7 @@ def test_deepseek_layout_equals_per_group_mmq_exactly(cuda):
 
 
 @pytest.mark.parametrize("qtype,groups,n,k,rows", [(go.Q4_K, 4, 512, 1024, 700), (go.Q8_0, 2, 48, 256, 33), (go.IQ2_XXS, 3, 256, 2048, 130),
-                                                  (go.Q6_K, 2, 256, 2048, 300), (go.Q5_K, 3, 128, 512, 90), (go.Q2_K, 2, 128, 1024, 200), (go.Q3_K, 2, 256, 2048, 150)])
+                                                  (go.Q6_K, 2, 256, 2048, 300), (go.Q5_K, 3, 128, 512, 90), (go.Q2_K, 2, 128, 1024, 200), (go.Q3_K, 2, 256, 2048, 150), (go.IQ2_S, 2, 128, 2048, 100)])
 def test_other_types_and_ragged_rows(cuda, qtype, groups, n, k, rows):
     from b2g import autograd as ag
 
@@ -78,6 +78,6 @@ def test_fail_closed(cuda):
     with pytest.raises(RuntimeError, match="contiguous"):
         ag.fixed_grouped_mmq(torch.zeros(2, 8, 8192, dtype=torch.bfloat16, device=cuda)[..., ::2], packed, 8)
     with pytest.raises(ValueError, match="not supported natively"):
-        ag.fixed_grouped_mmq(torch.zeros(2, 8, 4096, dtype=torch.bfloat16, device=cuda), packed, 22)
+        ag.fixed_grouped_mmq(torch.zeros(2, 8, 4096, dtype=torch.bfloat16, device=cuda), packed, 2)
     empty = ag.fixed_grouped_mmq(torch.zeros(0, 8, 4096, dtype=torch.bfloat16, device=cuda), packed, 8)
     assert empty.shape == (0, 8, 1024)

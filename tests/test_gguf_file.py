@@ -28,11 +28,11 @@ def small_file(tmp_path_factory):
     dense = go.quantize((rng.standard_normal((24, 2048)) * 0.05).astype(np.float32), go.Q6_K)
     bank = go.quantize((rng.standard_normal((3, 16, 512)) * 0.05).astype(np.float32), go.Q4_K)
     q8 = go.quantize((rng.standard_normal((40, 256)) * 0.05).astype(np.float32), go.Q8_0)
-    other = np.zeros((4, 82), dtype=np.uint8)                                    # IQ2_S: not native
+    other = np.zeros((4, 144), dtype=np.uint8)                                   # Q4_0: not native
     norm = rng.standard_normal(64).astype(np.float32)
     path = tmp_path_factory.mktemp("gguf") / "tiny.gguf"
     _write(path, {"output.weight": (dense, go.Q6_K, (24, 2048)), "blk.0.ffn_gate_exps.weight": (bank, go.Q4_K, (3, 16, 512)),
-                  "blk.0.attn_q.weight": (q8, go.Q8_0, (40, 256)), "blk.0.odd.weight": (other, 22, (4, 256)),
+                  "blk.0.attn_q.weight": (q8, go.Q8_0, (40, 256)), "blk.0.odd.weight": (other, 2, (4, 256)),
                   "blk.0.attn_norm.weight": (norm, None, (64,))})
     return path, {"dense": dense, "bank": bank, "q8": q8, "norm": norm}
 
@@ -57,7 +57,7 @@ def test_round_trip_bytes_types_and_shapes(small_file):
         gguf_file.load_tensor(path, "blk.0.odd.weight", "cpu")
     with pytest.raises(KeyError):
         gguf_file.load_tensor(path, "missing", "cpu")
-    assert gguf_file.type_census(path) == {go.Q6_K: 1, go.Q4_K: 1, go.Q8_0: 1, 22: 1, 0: 1}
+    assert gguf_file.type_census(path) == {go.Q6_K: 1, go.Q4_K: 1, go.Q8_0: 1, 2: 1, 0: 1}
     names = [n for n, _ in gguf_file.iter_tensors(path, "cpu", skip_unsupported=True)]
     assert "blk.0.odd.weight" not in names and len(names) == 4
 

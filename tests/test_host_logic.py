@@ -21,7 +21,7 @@ def test_torch_encoders_match_oracle_encoders():
     w = torch.randn(32, 1024, generator=torch.Generator().manual_seed(1)) * 0.02
     assert np.array_equal(gguf_quant.quantize_q8_0(w).numpy(), go.quantize(w.numpy(), go.Q8_0))
     assert np.array_equal(gguf_quant.quantize_q4_k(w).numpy(), go.quantize(w.numpy(), go.Q4_K))
-    for qt in (8, 10, 11, 12, 13, 14, 16):
+    for qt in (8, 10, 11, 12, 13, 14, 16, 22):
         p = gguf_quant.random_payload(qt, (3, 2, 2048), 5)
         d = go.dequantize(p.numpy(), qt)
         assert np.isfinite(d).all() and 0.005 < d.std() < 0.06
@@ -201,7 +201,7 @@ def test_packed_lm_head_loss_argument_contract():
             dl.deepseek_v4_packed_liger_causal_lm_loss(h[None], head, labels, hidden_size=256, loss_kwargs=kw)
     with pytest.raises(RuntimeError, match="hidden size does not match"):
         dl.deepseek_v4_packed_liger_causal_lm_loss(h[None], head, labels, hidden_size=128)
-    head.weight = GGUFQuantizedTensor(torch.zeros(37, 82, dtype=torch.uint8), quant_type=22, logical_shape=(37, 256))   # IQ2_S
+    head.weight = GGUFQuantizedTensor(torch.zeros(37, 144, dtype=torch.uint8), quant_type=2, logical_shape=(37, 256))   # Q4_0
     with pytest.raises(RuntimeError, match="validated only for Q8_0"):
         dl.deepseek_v4_packed_liger_causal_lm_loss(h[None], head, labels, hidden_size=256)
 

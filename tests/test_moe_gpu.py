@@ -11,7 +11,7 @@ TOL = 1e-2
 
 
 def _payload(qtype, shape, seed):
-    if qtype == go.IQ2_XXS:
+    if qtype in (go.IQ2_XXS, go.IQ2_S):
         return go.random_payload(qtype, shape, seed)
     return go.quantize((np.random.default_rng(seed).standard_normal(shape) * 0.02).astype(np.float32), qtype)
 
@@ -72,6 +72,7 @@ def test_constant_byte_iq2_xxs_payload_like_the_reference_test(cuda):
     (go.Q5_K, 8, 512, 256, 300, 2, 8, False),
     (go.Q2_K, 4, 1024, 1024, 400, 2, 8, False),
     (go.Q3_K, 4, 2048, 2048, 300, 2, 8, False),
+    (go.IQ2_S, 4, 2048, 2048, 300, 2, 8, False),
 ])
 def test_expert_layer_forward_backward(cuda, qtype, e, h, i, t, k, r, skew):
     from b2g import autograd as ag, routing

@@ -24,7 +24,7 @@ def test_sign_table_matches_golden():
     assert np.array_equal(go.iq2xxs_signs_u8(), GOLDEN["iq2_xxs_ksigns"])
 
 
-@pytest.mark.parametrize("qtype", [go.Q8_0, go.Q4_K, go.IQ2_XXS, go.Q6_K, go.Q5_K, go.Q2_K, go.Q3_K])
+@pytest.mark.parametrize("qtype", [go.Q8_0, go.Q4_K, go.IQ2_XXS, go.Q6_K, go.Q5_K, go.Q2_K, go.Q3_K, go.IQ2_S])
 def test_oracle_matches_gguf_py_live(qtype):
     gguf = pytest.importorskip("gguf")
     from gguf import quants as gq
@@ -44,7 +44,7 @@ def test_q8_encoder_is_gguf_py_encoder():
     assert np.array_equal(go.quantize(w, go.Q8_0), gq.quantize(w, gguf.GGMLQuantizationType.Q8_0))
 
 
-@pytest.mark.parametrize("qtype,tol", [(go.Q8_0, 0.01), (go.Q4_K, 0.12), (go.IQ2_XXS, 0.5), (go.Q6_K, 0.03), (go.Q5_K, 0.06), (go.Q2_K, 0.45), (go.Q3_K, 0.25)])
+@pytest.mark.parametrize("qtype,tol", [(go.Q8_0, 0.01), (go.Q4_K, 0.12), (go.IQ2_XXS, 0.5), (go.Q6_K, 0.03), (go.Q5_K, 0.06), (go.Q2_K, 0.45), (go.Q3_K, 0.25), (go.IQ2_S, 0.45)])
 def test_encoders_round_trip(qtype, tol):
     w = (np.random.default_rng(5).standard_normal((8, 2048)) * 0.02).astype(np.float32)
     p = go.quantize(w, qtype)

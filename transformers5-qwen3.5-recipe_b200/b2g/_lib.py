@@ -16,6 +16,7 @@ SIGNATURES = {
     "b2g_last_error": (C.c_char_p, []),
     "b2g_abi_version": (_i32, []),
     "b2g_set_iq2xxs_grid": (_i32, [_vp]),
+    "b2g_set_iq2s_grid": (_i32, [_vp]),
     "b2g_dequant": (_i32, [_i32, _vp, _i64, _i64, _vp, _vp]),
     "b2g_qlinear_fwd": (_i32, [_i32, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp]),
     "b2g_qlinear_dgrad": (_i32, [_i32, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp]),

@@ -67,7 +67,7 @@ def random_payload(qtype: int, shape: tuple[int, ...], seed: int, std: float = 0
     For IQ2_XXS this stands in for an encoder: every index/sign/sub-scale field is uniform and the
     fp16 block scale sets the magnitude.
     """
-    blk, nbytes = {8: (32, 34), 10: (256, 84), 11: (256, 110), 12: (256, 144), 13: (256, 176), 14: (256, 210), 16: (256, 66)}[int(qtype)]
+    blk, nbytes = {8: (32, 34), 10: (256, 84), 11: (256, 110), 12: (256, 144), 13: (256, 176), 14: (256, 210), 16: (256, 66), 22: (256, 82)}[int(qtype)]
     *lead, k = shape
     n = 1
     for v in lead:

@@ -14,9 +14,9 @@ import torch
 
 from . import _lib
 
-Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, IQ2_XXS = 8, 10, 11, 12, 13, 14, 16
-NATIVE_QUANT_TYPES = frozenset({Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, IQ2_XXS})
-_BLOCK = {Q8_0: (32, 34), Q2_K: (256, 84), Q3_K: (256, 110), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210), IQ2_XXS: (256, 66)}
+Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, IQ2_XXS, IQ2_S = 8, 10, 11, 12, 13, 14, 16, 22
+NATIVE_QUANT_TYPES = frozenset({Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, IQ2_XXS, IQ2_S})
+_BLOCK = {Q8_0: (32, 34), Q2_K: (256, 84), Q3_K: (256, 110), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210), IQ2_XXS: (256, 66), IQ2_S: (256, 82)}
 LORA_PAD = 16
 
 
@@ -102,10 +102,28 @@ def ensure_iq2xxs_grid(device: torch.device) -> None:
     _grid_done.add(idx)
 
 
+_grid_s_done: set[int] = set()
+
+
+def ensure_iq2s_grid(device: torch.device) -> None:
+    """The same for IQ2_S and its 1024-row table."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx in _grid_s_done:
+        return
+    import numpy as np
+    from gguf import quants as gq
+
+    gq.IQ2_S.init_grid()
+    grid = np.ascontiguousarray(np.asarray(gq.IQ2_S.grid, dtype=np.float32).reshape(1024, 8).astype(np.uint8))
+    with torch.cuda.device(idx):
+        _lib.call("b2g_set_iq2s_grid", C.c_void_p(grid.ctypes.data))
+    _grid_s_done.add(idx)
+
+
 def _check_payload(payload: torch.Tensor, qtype: int, rows: int, k: int, what: str) -> None:
     _need(payload, torch.uint8, what)
     if int(qtype) not in NATIVE_QUANT_TYPES:
-        raise ValueError(f"GGML type {qtype} is not supported natively (supported: 8 Q8_0, 10 Q2_K, 11 Q3_K, 12 Q4_K, 13 Q5_K, 14 Q6_K, 16 IQ2_XXS)")
+        raise ValueError(f"GGML type {qtype} is not supported natively (supported: 8 Q8_0, 10 Q2_K, 11 Q3_K, 12 Q4_K, 13 Q5_K, 14 Q6_K, 16 IQ2_XXS, 22 IQ2_S)")
     want = rows * payload_row_bytes(qtype, k)
     if payload.numel() != want:
         raise ValueError(f"{what} holds {payload.numel()} bytes, expected {want} for {rows} x {k} of type {qtype}")
@@ -113,6 +131,8 @@ def _check_payload(payload: torch.Tensor, qtype: int, rows: int, k: int, what: s
         raise RuntimeError(f"{what} must be 16-byte aligned")
     if int(qtype) == IQ2_XXS:
         ensure_iq2xxs_grid(payload.device)
+    if int(qtype) == IQ2_S:
+        ensure_iq2s_grid(payload.device)
 
 
 # --------------------------------------------------------------------------------------
@@ -243,7 +263,7 @@ def _fixed_group_geometry(a: torch.Tensor, payload: torch.Tensor, qtype: int, fo
         raise ValueError(f"activation has {a.shape[-2]} groups, the payload {groups}")
     block_values, block_bytes = _BLOCK[int(qtype)] if int(qtype) in NATIVE_QUANT_TYPES else (0, 0)
     if not block_values:
-        raise ValueError(f"GGML type {qtype} is not supported natively (supported: 8 Q8_0, 10 Q2_K, 11 Q3_K, 12 Q4_K, 13 Q5_K, 14 Q6_K, 16 IQ2_XXS)")
+        raise ValueError(f"GGML type {qtype} is not supported natively (supported: 8 Q8_0, 10 Q2_K, 11 Q3_K, 12 Q4_K, 13 Q5_K, 14 Q6_K, 16 IQ2_XXS, 22 IQ2_S)")
     if row_bytes % block_bytes:
         raise ValueError(f"payload rows of {row_bytes} bytes are not whole blocks of type {qtype}")
     k = row_bytes // block_bytes * block_values

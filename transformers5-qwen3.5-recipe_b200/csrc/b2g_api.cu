@@ -71,6 +71,21 @@ int iq2xxs_grid(const uint2** out) {
   return 0;
 }
 
+// IQ2_S magnitude table (1024 rows), likewise.
+__device__ uint2 g_iq2s_grid[1024];
+static bool g_grid_s_ready[64] = {false};
+
+int iq2s_grid(const uint2** out) {
+  int dev = 0;
+  B2G_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !g_grid_s_ready[dev])
+    return fail(B2G_E_STATE, "IQ2_S grid not uploaded on device %d: call b2g_set_iq2s_grid first", dev);
+  void* p = nullptr;
+  B2G_CUDA_OK(cudaGetSymbolAddress(&p, g_iq2s_grid));
+  *out = static_cast<const uint2*>(p);
+  return 0;
+}
+
 }  // namespace b2g
 
 extern "C" {
@@ -89,6 +104,20 @@ int b2g_set_iq2xxs_grid(const uint8_t* host_grid_256x8) {
   B2G_REQUIRE(dev >= 0 && dev < 64, "device index %d out of range", dev);
   B2G_CUDA_OK(cudaMemcpyToSymbol(b2g::g_iq2xxs_grid, host_grid_256x8, 2048));
   b2g::g_grid_ready[dev] = true;
+  return 0;
+}
+
+int b2g_set_iq2s_grid(const uint8_t* host_grid_1024x8) {
+  B2G_REQUIRE(host_grid_1024x8 != nullptr, "grid pointer is null");
+  for (int i = 0; i < 8192; ++i) {
+    const uint8_t v = host_grid_1024x8[i];
+    B2G_REQUIRE(v == 8 || v == 25 || v == 43, "grid byte %d has value %d, expected one of 8/25/43", i, (int)v);
+  }
+  int dev = 0;
+  B2G_CUDA_OK(cudaGetDevice(&dev));
+  B2G_REQUIRE(dev >= 0 && dev < 64, "device index %d out of range", dev);
+  B2G_CUDA_OK(cudaMemcpyToSymbol(b2g::g_iq2s_grid, host_grid_1024x8, 8192));
+  b2g::g_grid_s_ready[dev] = true;
   return 0;
 }
 

@@ -3,6 +3,7 @@
 
 namespace b2g {
 int iq2xxs_grid(const uint2** out);
+int iq2s_grid(const uint2** out);
 
 // One thread decodes 8 consecutive values and writes one 16-byte vector.  Consecutive threads take
 // consecutive 8-value chunks of a row, so stores are fully coalesced; the packed bytes (0.26-1.06
@@ -30,7 +31,7 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict_
 
 extern "C" int b2g_dequant(int qtype, const void* payload, int64_t rows, int64_t cols, void* out_bf16, void* stream) {
   using namespace b2g;
-  B2G_REQUIRE(qtype == B2G_Q8_0 || qtype == B2G_Q4_K || qtype == B2G_IQ2_XXS || qtype == B2G_Q6_K || qtype == B2G_Q5_K || qtype == B2G_Q2_K || qtype == B2G_Q3_K, "unsupported GGUF type id %d", qtype);
+  B2G_REQUIRE(qtype == B2G_Q8_0 || qtype == B2G_Q4_K || qtype == B2G_IQ2_XXS || qtype == B2G_Q6_K || qtype == B2G_Q5_K || qtype == B2G_Q2_K || qtype == B2G_Q3_K || qtype == B2G_IQ2_S, "unsupported GGUF type id %d", qtype);
   B2G_REQUIRE(rows >= 0 && cols > 0 && cols % fmt::block_values(qtype) == 0,
               "cols=%lld is not a multiple of the %d-value block", (long long)cols, fmt::block_values(qtype));
   B2G_REQUIRE(cols < (1ll << 31), "cols too large");
@@ -52,6 +53,11 @@ extern "C" int b2g_dequant(int qtype, const void* payload, int64_t rows, int64_t
   } else if (qtype == B2G_Q2_K) {
     B2G_REQUIRE(fmt::row_bytes(qtype, cols) % 4 == 0, "Q2_K rows must be 4-byte multiples");
     dequant_kernel<B2G_Q2_K><<<blocks, 256, 0, s>>>(p, rows, (int)cols, pitch, nullptr, o);
+  } else if (qtype == B2G_IQ2_S) {
+    const uint2* grid = nullptr;
+    int rc = iq2s_grid(&grid);
+    if (rc) return rc;
+    dequant_kernel<B2G_IQ2_S><<<blocks, 256, 0, s>>>(p, rows, (int)cols, pitch, grid, o);
   } else if (qtype == B2G_Q3_K) {
     dequant_kernel<B2G_Q3_K><<<blocks, 256, 0, s>>>(p, rows, (int)cols, pitch, nullptr, o);
   } else if (qtype == B2G_Q5_K) {

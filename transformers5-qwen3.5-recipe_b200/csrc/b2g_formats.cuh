@@ -1,4 +1,4 @@
-// Device-side decoders for the GGUF block formats on the path: Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, IQ2_XXS.
+// Device-side decoders for the GGUF block formats on the path: Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, IQ2_XXS, IQ2_S.
 //
 // The arithmetic reproduces the float32 decode of the public format definition bit for bit
 // after the final bf16 round-to-nearest-even:
@@ -10,12 +10,14 @@
 //   Q5_K    as Q4_K with a fifth bit per value    (products of 17 and 22 significant bits: exact)
 //   Q6_K    (d*scale)*q                           (11 x 7, then x 6 significant bits: both products exact)
 //   IQ2_XXS d*(0.5+s4)*0.25 * grid * sign         (22 significant bits: exact in fp32)
+//   IQ2_S   the same with a 1024-row grid, explicit sign bytes and a sub-scale per 16 values
 // Block layouts (bytes): Q8_0 34 = fp16 d | 32 x int8; Q4_K 144 = fp16 d | fp16 dmin | 12 scale bytes
 // | 128 nibble bytes; Q2_K 84 = 16 scale bytes (scale | min << 4, one per 16 values) | 64 bytes of 2-bit values
 // | fp16 d | fp16 dmin; Q3_K 110 = 32 mask bytes (bit g of byte l: group g, value l; CLEAR means minus 4) | 64 bytes of
 // 2-bit values | 12 bytes of packed 6-bit scales | fp16 d; Q5_K 176 = the Q4_K header | 32 bytes of fifth bits (bit j of byte l: value l of sub-block j)
 // | 128 nibble bytes; Q6_K 210 = 128 low-nibble bytes | 64 high-pair bytes | 16 int8 scales | fp16 d;
-// IQ2_XXS 66 = fp16 d | 8 x (4 grid indices | u32: 4 x 7-bit signs + 4-bit scale).
+// IQ2_XXS 66 = fp16 d | 8 x (4 grid indices | u32: 4 x 7-bit signs + 4-bit scale); IQ2_S 82 = fp16 d | 32 index bytes
+// | 32 sign bytes | 8 bytes of index bits 8-9 (four groups each) | 8 scale bytes (two nibbles, 16 values each).
 #pragma once
 
 #include "b2g_common.cuh"
@@ -31,6 +33,7 @@ template <> struct Block<B2G_Q6_K> { static constexpr int kValues = 256, kBytes 
 template <> struct Block<B2G_Q5_K> { static constexpr int kValues = 256, kBytes = 176; };
 template <> struct Block<B2G_Q2_K> { static constexpr int kValues = 256, kBytes = 84; };
 template <> struct Block<B2G_Q3_K> { static constexpr int kValues = 256, kBytes = 110; };
+template <> struct Block<B2G_IQ2_S> { static constexpr int kValues = 256, kBytes = 82; };
 
 __host__ __device__ inline int64_t row_bytes(int qtype, int64_t k) {
   switch (qtype) {
@@ -41,6 +44,7 @@ __host__ __device__ inline int64_t row_bytes(int qtype, int64_t k) {
     case B2G_Q5_K: return k / 256 * 176;
     case B2G_Q2_K: return k / 256 * 84;
     case B2G_Q3_K: return k / 256 * 110;
+    case B2G_IQ2_S: return k / 256 * 82;
     default: return -1;
   }
 }
@@ -230,6 +234,27 @@ struct Decode8<B2G_IQ2_XXS> {
     const float db = __fmul_rn(__fmul_rn(d, 0.5f + static_cast<float>(word >> 28)), 0.25f);
     const uint32_t signs = iq2_sign_byte((word >> (7 * sub)) & 127u);
     const uint2 mag = grid[(idx4 >> (8 * sub)) & 255u];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t m = ((i < 4 ? mag.x : mag.y) >> (8 * (i & 3))) & 0xFFu;
+      const float mv = __fmul_rn(db, static_cast<float>(m));
+      v[i] = ((signs >> i) & 1u) ? -mv : mv;
+    }
+  }
+};
+
+template <>
+struct Decode8<B2G_IQ2_S> {
+  __device__ static __forceinline__ void run(const uint8_t* __restrict__ row, int k0, const uint2* __restrict__ grid,
+                                             float (&v)[8]) {
+    const uint8_t* b = row + (k0 >> 8) * 82;   // 82-byte blocks are only 2-byte aligned
+    const int c = (k0 & 255) >> 3;             // group of 8 values, 0..31
+    const float d = dev::half_bits_to_float(*reinterpret_cast<const unsigned short*>(b));
+    const uint32_t idx = static_cast<uint32_t>(b[2 + c]) | (((static_cast<uint32_t>(b[66 + (c >> 2)]) >> (2 * (c & 3))) & 3u) << 8);
+    const uint32_t signs = b[34 + c];
+    const uint32_t s4 = (static_cast<uint32_t>(b[74 + (c >> 2)]) >> (4 * ((c >> 1) & 1))) & 15u;
+    const float db = __fmul_rn(__fmul_rn(d, 0.5f + static_cast<float>(s4)), 0.25f);
+    const uint2 mag = grid[idx];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const uint32_t m = ((i < 4 ? mag.x : mag.y) >> (8 * (i & 3))) & 0xFFu;

@@ -30,6 +30,7 @@
 
 namespace b2g {
 int iq2xxs_grid(const uint2** out);
+int iq2s_grid(const uint2** out);
 
 namespace qg {
 
@@ -84,6 +85,11 @@ template <> struct Packed<B2G_Q2_K, kDgrad> { static constexpr int kBoxWords = 4
 // below the values, two below the scales).  Forward slots serve step pairs as for Q6_K.
 template <> struct Packed<B2G_Q3_K, kFwd> { static constexpr int kBoxWords = 4, kBoxRows = 128, kBytes = 8 * 2048, kSteps = 2; };
 template <> struct Packed<B2G_Q3_K, kDgrad> { static constexpr int kBoxWords = 4, kBoxRows = 64, kBytes = 8 * 1024, kSteps = 1; };
+// IQ2_S: 82-byte super-blocks on even bytes; a 96-byte window from the 16-byte boundary below covers one, as six pieces per
+// row.  A step needs 8 index bytes, 8 sign bytes and a few bits more of its super-block; the whole window is loaded (it is
+// small) and, forward, shared by the two steps of a pair (the other pair of the super-block loads it again).
+template <> struct Packed<B2G_IQ2_S, kFwd> { static constexpr int kBoxWords = 4, kBoxRows = 128, kBytes = 6 * 2048, kSteps = 2; };
+template <> struct Packed<B2G_IQ2_S, kDgrad> { static constexpr int kBoxWords = 4, kBoxRows = 64, kBytes = 6 * 1024, kSteps = 1; };
 // Q5_K: 176-byte super-blocks keep 16-byte alignment like Q4_K.  Forward: header, the 32 bytes of fifth bits (all eight
 // sub-blocks share them) and the 32 nibble bytes of one 64-value pair, as five [128 rows x 16 B] boxes.  Dgrad: whole
 // super-blocks of 64 rows (row stride 176 B = 11 x 16: conflict-free 16-byte loads).
@@ -113,8 +119,9 @@ struct Cfg {
   static constexpr int kOffP = kOffB + kBStages * kBStage;
   static constexpr int kOffLA = kOffP + kPStages * kPStage;
   static constexpr int kOffLB = kOffLA + kMT * kLoraATile;
-  static constexpr int kOffGrid = kOffLB + kLoraBTile;                      // IQ2_XXS table (2 KB)
-  static constexpr int kOffBar = kOffGrid + (QT == B2G_IQ2_XXS ? 2048 : 0);
+  static constexpr int kGridRows = QT == B2G_IQ2_XXS ? 256 : (QT == B2G_IQ2_S ? 1024 : 0);   // magnitude table of the IQ2 types
+  static constexpr int kOffGrid = kOffLB + kLoraBTile;
+  static constexpr int kOffBar = kOffGrid + 8 * kGridRows;
   static constexpr int kNumBars = 2 * kAStages + 2 * kBStages + 2 * kPStages + 2 + 2;
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;                   // tmem slot, abort flag
   static constexpr int kSmemBytes = kOffMisc + 16 + 1024;                   // + alignment slack
@@ -335,6 +342,31 @@ __device__ __forceinline__ void q3k_half(const uint32_t (&hm)[8], const uint32_t
   }
 }
 
+// IQ2_S: 32 values = four groups of 8: index bytes `idx4` with their bits 8-9 in `hi` (two per group), sign bytes `sg4`,
+// `sc` = two 4-bit sub-scales (first / second 16 values).
+__device__ __forceinline__ void iq2s_half(float d, uint32_t idx4, uint32_t sg4, uint32_t hi, uint32_t sc, uint32_t grid_s,
+                                          uint32_t (&out)[16]) {
+  const float db0 = __fmul_rn(__fmul_rn(d, 0.5f + static_cast<float>(sc & 15u)), 0.25f);
+  const float db1 = __fmul_rn(__fmul_rn(d, 0.5f + static_cast<float>(sc >> 4)), 0.25f);
+#pragma unroll
+  for (int s = 0; s < 4; ++s) {
+    const uint32_t row = ((idx4 >> (8 * s)) & 255u) | (((hi >> (2 * s)) & 3u) << 8);
+    const uint2 mag = dev::lds64(grid_s + (row << 3));
+    const uint32_t sg = (sg4 >> (8 * s)) & 255u;
+    const float db = s < 2 ? db0 : db1;
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float m = __fmul_rn(db, fmt::byte_to_float(i < 4 ? mag.x : mag.y, i & 3));
+      v[i] = __uint_as_float(__float_as_uint(m) ^ (((sg >> i) & 1u) << 31));
+    }
+    out[4 * s + 0] = dev::pack_bf16(v[0], v[1]);
+    out[4 * s + 1] = dev::pack_bf16(v[2], v[3]);
+    out[4 * s + 2] = dev::pack_bf16(v[4], v[5]);
+    out[4 * s + 3] = dev::pack_bf16(v[6], v[7]);
+  }
+}
+
 // Q6_K: 32 values of a 64-value slice.  `j` = which quarter of the super-block the slice is (its parity picks the low or the
 // high nibbles and the bit pairs 0-3 or 4-7); `half` = first or second 32 values (nibble bytes 0-31 / 32-63, bit pair
 // 2*half of the nibble-parity's four).  value = (d * scale) * (q - 32), both products exact in fp32.
@@ -365,6 +397,7 @@ template <> struct RowData<B2G_Q8_0> { uint32_t w[17]; };
 template <> struct RowData<B2G_IQ2_XXS> { float d; uint32_t idx4[2], word[2]; };
 template <> struct RowData<B2G_Q2_K> { uint32_t qs[8]; uint32_t sc4, dd; };   // 32 bytes of 2-bit values, 4 scale bytes, d | dmin
 template <> struct RowData<B2G_Q3_K> { uint32_t hm[8], qs[8]; uint32_t sc_lo, sc_hi; float d; };   // mask, values, scale words
+template <> struct RowData<B2G_IQ2_S> { float d; uint32_t idx[2], sg[2], hi2, sc; };   // per half: 4 index bytes, 4 sign bytes; index bits 8-9; scales
 template <> struct RowData<B2G_Q5_K> { uint4 hdr, qa, qb, ha, hb; };
 template <> struct RowData<B2G_Q6_K> { uint32_t ql[16], qh[8]; uint32_t sc4; float d; };   // 64 nibble bytes, 32 bit-pair bytes, 4 int8 scales
 
@@ -421,6 +454,23 @@ __device__ __forceinline__ void load_row(uint32_t pk, int row, int pair, int it,
     rd.sc_lo = word_at(sft + 4 * (pair & 1));
     rd.sc_hi = word_at(sft + 8);
     rd.d = dev::half_bits_to_float(dev::lds16(win(sft + 12)));
+  } else if constexpr (QT == B2G_IQ2_S) {
+    // window pieces of this row; the super-block starts `sft` (even) bytes into the first; j = `pair` = quarter of the block
+    constexpr uint32_t kPiece = (MODE == kFwd ? 128u : 64u) * 16u;
+    const int sb = MODE == kFwd ? (it >> 2) : ct;
+    const int sft = (82 * sb) & 15;
+    const uint32_t base = pk + row * 16;
+    auto win = [&](int byte) { return base + (byte >> 4) * kPiece + (byte & 15); };
+    auto half_at = [&](int byte) { return dev::lds16(win(byte)); };
+    auto word_at = [&](int byte) { return half_at(byte) | (half_at(byte + 2) << 16); };
+    rd.d = dev::half_bits_to_float(half_at(sft));
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      rd.idx[half] = word_at(sft + 2 + 8 * pair + 4 * half);       // index bytes of groups 8j + 4 half .. + 3
+      rd.sg[half] = word_at(sft + 34 + 8 * pair + 4 * half);       // their sign bytes
+    }
+    rd.hi2 = half_at(sft + 66 + 2 * pair);                         // bytes 2j, 2j+1: index bits 8-9 of four groups each
+    rd.sc = half_at(sft + 74 + 2 * pair);                          // bytes 2j, 2j+1: two nibbles each, 16 values per nibble
   } else if constexpr (QT == B2G_Q5_K) {
     if constexpr (MODE == kFwd) {
       rd.hdr = dev::lds128(pk + row * 16);
@@ -490,6 +540,7 @@ __device__ __forceinline__ void decode_half(const RowData<QT>& rd, int pair, int
   else if constexpr (QT == B2G_Q8_0) q8_half(rd.w, half, out);
   else if constexpr (QT == B2G_Q2_K) q2k_half(rd.qs, rd.sc4, rd.dd, pair, half, out);
   else if constexpr (QT == B2G_Q3_K) q3k_half(rd.hm, rd.qs, rd.sc_lo, rd.sc_hi, rd.d, pair, half, out);
+  else if constexpr (QT == B2G_IQ2_S) iq2s_half(rd.d, rd.idx[half], rd.sg[half], (rd.hi2 >> (8 * half)) & 0xFFu, (rd.sc >> (8 * half)) & 0xFFu, grid_s, out);
   else if constexpr (QT == B2G_Q5_K) q5k_half(rd.hdr, rd.qa, rd.qb, rd.ha, rd.hb, pair, half, out);
   else if constexpr (QT == B2G_Q6_K) q6k_half(rd.ql, rd.qh, rd.sc4, rd.d, pair, half, out);
   else iq2_half(rd.d, rd.idx4[half], rd.word[half], grid_s, out);
@@ -587,9 +638,9 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
     dev::prefetch_tmap(&tm_a0);
     dev::prefetch_tmap(&tm_w0);
   }
-  if constexpr (QT == B2G_IQ2_XXS) {
+  if constexpr (C::kGridRows > 0) {
     uint2* gs = reinterpret_cast<uint2*>(smem + C::kOffGrid);
-    for (int i = threadIdx.x; i < 256; i += kThreads) gs[i] = p.grid[i];
+    for (int i = threadIdx.x; i < C::kGridRows; i += kThreads) gs[i] = p.grid[i];
   }
   if (warp == 1) {
     dev::tmem_alloc_pair(dev::smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
@@ -754,6 +805,12 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
             for (int q = 0; q < 3; ++q) dev::tma_load_2d(dst + q * kPiece, wm, bar(kFullP + sp), x0 + 4 * q, y);                  // mask
             for (int q = 0; q < 3; ++q) dev::tma_load_2d(dst + (3 + q) * kPiece, wm, bar(kFullP + sp), x0 + 8 + 8 * h + 4 * q, y);  // values of half h
             for (int q = 0; q < 2; ++q) dev::tma_load_2d(dst + (6 + q) * kPiece, wm, bar(kFullP + sp), x0 + 24 + 4 * q, y);       // scales, d
+          } else if (QT == B2G_IQ2_S) {
+            const int sb = MODE == kFwd ? (it >> 2) : t.ct;
+            const int x0 = ((82 * sb) & ~15) >> 2;
+            const int y = MODE == kFwd ? t.expert * p.n + col0 + static_cast<int>(rank) * kBNh : t.expert * p.n + red0;
+            constexpr uint32_t kPiece = P::kBoxRows * 16;
+            for (int q = 0; q < 6; ++q) dev::tma_load_2d(dst + q * kPiece, wm, bar(kFullP + sp), x0 + 4 * q, y);
           } else if (QT == B2G_Q5_K) {
             if (MODE == kFwd) {
               const int y = t.expert * p.n + col0 + static_cast<int>(rank) * kBNh;
@@ -896,6 +953,10 @@ int launch_impl(const Launch& L) {
   p.status = L.status;
   p.wide_ok = (p.ldc % 16 == 0) && (reinterpret_cast<uintptr_t>(L.out0) % 32 == 0) && (reinterpret_cast<uintptr_t>(L.out1) % 32 == 0);
   p.grid = nullptr;
+  if (QT == B2G_IQ2_S) {
+    int rc = iq2s_grid(&p.grid);
+    if (rc) return rc;
+  }
   if (QT == B2G_IQ2_XXS) {
     int rc = iq2xxs_grid(&p.grid);
     if (rc) return rc;
@@ -964,9 +1025,10 @@ int launch_mode(const Launch& L) {
     case B2G_IQ2_XXS: return launch_impl<B2G_IQ2_XXS, MODE>(L);
     case B2G_Q2_K: return launch_impl<B2G_Q2_K, MODE>(L);
     case B2G_Q3_K: return launch_impl<B2G_Q3_K, MODE>(L);
+    case B2G_IQ2_S: return launch_impl<B2G_IQ2_S, MODE>(L);
     case B2G_Q5_K: return launch_impl<B2G_Q5_K, MODE>(L);
     case B2G_Q6_K: return launch_impl<B2G_Q6_K, MODE>(L);
-    default: return fail(B2G_E_ARG, "unsupported GGUF type id %d (supported: 8 Q8_0, 10 Q2_K, 11 Q3_K, 12 Q4_K, 13 Q5_K, 14 Q6_K, 16 IQ2_XXS)", L.qtype);
+    default: return fail(B2G_E_ARG, "unsupported GGUF type id %d (supported: 8 Q8_0, 10 Q2_K, 11 Q3_K, 12 Q4_K, 13 Q5_K, 14 Q6_K, 16 IQ2_XXS, 22 IQ2_S)", L.qtype);
   }
 }
 
@@ -975,7 +1037,7 @@ int check_common(const Launch& L, const char* what) {
               (long long)L.n, (long long)L.k);
   B2G_REQUIRE(L.k % 256 == 0, "%s: K=%lld must be a multiple of 256", what, (long long)L.k);
   B2G_REQUIRE(fmt::row_bytes(L.qtype, L.k) % 16 == 0,
-              "%s: packed rows of %lld bytes are not 16-byte multiples (IQ2_XXS, Q3_K and Q6_K need K %% 2048 == 0, Q2_K K %% 1024 == 0 on this path)", what,
+              "%s: packed rows of %lld bytes are not 16-byte multiples (IQ2_XXS, IQ2_S, Q3_K and Q6_K need K %% 2048 == 0, Q2_K K %% 1024 == 0 on this path)", what,
               (long long)fmt::row_bytes(L.qtype, L.k));
   B2G_REQUIRE(L.m_total < (1ll << 31) && (int64_t)L.num_experts * L.n < (1ll << 31), "%s: shape too large", what);
   B2G_REQUIRE(L.m_total == 0 || (L.a0 && L.w0 && L.out0), "%s: null pointer", what);

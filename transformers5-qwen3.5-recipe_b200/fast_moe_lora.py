@@ -164,7 +164,7 @@ def _require_native(weight: Any) -> None:
     if not isinstance(weight, GGUFQuantizedTensor):
         raise RuntimeError("GGUF expert weights must be packed GGUFQuantizedTensor payloads on this path.")
     if not supports_native_mmq(weight):
-        raise RuntimeError(f"GGML type {int(weight.quant_type)} has no native B200 kernel (supported: 8, 10, 11, 12, 13, 14, 16); "
+        raise RuntimeError(f"GGML type {int(weight.quant_type)} has no native B200 kernel (supported: 8, 10, 11, 12, 13, 14, 16, 22); "
                            "there is no dequantise-then-matmul fallback in this build.")
     if weight.requires_grad:
         raise RuntimeError("Fast GGUF expert execution requires frozen packed base weights.")
