@@ -26,6 +26,33 @@ def test_binding_table_covers_header():
     assert set(_lib.SIGNATURES) == set(DECLARED)
 
 
+def test_binding_argument_counts_and_kinds_match_the_header():
+    """The ctypes table is written by hand: every prototype's parameter list is parsed from the header and compared with it
+    (count, and pointer / 64-bit / 32-bit / float per position), so a drifted binding fails here instead of on a GPU."""
+    from b2g import _lib
+
+    protos = dict(re.findall(r"^B2G_API\s+[\w\s\*]+?\b(b2g_\w+)\s*\(([^;]*?)\)\s*;", HEADER, flags=re.M | re.S))
+    assert set(protos) == set(DECLARED)
+
+    def kind(param: str) -> str:
+        param = " ".join(param.split())
+        if "*" in param:
+            return "ptr"
+        if param.startswith("int64_t"):
+            return "i64"
+        if param.startswith("float"):
+            return "f32"
+        if param.startswith("int "):
+            return "i32"
+        raise AssertionError(f"unrecognised parameter {param!r}")
+
+    table = {C.c_void_p: "ptr", C.c_char_p: "ptr", C.c_int64: "i64", C.c_int32: "i32", C.c_int: "i32", C.c_float: "f32"}
+    for name, params in protos.items():
+        want = [] if params.strip() in ("", "void") else [kind(p) for p in params.split(",")]
+        got = [table[t] for t in _lib.SIGNATURES[name][1]]
+        assert got == want, f"{name}: binding {got} != header {want}"
+
+
 def test_every_entry_cites_the_reference():
     # each prototype's comment names the reference lines it replaces
     blocks = re.split(r"\n\s*\n", HEADER)
