@@ -315,17 +315,19 @@ class _GroupedLoraExperts(torch.autograd.Function):
             out = ops.grouped_fwd(z, down_p.reshape(-1), None, quant_down, hidden, e, tiles, zas, ops.pad_rank_cols(down_b))
         else:
             out = ops.grouped_fwd(z, down_p.reshape(-1), None, quant_down, hidden, e, tiles)
-        ctx.save_for_backward(sel, gate_p, up_p, down_p, tiles, offsets_full, gate, up, xa, za, gu_a, gu_b, down_a, down_b)
+        # z is kept for the down-projection factor gradient (rows x inter_dim bf16: small next to 180 GB, and cheaper than a
+        # second pass over gate and up in the backward); without adapters nothing in the backward reads it
+        ctx.save_for_backward(sel, gate_p, up_p, down_p, tiles, offsets_full, gate, up, xa, za, gu_a, gu_b, down_a, down_b,
+                              z if has_lora else None)
         ctx.meta = (int(quant_gu), int(quant_down), int(inter_dim), e, r, float(scaling), float(swiglu_limit), has_lora)
         return out
 
     @staticmethod
     def backward(ctx, d_out):
-        sel, gate_p, up_p, down_p, tiles, offsets_full, gate, up, xa, za, gu_a, gu_b, down_a, down_b = ctx.saved_tensors
+        sel, gate_p, up_p, down_p, tiles, offsets_full, gate, up, xa, za, gu_a, gu_b, down_a, down_b, z = ctx.saved_tensors
         quant_gu, quant_down, inter_dim, e, r, scaling, limit, has_lora = ctx.meta
         hidden = sel.shape[1]
         d_out = d_out.contiguous()
-        z = ops.swiglu_fwd(gate, up, limit)
         d_gu_a = d_gu_b = d_down_a = d_down_b = None
         if has_lora:
             # down projection: dZ = dOut.deq(Wd) + s.(dOut.Bd).Ad ; dAd = s.(dOut.Bd)^T.Z ; dBd = s.dOut^T.(Z.Ad^T)
