@@ -304,14 +304,14 @@ class _GroupedLoraExperts(torch.autograd.Function):
         r = 0
         if has_lora:
             r = gu_a.shape[1]
-            xa, xas = ops.grouped_lora_down(sel, None, gu_a.contiguous(), False, scaling, r, tiles)
+            xa, xas = ops.grouped_lora_down(sel, None, gu_a.contiguous(), False, scaling, r, tiles, zero=False)
             gate, up = ops.grouped_fwd(sel, gate_p.reshape(-1), up_p.reshape(-1), quant_gu, inter_dim, e, tiles, xas,
                                        ops.pad_rank_cols(gu_b))
         else:
             gate, up = ops.grouped_fwd(sel, gate_p.reshape(-1), up_p.reshape(-1), quant_gu, inter_dim, e, tiles)
         z = ops.swiglu_fwd(gate, up, swiglu_limit)
         if has_lora:
-            za, zas = ops.grouped_lora_down(z, None, down_a.contiguous(), False, scaling, r, tiles)
+            za, zas = ops.grouped_lora_down(z, None, down_a.contiguous(), False, scaling, r, tiles, zero=False)
             out = ops.grouped_fwd(z, down_p.reshape(-1), None, quant_down, hidden, e, tiles, zas, ops.pad_rank_cols(down_b))
         else:
             out = ops.grouped_fwd(z, down_p.reshape(-1), None, quant_down, hidden, e, tiles)
@@ -331,7 +331,7 @@ class _GroupedLoraExperts(torch.autograd.Function):
         d_gu_a = d_gu_b = d_down_a = d_down_b = None
         if has_lora:
             # down projection: dZ = dOut.deq(Wd) + s.(dOut.Bd).Ad ; dAd = s.(dOut.Bd)^T.Z ; dBd = s.dOut^T.(Z.Ad^T)
-            dob, dobs = ops.grouped_lora_down(d_out, None, down_b.transpose(1, 2).contiguous(), False, scaling, r, tiles)
+            dob, dobs = ops.grouped_lora_down(d_out, None, down_b.transpose(1, 2).contiguous(), False, scaling, r, tiles, zero=False)
             dz = ops.grouped_dgrad(d_out, None, down_p.reshape(-1), None, quant_down, inter_dim, e, tiles, dobs,
                                    ops.pad_rank_rows(down_a))
             d_down_a = torch.empty_like(down_a)
@@ -343,7 +343,7 @@ class _GroupedLoraExperts(torch.autograd.Function):
         d_gate, d_up = ops.swiglu_bwd(gate, up, dz, limit)
         if has_lora:
             # gate|up: dX = dG.deq(Wg) + dU.deq(Wu) + s.([dG|dU].Bgu).Agu
-            dgb, dgbs = ops.grouped_lora_down(d_gate, d_up, gu_b.transpose(1, 2).contiguous(), False, scaling, r, tiles)
+            dgb, dgbs = ops.grouped_lora_down(d_gate, d_up, gu_b.transpose(1, 2).contiguous(), False, scaling, r, tiles, zero=False)
             d_sel = ops.grouped_dgrad(d_gate, d_up, gate_p.reshape(-1), up_p.reshape(-1), quant_gu, hidden, e, tiles, dgbs,
                                       ops.pad_rank_rows(gu_a))
             d_gu_a = torch.empty_like(gu_a)

@@ -493,15 +493,17 @@ def grouped_dgrad(dy0: torch.Tensor, dy1: Optional[torch.Tensor], payload0: torc
 
 
 def grouped_lora_down(x: torch.Tensor, x1: Optional[torch.Tensor], w: torch.Tensor, w_is_cr: bool, scale: float, r: int,
-                      tiles: torch.Tensor, plain: bool = True, scaled: bool = True):
+                      tiles: torch.Tensor, plain: bool = True, scaled: bool = True, zero: bool = True):
     """Per-expert projection onto the rank.  ``w`` is [E, r, C] or (w_is_cr) [E, C(or 2C), r].
-    Rows outside every tile of the table stay uninitialised, so outputs start zeroed."""
+    The kernel writes only rows that belong to a tile of the table, so the outputs start zeroed unless the caller says that
+    nobody reads the other rows (``zero=False``: the fused expert block, whose consumers walk the same table)."""
     _need(x, torch.bfloat16, "x")
     _need(w, torch.bfloat16, "w")
     rows, c = x.shape
     e = w.shape[0]
-    o_plain = torch.zeros(rows, LORA_PAD, dtype=torch.bfloat16, device=x.device) if plain else None
-    o_scaled = torch.zeros(rows, LORA_PAD, dtype=torch.bfloat16, device=x.device) if scaled else None
+    make = torch.zeros if zero else torch.empty
+    o_plain = make(rows, LORA_PAD, dtype=torch.bfloat16, device=x.device) if plain else None
+    o_scaled = make(rows, LORA_PAD, dtype=torch.bfloat16, device=x.device) if scaled else None
     with _DeviceCtx(x):
         _lib.call("b2g_grouped_lora_down", _p(x), _p(x1), _p(w), int(w_is_cr), float(scale), _p(tiles), _p(o_plain), _p(o_scaled),
                   rows, c, int(r), int(e), _stream(x))
