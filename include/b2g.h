@@ -44,6 +44,10 @@ extern "C" {
 #define B2G_Q2_K 10
 #define B2G_Q3_K 11
 #define B2G_IQ2_S 22
+/* OR-ed into the `qtype` argument of the matrix products: every payload row is padded to the next multiple of 16 bytes
+ * (TMA needs 16-byte row pitches; 66-, 82-, 84-, 110- and 210-byte blocks give them only for some K).  b2g_dequant takes
+ * plain type ids and unpadded rows only. */
+#define B2G_PADDED_ROWS 0x100
 
 #define B2G_LORA_PAD 16    /* LoRA rank operands are zero-padded to 16 columns / rows */
 

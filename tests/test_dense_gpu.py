@@ -56,6 +56,28 @@ def test_fused_lora_linear_forward_backward(cuda, qtype, m, n, k, r):
     assert y.dtype == torch.bfloat16 and xc.grad.shape == x.shape and bc.grad.shape == b.shape
 
 
+@pytest.mark.parametrize("qtype,m,n,k,r", [
+    (go.IQ2_XXS, 200, 512, 512, 8), (go.IQ2_S, 200, 264, 256, 4), (go.Q3_K, 300, 512, 512, 16), (go.Q6_K, 130, 256, 768, 16),
+    (go.Q2_K, 150, 520, 512, 2),
+])
+def test_row_pitches_that_are_not_16_byte_multiples(cuda, qtype, m, n, k, r):
+    """Widths whose packed rows are not multiples of 16 bytes (a 512-wide IQ2_XXS row is 132 bytes: the down projection of
+    the Qwen experts): the wrapper pads the rows and flags the type id, results as for any other width."""
+    from b2g import autograd as ag, ops
+
+    assert ops.payload_row_bytes(qtype, k) % 16 != 0
+    payload, x, dy, a, b = _case(qtype, m, n, k, r, 2000 + m, encoder="random" if qtype in (go.IQ2_XXS, go.IQ2_S) else "quantize")
+    ref = dense_ref.lora_linear_fwd_bwd(x, dense_ref.dequant_bf16(payload, qtype), a, b, 2.0, dy, torch.float32)
+    xc = x.to(cuda).requires_grad_(True)
+    ac, bc = a.to(cuda).requires_grad_(True), b.to(cuda).requires_grad_(True)
+    y = ag.lora_qlinear(xc, torch.from_numpy(payload).to(cuda), qtype, n, ac, bc, 2.0)
+    y.backward(dy.to(cuda))
+    assert dense_ref.rel_l2(y, ref["y"]) < TOL
+    assert dense_ref.rel_l2(xc.grad, ref["dx"]) < TOL
+    assert dense_ref.rel_l2(ac.grad, ref["da"]) < TOL
+    assert dense_ref.rel_l2(bc.grad, ref["db"]) < TOL
+
+
 def test_config0_q8_lora_linear(cuda):
     """The CPU-runnable benchmark configuration: Q8_0 2048x2048, r=16, alpha=32, 4096 tokens; also the bf16 oracle itself
     must sit inside the same tolerance of the fp32 oracle."""
@@ -167,7 +189,7 @@ def test_full_width_every_element_repeated(cuda):
 
 
 def test_fail_closed_arguments(cuda):
-    from b2g import autograd as ag, ops
+    from b2g import _lib, autograd as ag, ops
 
     p = torch.zeros(8 * 144, dtype=torch.uint8, device=cuda)
     x = torch.zeros(4, 256, dtype=torch.float32, device=cuda)
@@ -178,8 +200,10 @@ def test_fail_closed_arguments(cuda):
         ag.mmq(xb, p, 12, 8)
     with pytest.raises(ValueError):
         ops.qlinear_fwd(torch.zeros(4, 256, dtype=torch.bfloat16, device=cuda), p[:-1], 12, 8)
-    with pytest.raises(ValueError, match="K % 2048"):
-        ops.qlinear_fwd(torch.zeros(4, 256, dtype=torch.bfloat16, device=cuda), torch.zeros(8 * 66, dtype=torch.uint8, device=cuda), 16, 8)
+    # 66-byte rows are not TMA-compatible as they are: the wrapper pads them; the C entry point refuses them unpadded
+    assert ops.qlinear_fwd(torch.zeros(4, 256, dtype=torch.bfloat16, device=cuda), torch.zeros(8 * 66, dtype=torch.uint8, device=cuda), 16, 8).shape == (4, 8)
+    with pytest.raises(ValueError, match="B2G_PADDED_ROWS"):
+        _lib.call("b2g_qlinear_fwd", 16, None, None, None, None, None, None, 4, 8, 256, None, None)
     with pytest.raises(ValueError):
         ag.lora_qlinear(torch.zeros(4, 256, dtype=torch.bfloat16, device=cuda), p, 12, 8,
                         torch.zeros(32, 256, device=cuda), torch.zeros(8, 32, device=cuda), 1.0)

@@ -73,6 +73,8 @@ def test_constant_byte_iq2_xxs_payload_like_the_reference_test(cuda):
     (go.Q2_K, 4, 1024, 1024, 400, 2, 8, False),
     (go.Q3_K, 4, 2048, 2048, 300, 2, 8, False),
     (go.IQ2_S, 4, 2048, 2048, 300, 2, 8, False),
+    (go.IQ2_XXS, 8, 2048, 512, 500, 2, 16, False),      # the Qwen expert shape: 132-byte rows in the down projection
+    (go.Q3_K, 4, 2048, 512, 300, 2, 8, False),
 ])
 def test_expert_layer_forward_backward(cuda, qtype, e, h, i, t, k, r, skew):
     from b2g import autograd as ag, routing

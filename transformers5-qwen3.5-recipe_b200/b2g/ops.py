@@ -135,6 +135,24 @@ def _check_payload(payload: torch.Tensor, qtype: int, rows: int, k: int, what: s
         ensure_iq2s_grid(payload.device)
 
 
+PADDED_ROWS = 0x100     # B2G_PADDED_ROWS: flag on the type id, "payload rows are padded to a multiple of 16 bytes"
+
+
+def _tma_payload(payload: torch.Tensor, qtype: int, rows: int, k: int):
+    """The payload as the matrix-product kernels take it, and the type argument to pass with it.
+
+    TMA needs row pitches that are multiples of 16 bytes.  Q4_K, Q5_K and Q8_0 rows always are; the other formats' rows
+    only for some widths (a 512-wide IQ2_XXS row is 132 bytes).  Such payloads are copied into rows padded to the next
+    multiple of 16 -- a pass over the packed bytes, a few percent of the product that follows -- and flagged."""
+    pitch = payload_row_bytes(qtype, k)
+    if pitch % 16 == 0:
+        return payload, int(qtype)
+    padded = (pitch + 15) // 16 * 16
+    out = torch.zeros(rows, padded, dtype=torch.uint8, device=payload.device)
+    out[:, :pitch] = payload.reshape(rows, pitch)
+    return out.reshape(-1), int(qtype) | PADDED_ROWS
+
+
 # --------------------------------------------------------------------------------------
 # dequantise
 # --------------------------------------------------------------------------------------
@@ -220,8 +238,9 @@ def qlinear_fwd(x: torch.Tensor, payload: torch.Tensor, qtype: int, n: int, bias
         if tuple(xas.shape) != (m, LORA_PAD) or tuple(lora_b16.shape) != (n, LORA_PAD):
             raise ValueError("LoRA operands must be [M,16] and [N,16]")
     y = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
+    payload, qarg = _tma_payload(payload, qtype, n, k)
     with _DeviceCtx(x):
-        _lib.call("b2g_qlinear_fwd", int(qtype), _p(x), _p(payload), _p(bias), _p(xas), _p(lora_b16), _p(y), m, n, k,
+        _lib.call("b2g_qlinear_fwd", qarg, _p(x), _p(payload), _p(bias), _p(xas), _p(lora_b16), _p(y), m, n, k,
                   _p(status_word(x.device)), _stream(x))
     return y
 
@@ -279,8 +298,9 @@ def fixed_grouped_fwd(x: torch.Tensor, packed_groups: torch.Tensor, qtype: int) 
     """Y[..., g, :] = X[..., g, :] . deq(W_g)^T for every group, in place on column blocks (no per-group copies)."""
     m, groups, n, k = _fixed_group_geometry(x, packed_groups, qtype, True)
     y = torch.empty(*x.shape[:-1], n, dtype=torch.bfloat16, device=x.device)
+    packed_groups, qarg = _tma_payload(packed_groups, qtype, groups * n, k)
     with _DeviceCtx(x):
-        _lib.call("b2g_fixed_grouped_fwd", int(qtype), _p(x), _p(packed_groups), _p(y), m, groups, n, k, _p(status_word(x.device)), _stream(x))
+        _lib.call("b2g_fixed_grouped_fwd", qarg, _p(x), _p(packed_groups), _p(y), m, groups, n, k, _p(status_word(x.device)), _stream(x))
     return y
 
 
@@ -288,8 +308,9 @@ def fixed_grouped_dgrad(dy: torch.Tensor, packed_groups: torch.Tensor, qtype: in
     """dX[..., g, :] = dY[..., g, :] . deq(W_g) for every group."""
     m, groups, n, k = _fixed_group_geometry(dy, packed_groups, qtype, False)
     dx = torch.empty(*dy.shape[:-1], k, dtype=torch.bfloat16, device=dy.device)
+    packed_groups, qarg = _tma_payload(packed_groups, qtype, groups * n, k)
     with _DeviceCtx(dy):
-        _lib.call("b2g_fixed_grouped_dgrad", int(qtype), _p(dy), _p(packed_groups), _p(dx), m, groups, n, k, _p(status_word(dy.device)),
+        _lib.call("b2g_fixed_grouped_dgrad", qarg, _p(dy), _p(packed_groups), _p(dx), m, groups, n, k, _p(status_word(dy.device)),
                   _stream(dy))
     return dx
 
@@ -315,8 +336,9 @@ def qlinear_dgrad(dy: torch.Tensor, payload: torch.Tensor, qtype: int, k: int,
         if tuple(dybs.shape) != (m, LORA_PAD) or tuple(lora_a16.shape) != (LORA_PAD, k):
             raise ValueError("LoRA operands must be [M,16] and [16,K]")
     dx = torch.empty(m, k, dtype=torch.bfloat16, device=dy.device)
+    payload, qarg = _tma_payload(payload, qtype, n, k)
     with _DeviceCtx(dy):
-        _lib.call("b2g_qlinear_dgrad", int(qtype), _p(dy), _p(payload), _p(dybs), _p(lora_a16), _p(dx), m, n, k,
+        _lib.call("b2g_qlinear_dgrad", qarg, _p(dy), _p(payload), _p(dybs), _p(lora_a16), _p(dx), m, n, k,
                   _p(status_word(dy.device)), _stream(dy))
     return dx
 
@@ -465,8 +487,11 @@ def grouped_fwd(x: torch.Tensor, payload0: torch.Tensor, payload1: Optional[torc
             raise ValueError("bad LoRA operand shapes for the grouped forward")
     y0 = torch.empty(r, n, dtype=torch.bfloat16, device=x.device)
     y1 = torch.empty(r, n, dtype=torch.bfloat16, device=x.device) if payload1 is not None else None
+    payload0, qarg = _tma_payload(payload0, qtype, num_experts * n, k)
+    if payload1 is not None:
+        payload1, _ = _tma_payload(payload1, qtype, num_experts * n, k)
     with _DeviceCtx(x):
-        _lib.call("b2g_grouped_fwd", int(qtype), _p(x), _p(payload0), _p(payload1), _p(tiles), _p(xas), _p(lora_b16), lora_rows,
+        _lib.call("b2g_grouped_fwd", qarg, _p(x), _p(payload0), _p(payload1), _p(tiles), _p(xas), _p(lora_b16), lora_rows,
                   _p(y0), _p(y1), r, n, k, int(num_experts), _p(status_word(x.device)), _stream(x))
     return (y0, y1) if payload1 is not None else y0
 
@@ -486,8 +511,11 @@ def grouped_dgrad(dy0: torch.Tensor, dy1: Optional[torch.Tensor], payload0: torc
         if tuple(dybs.shape) != (r, LORA_PAD) or tuple(lora_a16.shape) != (num_experts, LORA_PAD, k):
             raise ValueError("bad LoRA operand shapes for the grouped input gradient")
     dx = torch.empty(r, k, dtype=torch.bfloat16, device=dy0.device)
+    payload0, qarg = _tma_payload(payload0, qtype, num_experts * n, k)
+    if payload1 is not None:
+        payload1, _ = _tma_payload(payload1, qtype, num_experts * n, k)
     with _DeviceCtx(dy0):
-        _lib.call("b2g_grouped_dgrad", int(qtype), _p(dy0), _p(dy1), _p(payload0), _p(payload1), _p(tiles), _p(dybs), _p(lora_a16),
+        _lib.call("b2g_grouped_dgrad", qarg, _p(dy0), _p(dy1), _p(payload0), _p(payload1), _p(tiles), _p(dybs), _p(lora_a16),
                   _p(dx), r, n, k, int(num_experts), _p(status_word(dy0.device)), _stream(dy0))
     return dx
 

@@ -908,6 +908,7 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
 // ------------------------------------------------------------------------------------------------
 struct Launch {
   int qtype, mode;
+  int padded;                 // payload rows are padded to the next multiple of 16 bytes (B2G_PADDED_ROWS flag of the type id)
   const void *a0, *a1;        // activations [m_total, red_dim]
   const void *w0, *w1;        // payloads
   const void *la, *lb;        // LoRA operands
@@ -921,6 +922,17 @@ struct Launch {
   int* status;
   cudaStream_t stream;
 };
+
+// Row pitch of a payload: the format's bytes per row, or that rounded up to 16 when the caller padded the rows.
+inline int64_t packed_pitch(int qtype, int64_t k, int padded) {
+  const int64_t b = fmt::row_bytes(qtype, k);
+  return padded ? (b + 15) / 16 * 16 : b;
+}
+// The `qtype` argument of the entry points: GGML type id, optionally with B2G_PADDED_ROWS.
+inline void split_qtype(int arg, Launch& L) {
+  L.qtype = arg & 0xFF;
+  L.padded = (arg & B2G_PADDED_ROWS) ? 1 : 0;
+}
 
 template <int QT, int MODE>
 int launch_impl(const Launch& L) {
@@ -975,7 +987,7 @@ int launch_impl(const Launch& L) {
   tm_a1 = tm_a0;
   if (L.a1 && (rc = make_tmap_2d(&tm_a1, L.a1, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, red_cols, L.m_total, a_pitch, kBK, kBM,
                                  CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-  const uint64_t w_pitch = (uint64_t)fmt::row_bytes(QT, L.k);
+  const uint64_t w_pitch = (uint64_t)packed_pitch(QT, L.k, L.padded);
   const uint64_t w_rows = (uint64_t)L.num_experts * L.n;
   if ((rc = make_tmap_2d(&tm_w0, L.w0, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, w_pitch / 4, w_rows, w_pitch, P::kBoxWords, P::kBoxRows,
                          CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
@@ -1036,9 +1048,9 @@ int check_common(const Launch& L, const char* what) {
   B2G_REQUIRE(L.m_total >= 0 && L.n > 0 && L.k > 0, "%s: bad shape M=%lld N=%lld K=%lld", what, (long long)L.m_total,
               (long long)L.n, (long long)L.k);
   B2G_REQUIRE(L.k % 256 == 0, "%s: K=%lld must be a multiple of 256", what, (long long)L.k);
-  B2G_REQUIRE(fmt::row_bytes(L.qtype, L.k) % 16 == 0,
-              "%s: packed rows of %lld bytes are not 16-byte multiples (IQ2_XXS, IQ2_S, Q3_K and Q6_K need K %% 2048 == 0, Q2_K K %% 1024 == 0 on this path)", what,
-              (long long)fmt::row_bytes(L.qtype, L.k));
+  B2G_REQUIRE(packed_pitch(L.qtype, L.k, L.padded) % 16 == 0,
+              "%s: packed rows of %lld bytes are not 16-byte multiples: pad every row to the next multiple of 16 bytes and pass the type "
+              "id with B2G_PADDED_ROWS", what, (long long)fmt::row_bytes(L.qtype, L.k));
   B2G_REQUIRE(L.m_total < (1ll << 31) && (int64_t)L.num_experts * L.n < (1ll << 31), "%s: shape too large", what);
   B2G_REQUIRE(L.m_total == 0 || (L.a0 && L.w0 && L.out0), "%s: null pointer", what);
   B2G_REQUIRE((L.la == nullptr) == (L.lb == nullptr), "%s: the two LoRA operands come together", what);
@@ -1093,7 +1105,7 @@ using namespace b2g;
 extern "C" int b2g_qlinear_fwd(int qtype, const void* x, const void* payload, const void* bias, const void* xas, const void* lora_b16,
                                void* y, int64_t M, int64_t N, int64_t K, int* status, void* stream) {
   qg::Launch L{};
-  L.qtype = qtype; L.mode = qg::kFwd; L.a0 = x; L.w0 = payload; L.la = xas; L.lb = lora_b16;
+  qg::split_qtype(qtype, L); L.mode = qg::kFwd; L.a0 = x; L.w0 = payload; L.la = xas; L.lb = lora_b16;
   L.m_total = M; L.n = N; L.k = K; L.num_experts = 1; L.lora_rows = N; L.out0 = y; L.bias = bias; L.status = status;
   L.stream = static_cast<cudaStream_t>(stream);
   int rc = qg::check_common(L, "qlinear_fwd");
@@ -1105,7 +1117,7 @@ extern "C" int b2g_qlinear_fwd(int qtype, const void* x, const void* payload, co
 extern "C" int b2g_qlinear_dgrad(int qtype, const void* dy, const void* payload, const void* dybs, const void* lora_a16, void* dx,
                                  int64_t M, int64_t N, int64_t K, int* status, void* stream) {
   qg::Launch L{};
-  L.qtype = qtype; L.mode = qg::kDgrad; L.a0 = dy; L.w0 = payload; L.la = dybs; L.lb = lora_a16;
+  qg::split_qtype(qtype, L); L.mode = qg::kDgrad; L.a0 = dy; L.w0 = payload; L.la = dybs; L.lb = lora_a16;
   L.m_total = M; L.n = N; L.k = K; L.num_experts = 1; L.lora_rows = 16; L.out0 = dx; L.status = status;
   L.stream = static_cast<cudaStream_t>(stream);
   int rc = qg::check_common(L, "qlinear_dgrad");
@@ -1135,7 +1147,7 @@ extern "C" int b2g_grouped_fwd(int qtype, const void* x, const void* payload0, c
                                const void* xas, const void* lora_b16, int64_t lora_rows, void* y0, void* y1, int64_t R, int64_t N,
                                int64_t K, int num_experts, int* status, void* stream) {
   qg::Launch L{};
-  L.qtype = qtype; L.mode = qg::kFwd; L.a0 = x; L.w0 = payload0; L.w1 = payload1; L.la = xas; L.lb = lora_b16;
+  qg::split_qtype(qtype, L); L.mode = qg::kFwd; L.a0 = x; L.w0 = payload0; L.w1 = payload1; L.la = xas; L.lb = lora_b16;
   L.m_total = R; L.n = N; L.k = K; L.num_experts = num_experts; L.tiles = tiles; L.lora_rows = lora_rows;
   L.out0 = y0; L.out1 = y1; L.status = status; L.stream = static_cast<cudaStream_t>(stream);
   int rc = qg::check_common(L, "grouped_fwd");
@@ -1151,7 +1163,7 @@ extern "C" int b2g_grouped_dgrad(int qtype, const void* dy0, const void* dy1, co
                                  const int32_t* tiles, const void* dybs, const void* lora_a16, void* dx, int64_t R, int64_t N,
                                  int64_t K, int num_experts, int* status, void* stream) {
   qg::Launch L{};
-  L.qtype = qtype; L.mode = qg::kDgrad; L.a0 = dy0; L.a1 = dy1; L.w0 = payload0; L.w1 = payload1; L.la = dybs; L.lb = lora_a16;
+  qg::split_qtype(qtype, L); L.mode = qg::kDgrad; L.a0 = dy0; L.a1 = dy1; L.w0 = payload0; L.w1 = payload1; L.la = dybs; L.lb = lora_a16;
   L.m_total = R; L.n = N; L.k = K; L.num_experts = num_experts; L.tiles = tiles; L.lora_rows = 16;
   L.out0 = dx; L.status = status; L.stream = static_cast<cudaStream_t>(stream);
   int rc = qg::check_common(L, "grouped_dgrad");
@@ -1170,10 +1182,10 @@ static int fixed_grouped(int mode, int qtype, const void* a, const void* payload
   const int64_t in_w = mode == qg::kFwd ? K : N, out_w = mode == qg::kFwd ? N : K;
   B2G_REQUIRE(in_w % 8 == 0 && out_w % 16 == 0, "%s: group widths %lld -> %lld must be multiples of 8 / 16", what, (long long)in_w,
               (long long)out_w);
-  const int64_t row_bytes = fmt::row_bytes(qtype, K);
+  const int64_t row_bytes = qg::packed_pitch(qtype & 0xFF, K, (qtype & B2G_PADDED_ROWS) ? 1 : 0);
   for (int g = 0; g < groups; ++g) {
     qg::Launch L{};
-    L.qtype = qtype; L.mode = mode;
+    qg::split_qtype(qtype, L); L.mode = mode;
     L.a0 = static_cast<const __nv_bfloat16*>(a) + g * in_w;
     L.w0 = static_cast<const uint8_t*>(payload) + (int64_t)g * N * row_bytes;
     L.out0 = static_cast<__nv_bfloat16*>(out) + g * out_w;
