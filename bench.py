@@ -310,6 +310,89 @@ def run_moe(args) -> int:
     return 0
 
 
+def _event_ms(fn, warmup: int, steps: int) -> float:
+    for _ in range(max(3, warmup)):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / steps
+
+
+def run_side(args) -> int:
+    """Single-GPU measurements of the rows next to the headline path, one JSON line each run:
+      formats : forward / input-gradient product of every native GGUF type at M=32768, N=4096, K=2048
+      fixed   : the fixed-group projection (Q8_0, 8 x (4096 -> 1024), 16384 rows), forward and input gradient
+      lmhead  : packed LM-head chunked cross-entropy, loss + hidden-state gradient (Q8_0 129280 x 4096 and Q6_K 248320 x 2048
+                heads, 4096 tokens)
+    Inputs are seeded random valid blocks and normal activations, all larger than L2; CUDA events on the launching stream."""
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "no CUDA device: the product path has no CPU fallback"}))
+        return 1
+    if int(os.environ.get("RANK", "0")) != 0:
+        return 0
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    from b2g import gguf_quant, ops
+
+    peaks, peak_src = load_peaks()
+    peak_tf = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+    gen = torch.Generator(device=dev).manual_seed(SEED)
+    base = {"n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+            "peak_tflops": peak_tf, "peak_source": peak_src}
+    if args.workload == "formats":
+        m, n, k = args.tokens, 4096, K_DIM
+        x = torch.randn(m, k, generator=gen, device=dev).bfloat16()
+        dy = torch.randn(m, n, generator=gen, device=dev).bfloat16()
+        tf = 2.0 * m * n * k / 1e12
+        names = {8: "Q8_0", 10: "Q2_K", 11: "Q3_K", 12: "Q4_K", 13: "Q5_K", 14: "Q6_K", 16: "IQ2_XXS", 22: "IQ2_S"}
+        out = {}
+        for qt, name in names.items():
+            p = gguf_quant.random_payload(qt, (n, k), 1, device=dev).reshape(-1)
+            f = _event_ms(lambda: ops.qlinear_fwd(x, p, qt, n), args.warmup, args.steps)
+            g = _event_ms(lambda: ops.qlinear_dgrad(dy, p, qt, k), args.warmup, args.steps)
+            out[name] = {"forward_ms": f, "forward_tflops": tf / f * 1e3, "dgrad_ms": g, "dgrad_tflops": tf / g * 1e3}
+        ops.check_status()
+        print(json.dumps({**base, "metric": "packed-weight product TFLOP/s per GGUF type", "unit": "TFLOP/s",
+                          "config": {"workload": "dense product, every native type", "M": m, "N": n, "K": k}, "kernels": out}))
+        return 0
+    if args.workload == "fixed":
+        rows, groups, n, k = 16384, 8, 1024, 4096
+        x = torch.randn(rows, groups, k, generator=gen, device=dev).bfloat16()
+        dy = torch.randn(rows, groups, n, generator=gen, device=dev).bfloat16()
+        p = gguf_quant.random_payload(8, (groups * n, k), 3, device=dev).reshape(groups, n, -1)
+        tf = 2.0 * rows * groups * n * k / 1e12
+        f = _event_ms(lambda: ops.fixed_grouped_fwd(x, p, 8), args.warmup, args.steps)
+        g = _event_ms(lambda: ops.fixed_grouped_dgrad(dy, p, 8), args.warmup, args.steps)
+        ops.check_status()
+        print(json.dumps({**base, "metric": "fixed-group projection rows/s (forward + input gradient)", "value": rows / ((f + g) * 1e-3),
+                          "unit": "rows/s", "ms_per_step": f + g,
+                          "config": {"workload": "fixed groups Q8_0", "rows": rows, "groups": groups, "in": k, "out": n},
+                          "forward_tflops": tf / f * 1e3, "dgrad_tflops": tf / g * 1e3}))
+        return 0
+    import deepseek_v4_liger_loss as dl
+
+    tokens = 4096
+    out = {}
+    for name, qt, vocab, hidden in (("Q8_0 129280x4096", 8, 129280, 4096), ("Q6_K 248320x2048", 14, 248320, 2048)):
+        head = gguf_quant.random_payload(qt, (vocab, hidden), 5, device=dev)
+        h = torch.randn(tokens, hidden, generator=gen, device=dev).bfloat16()
+        t = torch.randint(0, vocab, (tokens,), generator=gen, device=dev)
+        ms = _event_ms(lambda: dl._packed_q8_linear_cross_entropy_forward(h, head, t, qt, vocab, dl._PACKED_LM_HEAD_CHUNK_SIZE, -100, 0.0, 0.0,
+                                                                            "mean", None), args.warmup, args.steps)
+        out[name] = {"ms": ms, "tokens_per_s": tokens / (ms * 1e-3), "tflops_both_products": 4.0 * tokens * vocab * hidden / ms / 1e9}
+        del head
+    ops.check_status()
+    print(json.dumps({**base, "metric": "packed LM-head loss + hidden gradient tokens/s", "unit": "tokens/s",
+                      "config": {"workload": "packed LM-head chunked cross-entropy", "tokens": tokens, "chunk_rows": dl._PACKED_LM_HEAD_CHUNK_SIZE},
+                      "heads": out}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -320,11 +403,13 @@ def main() -> int:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ep", default="peer", choices=["peer", "nccl"],
                     help="MoE workload at N>1: row exchange by peer stores over NVLink (default) or by NCCL all-to-all")
-    ap.add_argument("--workload", default="dense", choices=["dense", "moe"],
-                    help="dense: the Q4_K attention-shape linears (default, replicas at N>1); moe: grouped Q4_K experts, expert-parallel at N>1")
+    ap.add_argument("--workload", default="dense", choices=["dense", "moe", "formats", "fixed", "lmhead"],
+                    help="dense: the Q4_K attention-shape linears (default, replicas at N>1); moe: grouped Q4_K experts, expert-parallel at N>1; formats / fixed / lmhead: single-GPU side measurements (see run_side)")
     args = ap.parse_args()
     if args.workload == "moe":
         return run_moe(args)
+    if args.workload in ("formats", "fixed", "lmhead"):
+        return run_side(args)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
