@@ -246,6 +246,16 @@ B2G_API int b2g_ep_scatter_rows(const void* src, const int64_t* perm, int top_k,
 B2G_API int b2g_ep_return_rows(const void* rows, const int32_t* blk_start, const int32_t* src_pos, const uint64_t* peer_ptrs,
                        int world, int num_blocks, int H, int64_t capacity_rows, void* stream);
 
+/* Slots of the two exchange kernels for rank `rank`, from the all-gathered histograms counts[world][num_experts]
+ * (int32, row g = rows of rank g per global expert; rank g owns experts [g*E/world, (g+1)*E/world)).  One launch;
+ * no value visits the host.  Outputs (int32, device): my_start[E], dest_base[E] as b2g_ep_scatter_rows reads them;
+ * blk_start[E/world*world + 1], src_pos[E/world*world] as b2g_ep_return_rows reads them; local_sizes[E/world] and
+ * local_offsets[E/world] (cumulative ends) = the expert segments of the rows this rank receives, in the form the
+ * grouped products take (the role that the expert histogram of GGUFExperts._prepare_expert_execution, called at
+ * fast_moe_lora.py:709, plays on a single GPU). */
+B2G_API int b2g_ep_peer_plan(const int32_t* counts, int world, int num_experts, int rank, int32_t* my_start, int32_t* dest_base,
+                     int32_t* blk_start, int32_t* src_pos, int32_t* local_sizes, int32_t* local_offsets, void* stream);
+
 /* SwiGLU between the two grouped products: z = silu(g) * u (optionally clamped as the DeepSeek
  * experts do: g <= limit, |u| <= limit; limit <= 0 disables).  Replaces GGUFExperts._apply_split_gate
  * (called at fast_moe_lora.py:747; clamp semantics at test_deepseek_v4_moe_lora.py:194-196). */

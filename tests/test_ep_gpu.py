@@ -64,3 +64,23 @@ def test_single_rank_expert_parallel_equals_local_layer(cuda):
                 assert torch.equal(l3[n].grad, l2[n].grad), n
     finally:
         dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,experts", [(1, 16), (2, 256), (4, 64), (8, 256), (8, 8)])
+def test_peer_plan_kernel_equals_the_host_side_slot_arithmetic(cuda, world, experts):
+    """One launch of b2g_ep_peer_plan gives, for every rank, exactly the slots that the tensor-op formulation
+    (checked on the CPU against a simulated four-rank exchange) computes; empty experts and empty ranks included."""
+    from b2g import ep_peer
+
+    rng = np.random.default_rng(100 * world + experts)
+    counts = rng.integers(0, 400, size=(world, experts)).astype(np.int32)
+    counts[:, rng.integers(0, experts)] = 0          # an expert nobody routes to
+    counts[rng.integers(0, world)] = 0               # a rank without tokens
+    counts_dev = torch.from_numpy(counts).to(cuda)
+    for rank in range(world):
+        want = ep_peer.build_peer_plan(counts_dev, rank)
+        got = ep_peer.build_peer_plan_device(counts_dev, rank)
+        for name in ("my_start", "dest_base", "blk_start", "src_pos", "local_sizes", "local_offsets"):
+            a, b = getattr(want, name), getattr(got, name)
+            assert a.dtype == b.dtype == torch.int32 and a.shape == b.shape, name
+            assert torch.equal(a, b), (name, rank)

@@ -44,6 +44,7 @@ SIGNATURES = {
     "b2g_grouped_lora_up": (_i32, [_vp, _i64, _vp, _i32, _vp, _vp, _i64, _i64, _i32, _i32, _vp]),
     "b2g_ep_scatter_rows": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i64, _i32, _i64, _vp, _vp]),
     "b2g_ep_return_rows": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i64, _vp]),
+    "b2g_ep_peer_plan": (_i32, [_vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "b2g_swiglu_fwd": (_i32, [_vp, _vp, _vp, _i64, _f32, _vp]),
     "b2g_swiglu_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _f32, _vp]),
 }
@@ -81,7 +82,7 @@ KERNELS_PER_CALL = {
     "b2g_dequant": 1, "b2g_qlinear_fwd": 1, "b2g_qlinear_dgrad": 1, "b2g_lora_down": 1, "b2g_lora_wgrad": 2, "b2g_lora_wgrad_static": 2,
     "b2g_router_topk": 1, "b2g_route_plan": 4, "b2g_route_gather": 1, "b2g_route_gather_bwd": 1, "b2g_route_combine": 1,
     "b2g_route_combine_bwd": 1, "b2g_grouped_schedule": 1, "b2g_grouped_fwd": 1, "b2g_grouped_dgrad": 1,
-    "b2g_grouped_lora_down": 1, "b2g_grouped_lora_wgrad": 1, "b2g_grouped_lora_up": 1, "b2g_ep_scatter_rows": 1, "b2g_ep_return_rows": 1, "b2g_swiglu_fwd": 1, "b2g_swiglu_bwd": 1,
+    "b2g_grouped_lora_down": 1, "b2g_grouped_lora_wgrad": 1, "b2g_grouped_lora_up": 1, "b2g_ep_scatter_rows": 1, "b2g_ep_return_rows": 1, "b2g_ep_peer_plan": 1, "b2g_swiglu_fwd": 1, "b2g_swiglu_bwd": 1,
     "b2g_cross_entropy_inplace": 1, "b2g_fixed_grouped_fwd": 8, "b2g_fixed_grouped_dgrad": 8,      # one launch per group (eight in the DeepSeek layout)
 }
 COUNT_LAUNCHES = False

@@ -55,6 +55,19 @@ def build_peer_plan(counts: torch.Tensor, rank: int) -> PeerPlan:
                     local_sizes=local_sizes.to(i32).contiguous(), local_offsets=local_sizes.cumsum(0).to(i32).contiguous())
 
 
+def build_peer_plan_device(counts: torch.Tensor, rank: int) -> PeerPlan:
+    """The same plan as :func:`build_peer_plan` in one kernel launch (``counts``: int32 [G, E] on the GPU)."""
+    g, e = counts.shape
+    per = e // g
+    dev = counts.device
+    buf = torch.empty(2 * e + (per * g + 1) + per * g + 2 * per, dtype=torch.int32, device=dev)
+    my_start, dest_base, blk_start, src_pos, local_sizes, local_offsets = torch.split(buf, [e, e, per * g + 1, per * g, per, per])
+    with torch.cuda.device(dev):
+        _lib.call("b2g_ep_peer_plan", C.c_void_p(counts.data_ptr()), g, e, int(rank), *(C.c_void_p(t.data_ptr()) for t in
+                  (my_start, dest_base, blk_start, src_pos, local_sizes, local_offsets)), C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    return PeerPlan(my_start, dest_base, blk_start, src_pos, local_sizes, local_offsets)
+
+
 class PeerExchange:
     """Symmetric receive / return buffers of one MoE layer and the two exchange kernels."""
 
@@ -148,7 +161,7 @@ def peer_moe_layer(xchg: PeerExchange, hidden: torch.Tensor, top_k_index: torch.
 
     top_k = top_k_index.shape[1]
     sorted_e, perm, inverse, sizes, _ = ops.route_plan(top_k_index.contiguous(), xchg.num_experts)
-    plan = build_peer_plan(xchg.gather_counts(sizes), xchg.rank)
+    plan = build_peer_plan_device(xchg.gather_counts(sizes), xchg.rank)
     local_rows = _PeerDispatch.apply(hidden, perm, inverse, sorted_e, plan, xchg, top_k)
     idx = torch.arange(xchg.experts_per_rank, device=hidden.device, dtype=torch.int64)
     lo = lora or {}

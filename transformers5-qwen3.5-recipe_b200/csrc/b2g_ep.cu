@@ -83,6 +83,64 @@ __global__ void __launch_bounds__(256) return_rows_kernel(const uint4* __restric
   }
 }
 
+
+// Slots of one rank from the all-gathered count matrix counts[G][E] (row g = histogram of rank g's routed rows over
+// the global experts), one CTA, a few thousand integer operations:
+//   my_start[e]   first position of expert e in THIS rank's sorted order
+//   dest_base[e]  slot at e's owner where this rank's rows of e start (owner's earlier experts, then earlier sources)
+//   blk_start[b]  owner side, b = local expert * G + source rank: first row of the block; blk_start[E_l*G] = rows held
+//   src_pos[b]    position of that block's first row in the source rank's sorted order
+//   local_sizes / local_offsets: rows per local expert and their cumulative ends
+constexpr int kPlanMaxExperts = 2048, kPlanMaxRanks = 64;
+
+__global__ void __launch_bounds__(256) peer_plan_kernel(const int32_t* __restrict__ counts, int G, int E, int rank, int32_t* __restrict__ my_start,
+                                                        int32_t* __restrict__ dest_base, int32_t* __restrict__ blk_start,
+                                                        int32_t* __restrict__ src_pos, int32_t* __restrict__ local_sizes,
+                                                        int32_t* __restrict__ local_offsets) {
+  __shared__ int32_t total[kPlanMaxExperts];
+  const int per = E / G, lo = rank * per;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int32_t sum = 0, before = 0;
+    for (int g = 0; g < G; ++g) {
+      const int32_t c = counts[g * E + e];
+      sum += c;
+      if (g < rank) before += c;
+    }
+    total[e] = sum;
+    dest_base[e] = before;          // earlier sources; the owner's earlier experts are added below
+  }
+  __syncthreads();
+  // one thread per owner rank: running sum of the totals of its experts
+  for (int o = threadIdx.x; o < G; o += blockDim.x) {
+    int32_t run = 0;
+    for (int j = 0; j < per; ++j) {
+      const int e = o * per + j;
+      dest_base[e] += run;
+      run += total[e];
+      if (o == rank) { local_sizes[j] = total[e]; local_offsets[j] = run; }
+    }
+  }
+  // one thread per source rank: where each of this rank's local experts starts in that source's sorted order
+  for (int g = threadIdx.x; g < G; g += blockDim.x) {
+    int32_t run = 0;
+    for (int e = 0; e < E; ++e) {
+      if (g == rank) my_start[e] = run;
+      if (e >= lo && e < lo + per) src_pos[(e - lo) * G + g] = run;
+      run += counts[g * E + e];
+    }
+  }
+  // blocks of the owner side in (local expert, source rank) order
+  if (threadIdx.x == 0) {
+    int32_t run = 0;
+    for (int j = 0; j < per; ++j)
+      for (int g = 0; g < G; ++g) {
+        blk_start[j * G + g] = run;
+        run += counts[g * E + lo + j];
+      }
+    blk_start[per * G] = run;
+  }
+}
+
 }  // namespace ep
 }  // namespace b2g
 
@@ -114,6 +172,19 @@ extern "C" int b2g_ep_return_rows(const void* rows, const int32_t* blk_start, co
   ep::return_rows_kernel<<<(int)(want < cap ? want : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(rows), blk_start, src_pos, reinterpret_cast<const unsigned long long*>(peer_ptrs), world, num_blocks, H / 8,
       capacity_rows);
+  B2G_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int b2g_ep_peer_plan(const int32_t* counts, int world, int num_experts, int rank, int32_t* my_start, int32_t* dest_base,
+                                int32_t* blk_start, int32_t* src_pos, int32_t* local_sizes, int32_t* local_offsets, void* stream) {
+  B2G_REQUIRE(world >= 1 && world <= ep::kPlanMaxRanks && num_experts >= world && num_experts <= ep::kPlanMaxExperts &&
+                  num_experts % world == 0, "ep_peer_plan: %d experts over %d ranks is outside what one CTA plans (<= %d experts, <= %d ranks)",
+              num_experts, world, ep::kPlanMaxExperts, ep::kPlanMaxRanks);
+  B2G_REQUIRE(rank >= 0 && rank < world, "ep_peer_plan: rank %d of %d", rank, world);
+  B2G_REQUIRE(counts && my_start && dest_base && blk_start && src_pos && local_sizes && local_offsets, "ep_peer_plan: null pointer");
+  ep::peer_plan_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(counts, world, num_experts, rank, my_start, dest_base, blk_start,
+                                                                         src_pos, local_sizes, local_offsets);
   B2G_CUDA_OK(cudaGetLastError());
   return 0;
 }
