@@ -234,10 +234,12 @@ B2G_API int b2g_grouped_lora_up(const void* p, int64_t ldp, const void* w, int w
  * peer pointers of a symmetric allocation) at row dest_base[e] + (s - my_start[e]).  With perm != NULL the row is
  * gathered from the token matrix (row perm[s] / top_k of src): the token permute of _route_gather_forward_kernel
  * (fast_moe_routing.py:101-123) and the inter-GPU dispatch in one pass; with perm == NULL row s of src is sent.
- * A slot at or beyond capacity_rows is never written; the status word is set to 901 instead. */
+ * A slot at or beyond capacity_rows is never written; the status word is set to 901 instead.  The walk over the rows
+ * starts at the first row of expert first_expert (a global id below the expert count) and wraps around: callers give every
+ * rank a different owner's first expert so that the ranks do not all store to the same owner at once. */
 B2G_API int b2g_ep_scatter_rows(const void* src, const int64_t* perm, int top_k, const int64_t* sorted_expert,
                         const int32_t* my_start, const int32_t* dest_base, const uint64_t* peer_ptrs, int experts_per_rank,
-                        int64_t R, int H, int64_t capacity_rows, int* status, void* stream);
+                        int64_t R, int H, int64_t capacity_rows, int first_expert, int* status, void* stream);
 
 /* Owner side, the inverse: rows of the grouped buffer (blocks ordered by (local expert, source rank), block b
  * spanning rows [blk_start[b], blk_start[b+1]), source rank b % world) go back to their source rank at row

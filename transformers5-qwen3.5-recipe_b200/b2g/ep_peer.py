@@ -110,6 +110,7 @@ class PeerExchange:
             _lib.call("b2g_ep_scatter_rows", C.c_void_p(src.data_ptr()), None if perm is None else C.c_void_p(perm.data_ptr()), int(top_k),
                       C.c_void_p(sorted_expert.data_ptr()), C.c_void_p(plan.my_start.data_ptr()), C.c_void_p(plan.dest_base.data_ptr()),
                       C.c_void_p(self._recv_ptrs[which].data_ptr()), self.experts_per_rank, rows, self.hidden, self.capacity,
+                      ((self.rank + 1) % self.world) * self.experts_per_rank,      # start with the next rank's experts
                       C.c_void_p(ops.status_word(self.device).data_ptr()), C.c_void_p(torch.cuda.current_stream().cuda_stream))
         self.sync()          # every source has delivered
         return self.recv[which]

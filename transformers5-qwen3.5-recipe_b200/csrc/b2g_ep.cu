@@ -18,11 +18,17 @@ namespace ep {
 __global__ void __launch_bounds__(256) scatter_rows_kernel(const uint4* __restrict__ src, const int64_t* __restrict__ perm, int top_k,
                                                            const int64_t* __restrict__ sorted_expert, const int32_t* __restrict__ my_start,
                                                            const int32_t* __restrict__ dest_base, const unsigned long long* __restrict__ peers,
-                                                           int experts_per_rank, int64_t R, int vec_per_row, int64_t capacity, int* status) {
+                                                           int experts_per_rank, int64_t R, int vec_per_row, int64_t capacity, int* status,
+                                                           int first_expert) {
   const int lane = threadIdx.x & 31;
   const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-  for (int64_t s = warp; s < R; s += nwarps) {
+  // Rows are sorted by expert, hence by owner rank.  Walking them from row 0 on every rank would aim all ranks at the
+  // same owner at the same time (one NVLink port takes everything while the others idle), so each rank starts at the
+  // first row of a different owner's experts and wraps around.
+  const int64_t start = my_start[first_expert];
+  for (int64_t s0 = warp; s0 < R; s0 += nwarps) {
+    const int64_t s = s0 + start < R ? s0 + start : s0 + start - R;
     const int e = static_cast<int>(sorted_expert[s]);
     const int owner = e / experts_per_rank;
     const int64_t slot = static_cast<int64_t>(dest_base[e]) + (s - my_start[e]);
@@ -148,16 +154,17 @@ using namespace b2g;
 
 extern "C" int b2g_ep_scatter_rows(const void* src, const int64_t* perm, int top_k, const int64_t* sorted_expert, const int32_t* my_start,
                                    const int32_t* dest_base, const uint64_t* peer_ptrs, int experts_per_rank, int64_t R, int H,
-                                   int64_t capacity_rows, int* status, void* stream) {
+                                   int64_t capacity_rows, int first_expert, int* status, void* stream) {
   B2G_REQUIRE(H > 0 && H % 8 == 0, "ep_scatter_rows: row width %d must be a positive multiple of 8", H);
   B2G_REQUIRE(experts_per_rank >= 1 && capacity_rows >= 0 && R >= 0, "ep_scatter_rows: bad sizes");
   B2G_REQUIRE(perm == nullptr || top_k >= 1, "ep_scatter_rows: top_k must be positive when rows are gathered");
+  B2G_REQUIRE(first_expert >= 0, "ep_scatter_rows: first_expert %d is negative", first_expert);
   if (R == 0) return 0;
   B2G_REQUIRE(src && sorted_expert && my_start && dest_base && peer_ptrs && aligned16(src), "ep_scatter_rows: null or misaligned pointer");
   const int64_t want = (R + 7) / 8, cap = (int64_t)sm_count() * 8;
   ep::scatter_rows_kernel<<<(int)(want < cap ? want : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(src), perm, top_k, sorted_expert, my_start, dest_base, reinterpret_cast<const unsigned long long*>(peer_ptrs),
-      experts_per_rank, R, H / 8, capacity_rows, status);
+      experts_per_rank, R, H / 8, capacity_rows, status, first_expert);
   B2G_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -38,13 +38,16 @@ struct Seg { int expert, row0, rows; };
 
 // ------------------------------------------------------------------------------------------------
 // Projection: P[rows,16] = X[rows,C] . W_e^T  (r <= 16 columns live, the rest zero)
-// CTA = 4 warps x 16 rows; reduction in chunks of 128 columns, 3-stage cp.async ring.
+// CTA = 4 warps x 16 rows; reduction in chunks of 128 columns, 4-stage cp.async ring.
 // ------------------------------------------------------------------------------------------------
 constexpr int kDownRows = 64, kDownBK = 128, kDownStages = 4, kDownStride = kDownBK * 2 + 16;  // 272-byte rows
 constexpr int kDownXBytes = kDownRows * kDownStride, kDownWBytes = kRankPad * kDownStride;
 constexpr int kDownStageBytes = kDownXBytes + kDownWBytes;
 
-__device__ __forceinline__ Seg down_segment(const int4* tiles, int64_t m_total, int item) {
+// Grouped: item = one 64-row slice of a tile of the schedule.  Dense: every CTA owns one contiguous range of
+// `dense_rows` rows (the same byte count for every CTA, so that none runs a round longer than the others) and
+// walks it in slices of 64; `item` is then blockIdx.x + slice * gridDim.x.
+__device__ __forceinline__ Seg down_segment(const int4* tiles, int64_t m_total, int item, int dense_rows) {
   Seg s;
   if (tiles) {
     const int rows_per_tile = tiles[0].y;
@@ -56,10 +59,14 @@ __device__ __forceinline__ Seg down_segment(const int4* tiles, int64_t m_total, 
     const int left = e.z - sub * kDownRows;
     s.rows = left < 0 ? 0 : (left < kDownRows ? left : kDownRows);
   } else {
+    const int cta = item % gridDim.x, slice = item / gridDim.x;
+    const int64_t first = (int64_t)cta * dense_rows + (int64_t)slice * kDownRows;
+    int64_t end = (int64_t)(cta + 1) * dense_rows;
+    if (end > m_total) end = m_total;
+    const int64_t left = end - first;
     s.expert = 0;
-    s.row0 = item * kDownRows;
-    const int64_t left = m_total - s.row0;
-    s.rows = left < kDownRows ? (int)left : kDownRows;
+    s.row0 = (int)first;
+    s.rows = left < 0 ? 0 : (left < kDownRows ? (int)left : kDownRows);
   }
   return s;
 }
@@ -71,13 +78,13 @@ template <bool kWisCR>
 __global__ void __launch_bounds__(128) lora_down_kernel(const __nv_bfloat16* __restrict__ x0, const __nv_bfloat16* __restrict__ x1,
                                                         const __nv_bfloat16* __restrict__ w, float scale, const int4* __restrict__ tiles,
                                                         __nv_bfloat16* __restrict__ out_plain, __nv_bfloat16* __restrict__ out_scaled,
-                                                        int64_t m_total, int C, int r, int dense_items) {
+                                                        int64_t m_total, int C, int r, int dense_rows) {
   extern __shared__ __align__(16) uint8_t sm[];
   const uint32_t sbase = dev::smem_u32(sm);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nseg = x1 ? 2 : 1;
   const int chunks = (C + kDownBK - 1) / kDownBK;
-  const int total_items = tiles ? tiles[0].x * (tiles[0].y / kDownRows) : dense_items;
+  const int total_items = tiles ? tiles[0].x * (tiles[0].y / kDownRows) : (int)gridDim.x * ((dense_rows + kDownRows - 1) / kDownRows);
   const int64_t w_per_expert = (int64_t)nseg * C * r;
   const int total_chunks = nseg * chunks;
 
@@ -89,7 +96,7 @@ __global__ void __launch_bounds__(128) lora_down_kernel(const __nv_bfloat16* __r
   __syncthreads();
 
   for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
-    const Seg s = down_segment(tiles, m_total, item);
+    const Seg s = down_segment(tiles, m_total, item, dense_rows);
     if (s.rows <= 0) continue;
     const __nv_bfloat16* we = w + s.expert * w_per_expert;
     float acc[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
@@ -193,7 +200,7 @@ __global__ void __launch_bounds__(128) lora_down_kernel(const __nv_bfloat16* __r
 
 // ------------------------------------------------------------------------------------------------
 // Factor gradient: G[16, 128-column chunk] = S[rows,16]^T . T[rows, chunk] over one row segment.
-// CTA = 4 warps x 32 columns; rows stream in steps of 64 through a 3-stage cp.async ring.
+// CTA = 4 warps x 32 columns; rows stream in steps of 64 through a 4-stage cp.async ring.
 //   kPartial = true : dense path, segment = one split of M, fp32 partial to the workspace
 //   kPartial = false: grouped path, segment = one expert, scaled bf16 straight to the output
 // ------------------------------------------------------------------------------------------------
@@ -351,7 +358,9 @@ __global__ void __launch_bounds__(128) lora_up_kernel(const __nv_bfloat16* __res
 
 inline int wgrad_splits(int64_t M, int64_t C) {
   const int chunks = (int)((C + kWgCols - 1) / kWgCols);
-  int splits = (4 * sm_count() + chunks - 1) / chunks;
+  // One wave: two CTAs are resident per SM, and chunks * splits never exceeds that, so no CTA waits for a slot and
+  // every CTA streams a long row range (measured: 4.1 / 5.0 TB/s at C = 2048 / 4096 against 3.7 / 4.8 with two waves).
+  int splits = 2 * sm_count() / chunks;
   const int64_t max_splits = (M + kWgRows - 1) / kWgRows;
   if (splits > max_splits) splits = (int)max_splits;
   if (splits < 1) splits = 1;
@@ -373,9 +382,13 @@ static int lora_down_launch(const void* x, const void* x1, const void* w, int w_
   B2G_REQUIRE(aligned16(x) && (!x1 || aligned16(x1)), "%s: activations must be 16-byte aligned", what);
   B2G_REQUIRE(w_is_cr || (reinterpret_cast<uintptr_t>(w) & 3) == 0, "%s: weight must be 4-byte aligned", what);
   const size_t smem = (size_t)lora::kDownStages * lora::kDownStageBytes;
-  const int dense_items = (int)((M + lora::kDownRows - 1) / lora::kDownRows);
-  int grid = sm_count() * 2;
-  if (!tiles && dense_items < grid) grid = dense_items;
+  int grid = sm_count() * 2;       // two resident CTAs per SM
+  int dense_rows = 0;
+  if (!tiles) {
+    const int64_t slices = (M + lora::kDownRows - 1) / lora::kDownRows;
+    if (slices < grid) grid = (int)slices;
+    dense_rows = (int)(((M + grid - 1) / grid + 15) / 16 * 16);   // whole 16-row MMA blocks
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   auto* xb = static_cast<const __nv_bfloat16*>(x);
   auto* x1b = static_cast<const __nv_bfloat16*>(x1);
@@ -385,10 +398,10 @@ static int lora_down_launch(const void* x, const void* x1, const void* w, int w_
   auto* tl = reinterpret_cast<const int4*>(tiles);
   if (w_is_cr) {
     B2G_CUDA_OK(cudaFuncSetAttribute(lora::lora_down_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    lora::lora_down_kernel<true><<<grid, 128, smem, s>>>(xb, x1b, wb, scale, tl, op, os, M, (int)C, r, dense_items);
+    lora::lora_down_kernel<true><<<grid, 128, smem, s>>>(xb, x1b, wb, scale, tl, op, os, M, (int)C, r, dense_rows);
   } else {
     B2G_CUDA_OK(cudaFuncSetAttribute(lora::lora_down_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    lora::lora_down_kernel<false><<<grid, 128, smem, s>>>(xb, x1b, wb, scale, tl, op, os, M, (int)C, r, dense_items);
+    lora::lora_down_kernel<false><<<grid, 128, smem, s>>>(xb, x1b, wb, scale, tl, op, os, M, (int)C, r, dense_rows);
   }
   B2G_CUDA_OK(cudaGetLastError());
   return 0;
