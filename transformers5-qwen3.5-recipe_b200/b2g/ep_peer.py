@@ -3,8 +3,10 @@
 Instead of gather -> NCCL all-to-all -> regroup (``b2g/ep.py``), the token permute and the transfer are one
 kernel: every routed row is read from the token matrix on its source rank and written straight into the owner
 rank's receive buffer, already grouped by (local expert, source rank); the way back is the mirror image.  The
-slots follow from the all-gathered per-rank expert histograms, computed with a handful of small integer ops on
-the device, so no split size is read on the host and nothing is regrouped afterwards.
+slots follow from the all-gathered per-rank expert histograms, computed by one small kernel on the device
+(``build_peer_plan_device``; ``build_peer_plan`` is the same arithmetic as tensor ops, kept as the checkable
+statement of it), so no split size is read on the host and nothing is regrouped afterwards.  Every rank starts
+its scatter at a different owner's experts, so that the ranks do not all store to one GPU at a time.
 
 Buffers are symmetric allocations (one per rank, same size, mapped into every rank): two receive buffers of
 ``capacity`` rows (activations forward, output gradients backward) and two return buffers of the rank's own
