@@ -60,7 +60,9 @@ def main() -> int:
 
     flat = [p.reshape(-1) for p in pk]
     via_nccl = run(lambda hh, ll: ep.cuda_moe_layer(hh, idx, wts, *flat, q4k, i, e, ll, 2.0), hidden, lora, gout)
-    xchg = ep_peer.PeerExchange(t * k, h, e, device=dev)
+    # receive buffers sized for the worst case (every routed row of every rank lands here): the router above is skewed far
+    # beyond the default 1.5x head-room, which the layer would report as status 901 rather than drop rows
+    xchg = ep_peer.PeerExchange(t * k, h, e, capacity_factor=float(world), device=dev)
     for _ in range(2):
         via_peer = run(lambda hh, ll: ep_peer.peer_moe_layer(xchg, hh, idx, wts, *flat, q4k, i, ll, 2.0), hidden, lora, gout)
         for a, b in zip(via_nccl, via_peer):
