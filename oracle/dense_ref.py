@@ -73,3 +73,31 @@ def fixed_grouped_grad_input(dy: torch.Tensor, weights: torch.Tensor) -> torch.T
     groups = weights.shape[0]
     cols = [dy[..., g, :].float() @ weights[g].float() for g in range(groups)]
     return torch.stack(cols, dim=-2)
+
+
+def shared_expert_fwd_bwd(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,
+                          lora: dict[str, tuple[torch.Tensor, torch.Tensor]], scaling: float, dy: torch.Tensor | None,
+                          swiglu_limit: float | None = None, compute_dtype: torch.dtype = torch.float32) -> dict[str, torch.Tensor]:
+    """A dense gated MLP of three LoRA linears, ``down(silu(gate(x)) * up(x))`` (clamped as the DeepSeek experts are when
+    ``swiglu_limit`` is given), each linear the expression of ``lora_linear_fwd_bwd``; ``lora[name] = (A [r,in], B [out,r])``
+    for name in gate, up, down.  Returns y and, with ``dy``, dx and d_<name>_a / d_<name>_b."""
+    need = dy is not None
+    cd = compute_dtype
+    xr = x.detach().to(cd).clone().requires_grad_(need)
+    p = {n: (a.detach().to(cd).clone().requires_grad_(need), b.detach().to(cd).clone().requires_grad_(need)) for n, (a, b) in lora.items()}
+
+    def lin(inp, w, name):
+        a, b = p[name]
+        return torch.addmm(torch.nn.functional.linear(inp, w.to(cd)), inp @ a.t(), b.t(), beta=1, alpha=scaling)
+
+    gate, up = lin(xr, w_gate, "gate"), lin(xr, w_up, "up")
+    if swiglu_limit is not None:
+        gate, up = gate.clamp(max=swiglu_limit), up.clamp(min=-swiglu_limit, max=swiglu_limit)
+    y = lin(torch.nn.functional.silu(gate) * up, w_down, "down")
+    out = {"y": y.detach()}
+    if need:
+        y.backward(dy.to(cd))
+        out["dx"] = xr.grad
+        for n, (a, b) in p.items():
+            out[f"d_{n}_a"], out[f"d_{n}_b"] = a.grad, b.grad
+    return out

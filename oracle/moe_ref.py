@@ -208,3 +208,35 @@ def moe_layer(hidden: torch.Tensor, top_k_index: torch.Tensor, top_k_weights: to
         for n, v in params.items():
             res["d_" + n] = v.grad if v.grad is not None else torch.zeros_like(v)
     return res
+
+
+def expert_slice(rows: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,
+                 lora: dict[str, torch.Tensor] | None, scaling: float, grad_out_rows: torch.Tensor | None = None,
+                 swiglu_limit: float | None = None, compute_dtype: torch.dtype = torch.float32) -> dict[str, torch.Tensor]:
+    """ONE expert of ``moe_layer`` on exactly the rows routed to it: gate|up -> LoRA -> SwiGLU (clamped when
+    ``swiglu_limit`` is given) -> down -> LoRA, and with ``grad_out_rows`` (the cotangent of the expert's output rows)
+    the backward: the rows' input gradient and the expert's four factor gradients.  Weights are this expert's logical
+    [out, in] matrices, ``lora`` its own factors gate_up_a [r,H], gate_up_b [2I,r], down_a [r,I], down_b [H,r].
+    A full-size layer is checked expert by expert with this (fast_moe_lora.py:720-763 restricted to one segment)."""
+    need = grad_out_rows is not None
+    cd = compute_dtype
+    x = rows.detach().to(cd).clone().requires_grad_(need)
+    p = {} if lora is None else {n: v.detach().to(cd).clone().requires_grad_(need) for n, v in lora.items()}
+    gate = x @ w_gate.to(cd).t()
+    up = x @ w_up.to(cd).t()
+    if lora is not None:
+        delta = (x @ p["gate_up_a"].t()) @ p["gate_up_b"].t()
+        dg, du = delta.chunk(2, dim=-1)
+        gate = torch.add(gate, dg, alpha=scaling)
+        up = torch.add(up, du, alpha=scaling)
+    inter = swiglu(gate, up, swiglu_limit)
+    out = inter @ w_down.to(cd).t()
+    if lora is not None:
+        out = torch.add(out, (inter @ p["down_a"].t()) @ p["down_b"].t(), alpha=scaling)
+    res = {"out": out.detach(), "gate": gate.detach(), "up": up.detach(), "inter": inter.detach()}
+    if need:
+        out.backward(grad_out_rows.to(cd))
+        res["d_rows"] = x.grad
+        for n, v in p.items():
+            res["d_" + n] = v.grad
+    return res

@@ -19,7 +19,8 @@ from . import autograd as ag
 from . import ops
 
 try:  # the fork, when present
-    from transformers.integrations.gguf import ALL_GGUF_EXPERTS_FUNCTIONS, GGUFExperts, GGUFGroupedLinear, GGUFLinear  # type: ignore
+    from transformers.integrations.gguf import (ALL_GGUF_EXPERTS_FUNCTIONS, DeepseekV4GGUFExperts, GGUFExperts,  # type: ignore
+                                                GGUFGroupedLinear, GGUFLinear)
     from transformers.integrations.gguf_dequant import GGUFQuantizedTensor, dequantize_gguf_tensor  # type: ignore
 
     HAVE_FORK = True
@@ -143,6 +144,20 @@ except Exception:  # stock transformers, or none
         def forward(self, hidden_states: torch.Tensor, top_k_index: torch.Tensor, top_k_weights: torch.Tensor, **kwargs: Any):
             fn = ALL_GGUF_EXPERTS_FUNCTIONS[self.config._experts_implementation]
             return fn(self, hidden_states, top_k_index, top_k_weights, **kwargs)
+
+    class DeepseekV4GGUFExperts(GGUFExperts):
+        """DeepSeek-V4 expert bank: built from a model config (``num_experts``, ``hidden_size``, ``moe_intermediate_size``,
+        ``swiglu_limit``) with the three packed projections assigned afterwards, as the fork's loader does.  Its
+        ``_apply_split_gate`` clamps before the activation: ``silu(min(gate, L)) * clamp(up, -L, L)``
+        (``test_deepseek_v4_moe_lora.py:194-196``)."""
+
+        def __init__(self, config: Any, device: Any = None, compute_dtype: torch.dtype = torch.bfloat16) -> None:
+            del device          # payloads are assigned by the caller; nothing is allocated here
+            super().__init__(int(config.num_experts), int(config.hidden_size), int(config.moe_intermediate_size), None, None, None,
+                             compute_dtype=compute_dtype, swiglu_limit=float(config.swiglu_limit),
+                             experts_implementation=getattr(config, "_experts_implementation", "eager"))
+            self.config = config
+            self.act_fn = torch.nn.functional.silu
 
 
 class _SwiGLU(torch.autograd.Function):

@@ -11,10 +11,13 @@ Mirrors the parts of the reference's ``deepseek_v4_lora.py`` that sit on the qua
   (``b2g.autograd.fixed_grouped_mmq`` in place of ``torch_ggml_ops.fixed_grouped_mmq``), failing closed when a module
   does not match the contract.
 
-The injection audit of the reference (adapter counts of one particular checkpoint) is trainer-side and not part of this path.
+* ``normalize_peft_path`` / ``audit_deepseek_v4_injection`` (``:165-287``): the check, run once before training, that the
+  adapters landed exactly where the DeepSeek-V4-Flash contract says (383 ordinary wrappers, 43 expert wrappers, 43 frozen
+  grouped projections, the rank-proportional parameter count, bf16 CUDA adapter tensors only, no packed payload trainable).
 """
 from __future__ import annotations
 
+import re
 from types import MethodType
 from typing import Any
 
@@ -29,6 +32,16 @@ DEEPSEEK_V4_TARGET_MODULES_PATTERN = (
     r"^(?!.*\.self_attn\.compressor\.indexer\.)(?:.*\.)?"
     r"(?:q_a_proj|q_b_proj|kv_proj|o_b_proj|gate_proj|up_proj|down_proj|experts)$"
 )
+
+EXPECTED_ORDINARY_WRAPPERS = 383
+EXPECTED_EXPERT_WRAPPERS = 43
+EXPECTED_RANK4_PARAMETERS = 645_609_472
+
+# no adapter may sit on (or train) any of these
+_FORBIDDEN_TRAINABLE_PATHS = (".o_a_proj.", ".mlp.gate.", ".attn_hc.", ".ffn_hc.", ".hc_head.", ".input_layernorm.",
+                              ".post_attention_layernorm.", ".q_a_norm.", ".q_b_norm.", ".kv_norm.", ".sinks", ".position_bias",
+                              ".self_attn.compressor.indexer.", "embed_tokens", "lm_head")
+_ADAPTER_PARAMETER = re.compile(r"\.lora_[AB](?:_down)?\.")
 
 FIXED_GROUPS, FIXED_IN_FEATURES, FIXED_GROUP_OUT_FEATURES, FIXED_QUANT_TYPE = 8, 4096, 1024, 8
 
@@ -108,3 +121,66 @@ def configure_deepseek_v4_grouped_mmq(model: torch.nn.Module) -> dict[str, Any]:
                 module._deepseek_v4_grouped_mmq_enabled = True
             enabled.append(path)
     return {"enabled": len(enabled), "paths": sorted(enabled)}
+
+
+def normalize_peft_path(path: str) -> str:
+    """Module path as it was before PEFT wrapped the model: PEFT's ``base_model.model.`` and a leading ``model.`` are
+    dropped, then decoder-layer paths get the one ``model.`` prefix the adapter contract uses."""
+    for prefix in ("base_model.model.", "model."):
+        if path.startswith(prefix):
+            path = path[len(prefix):]
+    if path.startswith("model.layers."):
+        return path
+    return f"model.{path}" if path.startswith("layers.") else path
+
+
+def audit_deepseek_v4_injection(model: torch.nn.Module, *, expert_wrapper_type: type[torch.nn.Module], rank: int) -> dict[str, Any]:
+    """Validate the complete adapter surface of a wrapped DeepSeek-V4-Flash model before training; raises one
+    ``RuntimeError`` listing every violated rule, otherwise returns the census."""
+    ordinary_types = (DeepseekV4LoraLinear, DeepseekV4GGUFLoraLinear)
+    ordinary, expert, grouped, grouped_trainable = [], [], [], []
+    for path, module in model.named_modules():
+        if isinstance(module, expert_wrapper_type):
+            expert.append(normalize_peft_path(path))
+        elif isinstance(module, ordinary_types):
+            ordinary.append(normalize_peft_path(path))
+        if isinstance(module, GGUFGroupedLinear):
+            grouped.append(normalize_peft_path(path))
+            if module.weight.requires_grad:
+                grouped_trainable.append(path)
+    named = list(model.named_parameters())
+    trainable = [(n, p) for n, p in named if p.requires_grad]
+    n_trainable = sum(p.numel() for _, p in trainable)
+    n_expected = EXPECTED_RANK4_PARAMETERS * rank // 4
+
+    problems: list[str] = []
+    for found, expected, what in ((len(ordinary), EXPECTED_ORDINARY_WRAPPERS, f"{EXPECTED_ORDINARY_WRAPPERS} ordinary wrappers"),
+                                  (len(expert), EXPECTED_EXPERT_WRAPPERS, f"{EXPECTED_EXPERT_WRAPPERS} expert wrappers"),
+                                  (len(grouped), EXPECTED_EXPERT_WRAPPERS, "43 frozen grouped o_a_proj modules"),
+                                  (n_trainable, n_expected, f"{n_expected} rank-{rank} adapter parameters")):
+        if found != expected:
+            problems.append(f"expected {what}, found {found}")
+    checks = (
+        ("non-adapter trainable tensors", [n for n, _ in trainable if _ADAPTER_PARAMETER.search(n) is None]),
+        ("forbidden trainable paths", [n for n, _ in trainable if any(frag in n for frag in _FORBIDDEN_TRAINABLE_PATHS)]),
+        ("non-BF16 adapter tensors", [n for n, p in trainable if p.dtype != torch.bfloat16]),
+        ("adapter tensors outside cuda:0", [n for n, p in trainable if p.device.type != "cuda"]),
+        ("trainable grouped o_a_proj weights", grouped_trainable),
+        ("trainable packed payloads", [n for n, p in named if isinstance(p, GGUFQuantizedTensor) and p.requires_grad]),
+    )
+    problems += [f"{what}: {names[:8]}" for what, names in checks if names]
+    if problems:
+        raise RuntimeError("DeepSeek V4 adapter injection audit failed: " + "; ".join(problems))
+    return {
+        "ordinary_wrappers": len(ordinary),
+        "expert_wrappers": len(expert),
+        "wrapped_modules": len(ordinary) + len(expert),
+        "trainable_tensors": len(trainable),
+        "trainable_parameters": n_trainable,
+        "trainable_bytes": sum(p.numel() * p.element_size() for _, p in trainable),
+        "adapter_dtypes": sorted({str(p.dtype) for _, p in trainable}),
+        "ordinary_target_paths": sorted(ordinary),
+        "expert_target_paths": sorted(expert),
+        "grouped_output_paths": sorted(grouped),
+        "packed_parameters": sum(isinstance(p, GGUFQuantizedTensor) for p in model.parameters()),
+    }
