@@ -11,7 +11,9 @@
  *     ([rows, K / block * block_bytes]); quant types use the GGML ids (8 = Q8_0, 10 = Q2_K,
  *     11 = Q3_K, 12 = Q4_K, 13 = Q5_K, 14 = Q6_K, 16 = IQ2_XXS, 22 = IQ2_S).
  *   - `status` (nullable) is a device int32 the kernels write a non-zero code into when a bounded
- *     device-side wait runs out; it is never written on a healthy run.
+ *     device-side wait runs out (1xx-4xx) or an input is out of range (901 receive buffer too small, 902 label
+ *     outside the vocabulary, 903 expert id outside [0, E), 904 expert offsets beyond the row count); it is
+ *     never written on a healthy run and only the first code is kept.
  *
  * Each entry names the reference interface it stands in for (file:line in
  * woct0rdho/transformers5-qwen3.5-recipe).  The reference reaches these through the third-party
@@ -152,12 +154,14 @@ B2G_API int b2g_router_topk(const void* logits, int logits_dtype, const float* b
 /* Stable counting sort of the flat [T*top_k] expert ids.  idx_dtype: 0 = int32, 1 = int64.
  * Outputs: sorted_expert[R], perm[R], inv_perm[R] (int64), group_sizes[E], offsets[E] (int32,
  * cumulative ends).  `workspace` is int32 scratch of b2g_route_plan_workspace_bytes(T*top_k, E).
+ * An id outside [0, E) is neither counted nor placed and sets status 903: its inv_perm entry and the last
+ * positions of sorted_expert / perm keep what the caller put there (pass zero-filled arrays to keep them in range).
  * Replaces torch.sort + _inverse_permutation_kernel (fast_moe_routing.py:400-410) and the expert
  * histogram of GGUFExperts._prepare_expert_execution (called at fast_moe_lora.py:709). */
 B2G_API int64_t b2g_route_plan_workspace_bytes(int64_t R, int E);
 B2G_API int b2g_route_plan(const void* topk_idx, int idx_dtype, int64_t T, int top_k, int E, int64_t* sorted_expert,
                    int64_t* perm, int64_t* inv_perm, int32_t* group_sizes, int32_t* offsets, void* workspace,
-                   int64_t workspace_bytes, void* stream);
+                   int64_t workspace_bytes, int* status, void* stream);
 
 /* sel[s,:] = hidden[perm[s] / top_k, :]            (_route_gather_forward_kernel, fast_moe_routing.py:101-123) */
 B2G_API int b2g_route_gather(const void* hidden, const int64_t* perm, void* selected, int64_t T, int top_k, int H, void* stream);
@@ -180,10 +184,11 @@ B2G_API int b2g_route_combine_bwd(const void* expert_out, const void* weights, i
 /* Tile table for the persistent grouped kernels: one entry per (active expert, block of rows).
  * expert_indices[G] int64, offsets[G] int32 cumulative ends (the pair produced by
  * GGUFExperts._prepare_expert_execution, fast_moe_lora.py:709-719).  `tiles` is int32 scratch of
- * b2g_grouped_tiles_bytes(R, G) bytes that the grouped calls below consume. */
+ * b2g_grouped_tiles_bytes(R, G) bytes that the grouped calls below consume.  Offsets beyond R are clamped to R (no
+ * tile ever reaches past the R activation rows, nor past the table) and set status 904. */
 B2G_API int64_t b2g_grouped_tiles_bytes(int64_t R, int G);
 B2G_API int b2g_grouped_schedule(const int64_t* expert_indices, const int32_t* offsets, int G, int64_t R, int32_t* tiles,
-                         void* stream);
+                         int* status, void* stream);
 
 /* One persistent launch over the ragged expert segments:
  *   Y0[rows_g, N] = X[rows_g, K] . deq(W0[e_g])^T   and, when payload1 != NULL, Y1 likewise from W1.
@@ -234,7 +239,8 @@ B2G_API int b2g_grouped_lora_up(const void* p, int64_t ldp, const void* w, int w
  * peer pointers of a symmetric allocation) at row dest_base[e] + (s - my_start[e]).  With perm != NULL the row is
  * gathered from the token matrix (row perm[s] / top_k of src): the token permute of _route_gather_forward_kernel
  * (fast_moe_routing.py:101-123) and the inter-GPU dispatch in one pass; with perm == NULL row s of src is sent.
- * A slot at or beyond capacity_rows is never written; the status word is set to 901 instead.  The walk over the rows
+ * A slot at or beyond capacity_rows is never written; the status word is set to 901 instead (b2g_ep_peer_plan clamps the
+ * owner's segments to the same capacity, so the rows that were dropped are not read either).  The walk over the rows
  * starts at the first row of expert first_expert (a global id below the expert count) and wraps around: callers give every
  * rank a different owner's first expert so that the ranks do not all store to the same owner at once. */
 B2G_API int b2g_ep_scatter_rows(const void* src, const int64_t* perm, int top_k, const int64_t* sorted_expert,
@@ -249,21 +255,28 @@ B2G_API int b2g_ep_return_rows(const void* rows, const int32_t* blk_start, const
                        int world, int num_blocks, int H, int64_t capacity_rows, void* stream);
 
 /* Slots of the two exchange kernels for rank `rank`, from the all-gathered histograms counts[world][num_experts]
- * (int32, row g = rows of rank g per global expert; rank g owns experts [g*E/world, (g+1)*E/world)).  One launch;
+ * (int32, row g = rows of rank g per global expert, rows count_stride elements apart; rank g owns experts
+ * [g*E/world, (g+1)*E/world)).  One launch;
  * no value visits the host.  Outputs (int32, device): my_start[E], dest_base[E] as b2g_ep_scatter_rows reads them;
  * blk_start[E/world*world + 1], src_pos[E/world*world] as b2g_ep_return_rows reads them; local_sizes[E/world] and
  * local_offsets[E/world] (cumulative ends) = the expert segments of the rows this rank receives, in the form the
  * grouped products take (the role that the expert histogram of GGUFExperts._prepare_expert_execution, called at
- * fast_moe_lora.py:709, plays on a single GPU). */
-B2G_API int b2g_ep_peer_plan(const int32_t* counts, int world, int num_experts, int rank, int32_t* my_start, int32_t* dest_base,
-                     int32_t* blk_start, int32_t* src_pos, int32_t* local_sizes, int32_t* local_offsets, void* stream);
+ * fast_moe_lora.py:709, plays on a single GPU).  blk_start, local_sizes and local_offsets are clamped to capacity_rows, the
+ * row count of this rank's receive buffer; when the rows sent to this rank exceed it, status 901 is set and the rows past
+ * the capacity are neither stored (b2g_ep_scatter_rows) nor read by anything that follows this plan. */
+B2G_API int b2g_ep_peer_plan(const int32_t* counts, int64_t count_stride, int world, int num_experts, int rank, int32_t* my_start,
+                     int32_t* dest_base, int32_t* blk_start, int32_t* src_pos, int32_t* local_sizes, int32_t* local_offsets,
+                     int64_t capacity_rows, int* status, void* stream);
 
 /* SwiGLU between the two grouped products: z = silu(g) * u (optionally clamped as the DeepSeek
  * experts do: g <= limit, |u| <= limit; limit <= 0 disables).  Replaces GGUFExperts._apply_split_gate
- * (called at fast_moe_lora.py:747; clamp semantics at test_deepseek_v4_moe_lora.py:194-196). */
-B2G_API int b2g_swiglu_fwd(const void* gate, const void* up, void* z, int64_t n, float limit, void* stream);
-B2G_API int b2g_swiglu_bwd(const void* gate, const void* up, const void* dz, void* dgate, void* dup, int64_t n, float limit,
+ * (called at fast_moe_lora.py:747; clamp semantics at test_deepseek_v4_moe_lora.py:194-196).  n = elements of each tensor.
+ * live_rows (nullable, device int32): only the first *live_rows rows of `cols` elements are processed, for tensors that are
+ * the partly filled receive buffer of an expert-parallel exchange, whose fill count never visits the host. */
+B2G_API int b2g_swiglu_fwd(const void* gate, const void* up, void* z, int64_t n, float limit, const int32_t* live_rows, int64_t cols,
                    void* stream);
+B2G_API int b2g_swiglu_bwd(const void* gate, const void* up, const void* dz, void* dgate, void* dup, int64_t n, float limit,
+                   const int32_t* live_rows, int64_t cols, void* stream);
 
 #ifdef __cplusplus
 }

@@ -3,10 +3,12 @@
 Every rank holds its own tokens and its own experts.  The layer is evaluated three ways on the same inputs:
   1. peer stores over NVLink (b2g/ep_peer.py), twice, so that the second call reuses the symmetric buffers;
   2. NCCL all-to-all (b2g/ep.py);
-  3. on one device: all ranks' tokens and all experts gathered onto this rank, plain single-GPU layer.
+  3. on one device: all ranks' tokens and all experts gathered onto this rank, plain single-GPU layer;
+  4. peer stores again with the token range in two chunks (exchange stream beside the compute stream) and the experts
+     placed over the ranks by load instead of in contiguous blocks.
 1 and 2 run the same kernels on the same rows in the same order and must agree bit for bit.  Against 3 the outputs
-and token gradients are compared exactly (a row's result does not depend on which rows share its tile) and the factor
-gradients within rel-L2 1e-2 (their sums over rows run in a different order).
+and token gradients of 1 and 4 are compared exactly (a row's result does not depend on which rows share its tile) and
+the factor gradients within rel-L2 1e-2 (their sums over rows run in a different order).
 Prints one line "rank R: OK" or raises.
 """
 import os
@@ -60,9 +62,9 @@ def main() -> int:
 
     flat = [p.reshape(-1) for p in pk]
     via_nccl = run(lambda hh, ll: ep.cuda_moe_layer(hh, idx, wts, *flat, q4k, i, e, ll, 2.0), hidden, lora, gout)
-    # receive buffers sized for the worst case (every routed row of every rank lands here): the router above is skewed far
-    # beyond the default 1.5x head-room, which the layer would report as status 901 rather than drop rows
-    xchg = ep_peer.PeerExchange(t * k, h, e, capacity_factor=float(world), device=dev)
+    # receive buffers default to the worst case (every routed row of every rank lands here), so the skewed router above fits
+    xchg = ep_peer.PeerExchange(t * k, h, e, device=dev)
+    assert xchg.capacity >= world * t * k
     for _ in range(2):
         via_peer = run(lambda hh, ll: ep_peer.peer_moe_layer(xchg, hh, idx, wts, *flat, q4k, i, ll, 2.0), hidden, lora, gout)
         for a, b in zip(via_nccl, via_peer):
@@ -88,6 +90,22 @@ def main() -> int:
         want = want[mine].float()
         err = float((got.float() - want).norm() / want.norm().clamp_min(1e-20))
         assert err <= 1e-2, (name, err)
+
+    # two chunks, load-aware placement: this rank now holds the experts the placement gives it
+    load = torch.bincount(all_idx.flatten(), minlength=e).float()
+    placement = ep_peer.balanced_placement(load, world)
+    order = ep_peer.experts_of_rank(placement, rank, world).to(dev)
+    pk_placed = [p.reshape(e, -1).index_select(0, order).reshape(-1) for p in all_pk]
+    lora_placed = {n: v.index_select(0, order) for n, v in all_lora.items()}
+    xchg2 = ep_peer.PeerExchange(t * k, h, e, device=dev, chunks=2, placement=placement)
+    for _ in range(2):
+        placed = run(lambda hh, ll: ep_peer.peer_moe_layer(xchg2, hh, idx, wts, *pk_placed, q4k, i, ll, 2.0), hidden, lora_placed, gout)
+        assert torch.equal(placed[0], whole[0][rows]), "chunked / placed outputs differ from the single-device layer"
+        assert torch.equal(placed[1], whole[1][rows]), "chunked / placed token gradients differ from the single-device layer"
+        for got, want, name in zip(placed[2:], whole[2:], lora):
+            want = want.index_select(0, order).float()
+            err = float((got.float() - want).norm() / want.norm().clamp_min(1e-20))
+            assert err <= 1e-2, (name, err)
     ops.check_status()
     print(f"rank {rank}: OK", flush=True)
     dist.destroy_process_group()

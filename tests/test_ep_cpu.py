@@ -181,3 +181,45 @@ def test_peer_exchange_plan_places_every_row_once_and_returns_it():
                 assert recv[o][j].tolist() == [src, pos]
                 assert int(plans[src]["expert_indices"][pos]) == o * per + b // g_ranks
         assert pp[o].local_offsets.tolist() == torch.cumsum(pp[o].local_sizes, 0).tolist()
+
+
+def test_a_receive_buffer_that_is_too_small_clamps_every_owner_side_segment():
+    """With a capacity below the rows an owner receives, the plan's segments and blocks stop at the capacity: the grouped
+    products and the return walk that follow the plan touch no row at or beyond it (the scatter drops those rows)."""
+    from b2g import ep_peer
+
+    counts = torch.tensor([[5, 0, 7, 1], [2, 9, 0, 4]], dtype=torch.int32)          # 2 ranks, 4 experts, rank 0 owns experts 0-1
+    full = ep_peer.build_peer_plan(counts, 0)
+    assert full.local_offsets.tolist() == [7, 16] and full.blk_start.tolist() == [0, 5, 7, 7, 16]
+    cut = ep_peer.build_peer_plan(counts, 0, capacity=10)
+    assert cut.local_offsets.tolist() == [7, 10] and cut.local_sizes.tolist() == [7, 3]
+    assert cut.blk_start.tolist() == [0, 5, 7, 7, 10]
+    assert torch.equal(cut.dest_base, full.dest_base) and torch.equal(cut.my_start, full.my_start)   # the source side is not clamped:
+    # it is the scatter that compares every slot with the capacity
+    none = ep_peer.build_peer_plan(counts, 0, capacity=0)
+    assert none.local_sizes.tolist() == [0, 0] and none.blk_start.tolist() == [0, 0, 0, 0, 0]
+
+
+def test_balanced_placement_spreads_a_skewed_router():
+    """The benchmark's skewed router (logits N(0,1) + a per-expert bias N(0,0.5), top-8 of 256): contiguous blocks of 32
+    experts load the busiest of 8 ranks well above the mean, the load-aware placement brings it within a few percent, with
+    exactly 32 experts on every rank and a table that inverts cleanly."""
+    from b2g import ep_peer
+
+    gen = torch.Generator().manual_seed(19260817 + 4)
+    e, world, tokens, k = 256, 8, 16384, 8
+    logits = torch.randn(tokens, e, generator=gen) + torch.randn(e, generator=gen) * 0.5
+    load = torch.bincount(logits.topk(k, 1).indices.flatten(), minlength=e).double()
+    plain = ep_peer.rank_loads(load, ep_peer.contiguous_placement(e), world)
+    placement = ep_peer.balanced_placement(load, world)
+    spread = ep_peer.rank_loads(load, placement, world)
+    assert sorted(placement.tolist()) == list(range(e))
+    assert torch.bincount(placement // (e // world), minlength=world).tolist() == [e // world] * world
+    assert float(plain.max() / plain.mean()) > 1.1
+    assert float(spread.max() / spread.mean()) < 1.03
+    for rank in range(world):
+        mine = ep_peer.experts_of_rank(placement, rank, world)
+        assert (placement[mine] == torch.arange(rank * 32, (rank + 1) * 32)).all()
+    assert torch.equal(ep_peer.balanced_placement(load, world), placement)          # deterministic
+    with pytest.raises(ValueError, match="do not divide"):
+        ep_peer.balanced_placement(load[:255], world)

@@ -57,11 +57,61 @@ def test_single_rank_expert_parallel_equals_local_layer(cuda):
         for _ in range(2):                                   # twice: the second call reuses the buffers
             h3 = hidden.clone().requires_grad_(True)
             l3 = {n: v.clone().requires_grad_(True) for n, v in lora.items()}
-            out3 = ep_peer.peer_moe_layer(xchg, h3, idx, wts, *pk, go.Q4_K, i, l3, 2.0)
+            w3 = wts.clone().requires_grad_(True)
+            out3 = ep_peer.peer_moe_layer(xchg, h3, idx, w3, *pk, go.Q4_K, i, l3, 2.0)
             out3.backward(gout)
             assert torch.equal(out3, out2) and torch.equal(h3.grad, h2.grad)
             for n in lora:
                 assert torch.equal(l3[n].grad, l2[n].grad), n
+        w2 = wts.clone().requires_grad_(True)
+        plan = routing.build_plan(hidden, idx, w2, e)
+        routing.combine(ex.detach(), plan).backward(gout)
+        assert torch.equal(w3.grad, w2.grad)
+
+        # the token range in three chunks on two streams (exchange beside the expert products) and the experts placed by load:
+        # outputs and token gradients are the same bits (a row's result does not depend on its neighbours), factor gradients
+        # are sums over rows taken chunk by chunk
+        load = torch.bincount(idx.flatten().cpu(), minlength=e).float()
+        placement = ep_peer.balanced_placement(load, 1)
+        order = ep_peer.experts_of_rank(placement, 0, 1).to(cuda)
+        pk_placed = [p.reshape(e, -1).index_select(0, order).reshape(-1) for p in pk]
+        lora_placed = {n: v.index_select(0, order) for n, v in lora.items()}
+        xchg3 = ep_peer.PeerExchange(t * k, h, e, device=cuda, chunks=3, placement=placement)
+        assert xchg3.token_bounds(t) == [(0, 100), (100, 200), (200, 300)] and xchg3.token_bounds(7) == [(0, 3), (3, 5), (5, 7)]
+        xchg3.profile = True
+        for _ in range(2):
+            h4 = hidden.clone().requires_grad_(True)
+            l4 = {n: v.clone().requires_grad_(True) for n, v in lora_placed.items()}
+            out4 = ep_peer.peer_moe_layer(xchg3, h4, idx, wts, *pk_placed, go.Q4_K, i, l4, 2.0)
+            out4.backward(gout)
+            assert torch.equal(out4, out2) and torch.equal(h4.grad, h2.grad)
+            for n in lora:
+                want = l2[n].grad.index_select(0, order).float()
+                err = float((l4[n].grad.float() - want).norm() / want.norm())
+                assert err < 1e-2, (n, err)
+        phases = xchg3.phase_ms()
+        assert {"dispatch", "experts_forward", "return", "combine", "experts_backward", "gather_backward"} <= set(phases)
+
+        # a receive buffer smaller than the routed rows: rows beyond it are dropped, everything downstream is clamped to it,
+        # the status word says so, and the next ordinary call is untouched by it
+        from b2g import ops
+
+        ops.check_status()
+        small = ep_peer.PeerExchange(t * k, h, e, device=cuda, capacity_factor=0.5)
+        assert small.capacity < t * k
+        h5 = hidden.clone().requires_grad_(True)
+        out5 = ep_peer.peer_moe_layer(small, h5, idx, wts, *pk, go.Q4_K, i, {n: v.clone().requires_grad_(True) for n, v in lora.items()}, 2.0)
+        out5.backward(gout)
+        torch.cuda.synchronize()
+        assert int(small.plans[0].local_offsets[-1]) == small.capacity and int(small.plans[0].blk_start[-1]) == small.capacity
+        assert int(small.plans[0].local_sizes.sum()) == small.capacity
+        with pytest.raises(Exception, match="901"):
+            ops.check_status()
+        h6 = hidden.clone().requires_grad_(True)
+        out6 = ep_peer.peer_moe_layer(xchg, h6, idx, wts, *pk, go.Q4_K, i, {n: v.clone().requires_grad_(True) for n, v in lora.items()}, 2.0)
+        out6.backward(gout)
+        assert torch.equal(out6, out2) and torch.equal(h6.grad, h2.grad)
+        ops.check_status()
     finally:
         dist.destroy_process_group()
 
@@ -77,10 +127,18 @@ def test_peer_plan_kernel_equals_the_host_side_slot_arithmetic(cuda, world, expe
     counts[:, rng.integers(0, experts)] = 0          # an expert nobody routes to
     counts[rng.integers(0, world)] = 0               # a rank without tokens
     counts_dev = torch.from_numpy(counts).to(cuda)
+    from b2g import ops
+
     for rank in range(world):
-        want = ep_peer.build_peer_plan(counts_dev, rank)
-        got = ep_peer.build_peer_plan_device(counts_dev, rank)
-        for name in ("my_start", "dest_base", "blk_start", "src_pos", "local_sizes", "local_offsets"):
-            a, b = getattr(want, name), getattr(got, name)
-            assert a.dtype == b.dtype == torch.int32 and a.shape == b.shape, name
-            assert torch.equal(a, b), (name, rank)
+        for capacity in (None, int(counts[:, rank * (experts // world):(rank + 1) * (experts // world)].sum()) // 2):
+            want = ep_peer.build_peer_plan(counts_dev, rank, capacity)
+            got = ep_peer.build_peer_plan_device(counts_dev, rank, capacity)
+            for name in ("my_start", "dest_base", "blk_start", "src_pos", "local_sizes", "local_offsets"):
+                a, b = getattr(want, name), getattr(got, name)
+                assert a.dtype == b.dtype == torch.int32 and a.shape == b.shape, name
+                assert torch.equal(a, b), (name, rank, capacity)
+            overflowed = capacity is not None and int(want.local_offsets[-1]) == capacity and capacity > 0
+            torch.cuda.synchronize()
+            code = int(ops.status_word(cuda).item())
+            ops.status_word(cuda).zero_()
+            assert code == (901 if overflowed else 0), (rank, capacity, code)

@@ -286,73 +286,91 @@ def grouped_mmq_pair(x, payload0, payload1, expert_indices, expert_offsets, quan
     return torch.ops.b2g.grouped_mmq_pair(x, payload0, payload1, expert_indices, expert_offsets, int(quant_type), int(out_features))
 
 
-class _GroupedLoraExperts(torch.autograd.Function):
-    """Pair product + LoRA, SwiGLU, down product + LoRA over sorted expert segments.
+def expert_block_forward(sel, gate_p, up_p, down_p, quant_gu, quant_down, inter_dim, expert_indices, expert_offsets, offsets_full,
+                         gu_a, gu_b, down_a, down_b, scaling, swiglu_limit):
+    """Pair product + LoRA, SwiGLU, down product + LoRA over sorted expert segments: ``(out, saved)``.
 
-    Saves the activations the backward needs (selected rows, gate, up, the two rank projections)
-    and recomputes the SwiGLU output, so nothing of size [rows, hidden] is kept twice.
-    """
+    ``saved`` is what :func:`expert_block_backward` needs (selected rows, gate, up, the two rank projections and, with
+    adapters, the SwiGLU output), so nothing of size [rows, hidden] is kept twice.  Plain functions, so that a caller that
+    schedules its own backward (the expert-parallel layer) can use them outside an autograd node."""
+    rows, hidden = sel.shape
+    tiles = ops.grouped_schedule(expert_indices, expert_offsets, rows)
+    e = _payload_experts(gate_p, quant_gu, inter_dim, hidden)
+    has_lora = gu_a is not None
+    xa = xas = za = zas = None
+    r = 0
+    if has_lora:
+        r = gu_a.shape[1]
+        xa, xas = ops.grouped_lora_down(sel, None, gu_a.contiguous(), False, scaling, r, tiles, zero=False)
+        gate, up = ops.grouped_fwd(sel, gate_p.reshape(-1), up_p.reshape(-1), quant_gu, inter_dim, e, tiles, xas,
+                                   ops.pad_rank_cols(gu_b))
+    else:
+        gate, up = ops.grouped_fwd(sel, gate_p.reshape(-1), up_p.reshape(-1), quant_gu, inter_dim, e, tiles)
+    # the last cumulative end = rows that hold data; an expert-parallel receive buffer is larger than that
+    live = offsets_full[-1:] if offsets_full is not None and offsets_full.numel() else None
+    z = ops.swiglu_fwd(gate, up, swiglu_limit, live)
+    if has_lora:
+        za, zas = ops.grouped_lora_down(z, None, down_a.contiguous(), False, scaling, r, tiles, zero=False)
+        out = ops.grouped_fwd(z, down_p.reshape(-1), None, quant_down, hidden, e, tiles, zas, ops.pad_rank_cols(down_b))
+    else:
+        out = ops.grouped_fwd(z, down_p.reshape(-1), None, quant_down, hidden, e, tiles)
+    # z is kept for the down-projection factor gradient (rows x inter_dim bf16: small next to 180 GB, and cheaper than a
+    # second pass over gate and up in the backward); without adapters nothing in the backward reads it
+    tensors = (sel, gate_p, up_p, down_p, tiles, offsets_full, gate, up, xa, za, gu_a, gu_b, down_a, down_b, z if has_lora else None)
+    meta = (int(quant_gu), int(quant_down), int(inter_dim), e, r, float(scaling), float(swiglu_limit), has_lora)
+    return out, (tensors, meta)
+
+
+def expert_block_backward(saved, d_out):
+    """``(d_sel, d_gate_up_a, d_gate_up_b, d_down_a, d_down_b)`` from what :func:`expert_block_forward` saved."""
+    (sel, gate_p, up_p, down_p, tiles, offsets_full, gate, up, xa, za, gu_a, gu_b, down_a, down_b, z), meta = saved
+    quant_gu, quant_down, inter_dim, e, r, scaling, limit, has_lora = meta
+    hidden = sel.shape[1]
+    d_out = d_out.contiguous()
+    d_gu_a = d_gu_b = d_down_a = d_down_b = None
+    if has_lora:
+        # down projection: dZ = dOut.deq(Wd) + s.(dOut.Bd).Ad ; dAd = s.(dOut.Bd)^T.Z ; dBd = s.dOut^T.(Z.Ad^T)
+        dob, dobs = ops.grouped_lora_down(d_out, None, down_b.transpose(1, 2).contiguous(), False, scaling, r, tiles, zero=False)
+        dz = ops.grouped_dgrad(d_out, None, down_p.reshape(-1), None, quant_down, inter_dim, e, tiles, dobs,
+                               ops.pad_rank_rows(down_a))
+        d_down_a = torch.empty_like(down_a)
+        ops.grouped_lora_wgrad(dob, z, scaling, r, offsets_full, d_down_a, False)
+        d_down_b = torch.empty_like(down_b)
+        ops.grouped_lora_wgrad(za, d_out, scaling, r, offsets_full, d_down_b, True)
+    else:
+        dz = ops.grouped_dgrad(d_out, None, down_p.reshape(-1), None, quant_down, inter_dim, e, tiles)
+    live = offsets_full[-1:] if offsets_full is not None and offsets_full.numel() else None
+    d_gate, d_up = ops.swiglu_bwd(gate, up, dz, limit, live)
+    if has_lora:
+        # gate|up: dX = dG.deq(Wg) + dU.deq(Wu) + s.([dG|dU].Bgu).Agu
+        dgb, dgbs = ops.grouped_lora_down(d_gate, d_up, gu_b.transpose(1, 2).contiguous(), False, scaling, r, tiles, zero=False)
+        d_sel = ops.grouped_dgrad(d_gate, d_up, gate_p.reshape(-1), up_p.reshape(-1), quant_gu, hidden, e, tiles, dgbs,
+                                  ops.pad_rank_rows(gu_a))
+        d_gu_a = torch.empty_like(gu_a)
+        ops.grouped_lora_wgrad(dgb, sel, scaling, r, offsets_full, d_gu_a, False)
+        d_gu_b = torch.empty_like(gu_b)
+        ops.grouped_lora_wgrad(xa, d_gate, scaling, r, offsets_full, d_gu_b, True, 0)
+        ops.grouped_lora_wgrad(xa, d_up, scaling, r, offsets_full, d_gu_b, True, inter_dim)
+    else:
+        d_sel = ops.grouped_dgrad(d_gate, d_up, gate_p.reshape(-1), up_p.reshape(-1), quant_gu, hidden, e, tiles)
+    return d_sel, d_gu_a, d_gu_b, d_down_a, d_down_b
+
+
+class _GroupedLoraExperts(torch.autograd.Function):
+    """The expert block (:func:`expert_block_forward` / :func:`expert_block_backward`) as one autograd node."""
 
     @staticmethod
     def forward(ctx, sel, gate_p, up_p, down_p, quant_gu, quant_down, inter_dim, expert_indices, expert_offsets, offsets_full,
                 gu_a, gu_b, down_a, down_b, scaling, swiglu_limit):
-        rows, hidden = sel.shape
-        tiles = ops.grouped_schedule(expert_indices, expert_offsets, rows)
-        e = _payload_experts(gate_p, quant_gu, inter_dim, hidden)
-        has_lora = gu_a is not None
-        xa = xas = za = zas = None
-        r = 0
-        if has_lora:
-            r = gu_a.shape[1]
-            xa, xas = ops.grouped_lora_down(sel, None, gu_a.contiguous(), False, scaling, r, tiles, zero=False)
-            gate, up = ops.grouped_fwd(sel, gate_p.reshape(-1), up_p.reshape(-1), quant_gu, inter_dim, e, tiles, xas,
-                                       ops.pad_rank_cols(gu_b))
-        else:
-            gate, up = ops.grouped_fwd(sel, gate_p.reshape(-1), up_p.reshape(-1), quant_gu, inter_dim, e, tiles)
-        z = ops.swiglu_fwd(gate, up, swiglu_limit)
-        if has_lora:
-            za, zas = ops.grouped_lora_down(z, None, down_a.contiguous(), False, scaling, r, tiles, zero=False)
-            out = ops.grouped_fwd(z, down_p.reshape(-1), None, quant_down, hidden, e, tiles, zas, ops.pad_rank_cols(down_b))
-        else:
-            out = ops.grouped_fwd(z, down_p.reshape(-1), None, quant_down, hidden, e, tiles)
-        # z is kept for the down-projection factor gradient (rows x inter_dim bf16: small next to 180 GB, and cheaper than a
-        # second pass over gate and up in the backward); without adapters nothing in the backward reads it
-        ctx.save_for_backward(sel, gate_p, up_p, down_p, tiles, offsets_full, gate, up, xa, za, gu_a, gu_b, down_a, down_b,
-                              z if has_lora else None)
-        ctx.meta = (int(quant_gu), int(quant_down), int(inter_dim), e, r, float(scaling), float(swiglu_limit), has_lora)
+        out, (tensors, meta) = expert_block_forward(sel, gate_p, up_p, down_p, quant_gu, quant_down, inter_dim, expert_indices,
+                                                    expert_offsets, offsets_full, gu_a, gu_b, down_a, down_b, scaling, swiglu_limit)
+        ctx.save_for_backward(*tensors)
+        ctx.meta = meta
         return out
 
     @staticmethod
     def backward(ctx, d_out):
-        sel, gate_p, up_p, down_p, tiles, offsets_full, gate, up, xa, za, gu_a, gu_b, down_a, down_b, z = ctx.saved_tensors
-        quant_gu, quant_down, inter_dim, e, r, scaling, limit, has_lora = ctx.meta
-        hidden = sel.shape[1]
-        d_out = d_out.contiguous()
-        d_gu_a = d_gu_b = d_down_a = d_down_b = None
-        if has_lora:
-            # down projection: dZ = dOut.deq(Wd) + s.(dOut.Bd).Ad ; dAd = s.(dOut.Bd)^T.Z ; dBd = s.dOut^T.(Z.Ad^T)
-            dob, dobs = ops.grouped_lora_down(d_out, None, down_b.transpose(1, 2).contiguous(), False, scaling, r, tiles, zero=False)
-            dz = ops.grouped_dgrad(d_out, None, down_p.reshape(-1), None, quant_down, inter_dim, e, tiles, dobs,
-                                   ops.pad_rank_rows(down_a))
-            d_down_a = torch.empty_like(down_a)
-            ops.grouped_lora_wgrad(dob, z, scaling, r, offsets_full, d_down_a, False)
-            d_down_b = torch.empty_like(down_b)
-            ops.grouped_lora_wgrad(za, d_out, scaling, r, offsets_full, d_down_b, True)
-        else:
-            dz = ops.grouped_dgrad(d_out, None, down_p.reshape(-1), None, quant_down, inter_dim, e, tiles)
-        d_gate, d_up = ops.swiglu_bwd(gate, up, dz, limit)
-        if has_lora:
-            # gate|up: dX = dG.deq(Wg) + dU.deq(Wu) + s.([dG|dU].Bgu).Agu
-            dgb, dgbs = ops.grouped_lora_down(d_gate, d_up, gu_b.transpose(1, 2).contiguous(), False, scaling, r, tiles, zero=False)
-            d_sel = ops.grouped_dgrad(d_gate, d_up, gate_p.reshape(-1), up_p.reshape(-1), quant_gu, hidden, e, tiles, dgbs,
-                                      ops.pad_rank_rows(gu_a))
-            d_gu_a = torch.empty_like(gu_a)
-            ops.grouped_lora_wgrad(dgb, sel, scaling, r, offsets_full, d_gu_a, False)
-            d_gu_b = torch.empty_like(gu_b)
-            ops.grouped_lora_wgrad(xa, d_gate, scaling, r, offsets_full, d_gu_b, True, 0)
-            ops.grouped_lora_wgrad(xa, d_up, scaling, r, offsets_full, d_gu_b, True, inter_dim)
-        else:
-            d_sel = ops.grouped_dgrad(d_gate, d_up, gate_p.reshape(-1), up_p.reshape(-1), quant_gu, hidden, e, tiles)
+        d_sel, d_gu_a, d_gu_b, d_down_a, d_down_b = expert_block_backward((ctx.saved_tensors, ctx.meta), d_out)
         return (d_sel, None, None, None, None, None, None, None, None, None, d_gu_a, d_gu_b, d_down_a, d_down_b, None, None)
 
 

@@ -8,6 +8,7 @@ instead of copying behind the caller's back.
 from __future__ import annotations
 
 import ctypes as C
+import weakref
 from typing import Optional
 
 import torch
@@ -74,7 +75,8 @@ def status_word(device: torch.device) -> torch.Tensor:
 def check_status(device: Optional[torch.device] = None) -> None:
     """Synchronise and raise if any kernel on the device reported a problem through the status word: a bounded wait that
     ran out (sites 1xx-4xx), a receive buffer too small for an expert-parallel exchange (901), a label outside the
-    vocabulary in the cross-entropy kernel (902)."""
+    vocabulary in the cross-entropy kernel (902), an expert id outside the expert count in the routing plan (903), expert
+    offsets beyond the rows of a grouped product (904)."""
     devs = [device.index if device is not None and device.index is not None else torch.cuda.current_device()] \
         if device is not None else list(_status)
     for idx in devs:
@@ -82,7 +84,10 @@ def check_status(device: Optional[torch.device] = None) -> None:
             code = int(_status[idx].item())
             if code:
                 _status[idx].zero_()
-                what = {901: "an expert-parallel receive buffer was too small", 902: "a cross-entropy target was outside the vocabulary"}.get(
+                what = {901: "an expert-parallel receive buffer was too small (rows beyond it were dropped)",
+                        902: "a cross-entropy target was outside the vocabulary",
+                        903: "an expert id was outside the expert count (its route was dropped)",
+                        904: "expert offsets reached beyond the rows of a grouped product (they were clamped)"}.get(
                     code, "a libb2g kernel gave up a bounded wait")
                 raise _lib.B2GError(f"{what} on cuda:{idx} (status {code})")
 
@@ -138,19 +143,41 @@ def _check_payload(payload: torch.Tensor, qtype: int, rows: int, k: int, what: s
 PADDED_ROWS = 0x100     # B2G_PADDED_ROWS: flag on the type id, "payload rows are padded to a multiple of 16 bytes"
 
 
+# Padded copies of frozen payloads whose rows are not 16-byte multiples, made ONCE per payload and kept for as long as the
+# payload itself lives: key = (storage address, byte count, tensor version), value = (weak reference to the payload's
+# storage owner, padded copy).  A frozen weight is padded on its first product and never again.
+_padded: dict[tuple[int, int, int], tuple[weakref.ref, torch.Tensor]] = {}
+
+
+def pad_payload_rows(payload: torch.Tensor, qtype: int, rows: int, k: int) -> torch.Tensor:
+    """``payload`` copied into rows padded to the next multiple of 16 bytes (what ``B2G_PADDED_ROWS`` announces)."""
+    pitch = payload_row_bytes(qtype, k)
+    padded = (pitch + 15) // 16 * 16
+    out = torch.zeros(rows, padded, dtype=torch.uint8, device=payload.device)
+    out[:, :pitch] = payload.reshape(rows, pitch)
+    return out.reshape(-1)
+
+
 def _tma_payload(payload: torch.Tensor, qtype: int, rows: int, k: int):
     """The payload as the matrix-product kernels take it, and the type argument to pass with it.
 
     TMA needs row pitches that are multiples of 16 bytes.  Q4_K, Q5_K and Q8_0 rows always are; the other formats' rows
-    only for some widths (a 512-wide IQ2_XXS row is 132 bytes).  Such payloads are copied into rows padded to the next
-    multiple of 16 -- a pass over the packed bytes, a few percent of the product that follows -- and flagged."""
+    only for some widths (a 512-wide IQ2_XXS row is 132 bytes).  Such a payload is copied into padded rows the first time
+    a product sees it; the copy is cached beside the (frozen) payload and reused by every later forward and backward, so
+    no call after the first moves or allocates packed bytes.  A payload that was modified in place (its version counter
+    moved) is padded again."""
     pitch = payload_row_bytes(qtype, k)
     if pitch % 16 == 0:
         return payload, int(qtype)
-    padded = (pitch + 15) // 16 * 16
-    out = torch.zeros(rows, padded, dtype=torch.uint8, device=payload.device)
-    out[:, :pitch] = payload.reshape(rows, pitch)
-    return out.reshape(-1), int(qtype) | PADDED_ROWS
+    key = (payload.data_ptr(), payload.numel(), payload._version)
+    hit = _padded.get(key)
+    if hit is not None and hit[0]() is not None:
+        return hit[1], int(qtype) | PADDED_ROWS
+    for stale in [kk for kk, (ref, _) in _padded.items() if ref() is None]:
+        del _padded[stale]
+    out = pad_payload_rows(payload, qtype, rows, k)
+    _padded[key] = (weakref.ref(payload.untyped_storage()), out)
+    return out, int(qtype) | PADDED_ROWS
 
 
 # --------------------------------------------------------------------------------------
@@ -368,16 +395,17 @@ def route_plan(top_k_index: torch.Tensor, num_experts: int = 256):
     t, k = top_k_index.shape
     r = t * k
     dev = top_k_index.device
-    sorted_e = torch.empty(r, dtype=torch.int64, device=dev)
-    perm = torch.empty(r, dtype=torch.int64, device=dev)
-    inv = torch.empty(r, dtype=torch.int64, device=dev)
+    # zero-filled: a route whose expert id is out of range is dropped by the kernel (status 903), and its slots must still
+    # hold indices that the permute kernels can follow without leaving their tensors
+    triple = torch.zeros(3, r, dtype=torch.int64, device=dev)
+    sorted_e, perm, inv = triple[0], triple[1], triple[2]
     sizes = torch.empty(num_experts, dtype=torch.int32, device=dev)
     offsets = torch.empty(num_experts, dtype=torch.int32, device=dev)
     nbytes = _lib.query("b2g_route_plan_workspace_bytes", r, num_experts)
     ws = torch.empty((nbytes + 3) // 4, dtype=torch.int32, device=dev)
     with _DeviceCtx(top_k_index):
         _lib.call("b2g_route_plan", _p(top_k_index), int(top_k_index.dtype == torch.int64), t, k, num_experts, _p(sorted_e),
-                  _p(perm), _p(inv), _p(sizes), _p(offsets), _p(ws), nbytes, _stream(top_k_index))
+                  _p(perm), _p(inv), _p(sizes), _p(offsets), _p(ws), nbytes, _p(status_word(dev)), _stream(top_k_index))
     return sorted_e, perm, inv, sizes, offsets
 
 
@@ -391,11 +419,14 @@ def route_gather(hidden: torch.Tensor, perm: torch.Tensor, top_k: int) -> torch.
     return out
 
 
-def route_gather_bwd(grad_sel: torch.Tensor, inv: torch.Tensor, num_tokens: int, top_k: int) -> torch.Tensor:
+def route_gather_bwd(grad_sel: torch.Tensor, inv: torch.Tensor, num_tokens: int, top_k: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     _need(grad_sel, torch.bfloat16, "grad_selected")
     _need(inv, torch.int64, "inverse_permutation")
     h = grad_sel.shape[1]
-    out = torch.empty(num_tokens, h, dtype=torch.bfloat16, device=grad_sel.device)
+    if out is None:
+        out = torch.empty(num_tokens, h, dtype=torch.bfloat16, device=grad_sel.device)
+    else:
+        _need(out, torch.bfloat16, "out")
     with _DeviceCtx(grad_sel):
         _lib.call("b2g_route_gather_bwd", _p(grad_sel), _p(inv), _p(out), num_tokens, int(top_k), h, _stream(grad_sel))
     return out
@@ -407,13 +438,16 @@ def _wdtype(w: torch.Tensor) -> int:
     return int(w.dtype == torch.float32)
 
 
-def route_combine(expert_out: torch.Tensor, weights: torch.Tensor, inv: torch.Tensor) -> torch.Tensor:
+def route_combine(expert_out: torch.Tensor, weights: torch.Tensor, inv: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     _need(expert_out, torch.bfloat16, "expert_out")
     _need(weights, weights.dtype, "routing_weights")
     _need(inv, torch.int64, "inverse_permutation")
     t, k = weights.shape
     h = expert_out.shape[1]
-    out = torch.empty(t, h, dtype=torch.bfloat16, device=expert_out.device)
+    if out is None:
+        out = torch.empty(t, h, dtype=torch.bfloat16, device=expert_out.device)
+    else:
+        _need(out, torch.bfloat16, "out")
     with _DeviceCtx(expert_out):
         _lib.call("b2g_route_combine", _p(expert_out), _p(weights), _wdtype(weights), _p(inv), _p(out), t, k, h, _stream(expert_out))
     return out
@@ -434,20 +468,23 @@ def route_combine_bwd(expert_out: torch.Tensor, weights: torch.Tensor, perm: tor
     return d_out, d_w
 
 
-def swiglu_fwd(gate: torch.Tensor, up: torch.Tensor, limit: float = 0.0) -> torch.Tensor:
+def swiglu_fwd(gate: torch.Tensor, up: torch.Tensor, limit: float = 0.0, live_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``silu(gate) * up`` (clamped when ``limit > 0``).  ``live_rows``: one-element int32 device tensor, the number of
+    leading rows that hold data (the rest is left untouched)."""
     _need(gate, torch.bfloat16, "gate")
     _need(up, torch.bfloat16, "up")
     z = torch.empty_like(gate)
     with _DeviceCtx(gate):
-        _lib.call("b2g_swiglu_fwd", _p(gate), _p(up), _p(z), gate.numel(), float(limit), _stream(gate))
+        _lib.call("b2g_swiglu_fwd", _p(gate), _p(up), _p(z), gate.numel(), float(limit), _p(live_rows), gate.shape[-1], _stream(gate))
     return z
 
 
-def swiglu_bwd(gate: torch.Tensor, up: torch.Tensor, dz: torch.Tensor, limit: float = 0.0):
+def swiglu_bwd(gate: torch.Tensor, up: torch.Tensor, dz: torch.Tensor, limit: float = 0.0, live_rows: Optional[torch.Tensor] = None):
     _need(dz, torch.bfloat16, "dz")
     dg, du = torch.empty_like(gate), torch.empty_like(up)
     with _DeviceCtx(gate):
-        _lib.call("b2g_swiglu_bwd", _p(gate), _p(up), _p(dz), _p(dg), _p(du), gate.numel(), float(limit), _stream(gate))
+        _lib.call("b2g_swiglu_bwd", _p(gate), _p(up), _p(dz), _p(dg), _p(du), gate.numel(), float(limit), _p(live_rows), gate.shape[-1],
+                  _stream(gate))
     return dg, du
 
 
@@ -464,7 +501,8 @@ def grouped_schedule(expert_indices: torch.Tensor, offsets: torch.Tensor, total_
     nbytes = _lib.query("b2g_grouped_tiles_bytes", total_rows, g)
     tiles = torch.empty(nbytes // 4, dtype=torch.int32, device=offsets.device)
     with _DeviceCtx(offsets):
-        _lib.call("b2g_grouped_schedule", _p(expert_indices), _p(offsets), g, total_rows, _p(tiles), _stream(offsets))
+        _lib.call("b2g_grouped_schedule", _p(expert_indices), _p(offsets), g, total_rows, _p(tiles), _p(status_word(offsets.device)),
+                  _stream(offsets))
     return tiles
 
 

@@ -10,12 +10,22 @@
 // Slots come from the all-gathered count matrix, so no split size ever visits the host.  Plain 16-byte peer
 // stores only: no multicast, no waits inside the kernels (ranks synchronise between the two phases on the
 // stream, outside these kernels).
+//
+// The two copy kernels are built to run BESIDE the quantized GEMM on the same SMs: 128 threads of at most 48
+// registers and no shared memory fit next to the GEMM's 736-thread CTA (which leaves about 6.6 K registers
+// and 25 KB of shared memory per SM), so an exchange of one token chunk on its own stream proceeds while the
+// expert products of another chunk compute.
+//
+// A receive buffer that is too small is CONTAINED, not only reported: the plan kernel clamps every segment
+// of the rows this rank receives to the buffer's capacity (and sets status 901), so that the grouped
+// products that consume the plan never index past the buffer; the scatter kernel drops the rows that
+// would land beyond it.
 #include "b2g_common.cuh"
 
 namespace b2g {
 namespace ep {
 
-__global__ void __launch_bounds__(256) scatter_rows_kernel(const uint4* __restrict__ src, const int64_t* __restrict__ perm, int top_k,
+__global__ void __launch_bounds__(128, 10) scatter_rows_kernel(const uint4* __restrict__ src, const int64_t* __restrict__ perm, int top_k,
                                                            const int64_t* __restrict__ sorted_expert, const int32_t* __restrict__ my_start,
                                                            const int32_t* __restrict__ dest_base, const unsigned long long* __restrict__ peers,
                                                            int experts_per_rank, int64_t R, int vec_per_row, int64_t capacity, int* status,
@@ -55,7 +65,7 @@ __global__ void __launch_bounds__(256) scatter_rows_kernel(const uint4* __restri
   }
 }
 
-__global__ void __launch_bounds__(256) return_rows_kernel(const uint4* __restrict__ rows, const int32_t* __restrict__ blk_start,
+__global__ void __launch_bounds__(128, 10) return_rows_kernel(const uint4* __restrict__ rows, const int32_t* __restrict__ blk_start,
                                                           const int32_t* __restrict__ src_pos, const unsigned long long* __restrict__ peers,
                                                           int world, int num_blocks, int vec_per_row, int64_t capacity) {
   const int lane = threadIdx.x & 31;
@@ -99,16 +109,17 @@ __global__ void __launch_bounds__(256) return_rows_kernel(const uint4* __restric
 //   local_sizes / local_offsets: rows per local expert and their cumulative ends
 constexpr int kPlanMaxExperts = 2048, kPlanMaxRanks = 64;
 
-__global__ void __launch_bounds__(256) peer_plan_kernel(const int32_t* __restrict__ counts, int G, int E, int rank, int32_t* __restrict__ my_start,
-                                                        int32_t* __restrict__ dest_base, int32_t* __restrict__ blk_start,
-                                                        int32_t* __restrict__ src_pos, int32_t* __restrict__ local_sizes,
-                                                        int32_t* __restrict__ local_offsets) {
+__global__ void __launch_bounds__(256) peer_plan_kernel(const int32_t* __restrict__ counts, int64_t count_stride, int G, int E, int rank,
+                                                        int32_t* __restrict__ my_start, int32_t* __restrict__ dest_base,
+                                                        int32_t* __restrict__ blk_start, int32_t* __restrict__ src_pos,
+                                                        int32_t* __restrict__ local_sizes, int32_t* __restrict__ local_offsets,
+                                                        int64_t capacity, int* __restrict__ status) {
   __shared__ int32_t total[kPlanMaxExperts];
   const int per = E / G, lo = rank * per;
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     int32_t sum = 0, before = 0;
     for (int g = 0; g < G; ++g) {
-      const int32_t c = counts[g * E + e];
+      const int32_t c = counts[g * count_stride + e];
       sum += c;
       if (g < rank) before += c;
     }
@@ -122,8 +133,15 @@ __global__ void __launch_bounds__(256) peer_plan_kernel(const int32_t* __restric
     for (int j = 0; j < per; ++j) {
       const int e = o * per + j;
       dest_base[e] += run;
+      if (o == rank) {
+        // what the grouped products may touch: segments clamped to the receive buffer
+        const int64_t begin = run < capacity ? run : capacity;
+        const int64_t end = (int64_t)run + total[e] < capacity ? (int64_t)run + total[e] : capacity;
+        local_sizes[j] = static_cast<int32_t>(end - begin);
+        local_offsets[j] = static_cast<int32_t>(end);
+        if ((int64_t)run + total[e] > capacity && status) atomicCAS(status, 0, 901);
+      }
       run += total[e];
-      if (o == rank) { local_sizes[j] = total[e]; local_offsets[j] = run; }
     }
   }
   // one thread per source rank: where each of this rank's local experts starts in that source's sorted order
@@ -132,18 +150,18 @@ __global__ void __launch_bounds__(256) peer_plan_kernel(const int32_t* __restric
     for (int e = 0; e < E; ++e) {
       if (g == rank) my_start[e] = run;
       if (e >= lo && e < lo + per) src_pos[(e - lo) * G + g] = run;
-      run += counts[g * E + e];
+      run += counts[g * count_stride + e];
     }
   }
-  // blocks of the owner side in (local expert, source rank) order
+  // blocks of the owner side in (local expert, source rank) order, clamped like the segments above
   if (threadIdx.x == 0) {
-    int32_t run = 0;
+    int64_t run = 0;
     for (int j = 0; j < per; ++j)
       for (int g = 0; g < G; ++g) {
-        blk_start[j * G + g] = run;
-        run += counts[g * E + lo + j];
+        blk_start[j * G + g] = static_cast<int32_t>(run < capacity ? run : capacity);
+        run += counts[g * count_stride + lo + j];
       }
-    blk_start[per * G] = run;
+    blk_start[per * G] = static_cast<int32_t>(run < capacity ? run : capacity);
   }
 }
 
@@ -161,8 +179,8 @@ extern "C" int b2g_ep_scatter_rows(const void* src, const int64_t* perm, int top
   B2G_REQUIRE(first_expert >= 0, "ep_scatter_rows: first_expert %d is negative", first_expert);
   if (R == 0) return 0;
   B2G_REQUIRE(src && sorted_expert && my_start && dest_base && peer_ptrs && aligned16(src), "ep_scatter_rows: null or misaligned pointer");
-  const int64_t want = (R + 7) / 8, cap = (int64_t)sm_count() * 8;
-  ep::scatter_rows_kernel<<<(int)(want < cap ? want : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  const int64_t want = (R + 3) / 4, cap = (int64_t)sm_count() * 8;
+  ep::scatter_rows_kernel<<<(int)(want < cap ? want : cap), 128, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(src), perm, top_k, sorted_expert, my_start, dest_base, reinterpret_cast<const unsigned long long*>(peer_ptrs),
       experts_per_rank, R, H / 8, capacity_rows, status, first_expert);
   B2G_CUDA_OK(cudaGetLastError());
@@ -175,23 +193,25 @@ extern "C" int b2g_ep_return_rows(const void* rows, const int32_t* blk_start, co
   B2G_REQUIRE(world >= 1 && num_blocks >= 1 && num_blocks % world == 0, "ep_return_rows: %d blocks do not split over %d ranks", num_blocks, world);
   if (capacity_rows == 0) return 0;
   B2G_REQUIRE(rows && blk_start && src_pos && peer_ptrs && aligned16(rows), "ep_return_rows: null or misaligned pointer");
-  const int64_t want = (capacity_rows + 7) / 8, cap = (int64_t)sm_count() * 8;
-  ep::return_rows_kernel<<<(int)(want < cap ? want : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  const int64_t want = (capacity_rows + 3) / 4, cap = (int64_t)sm_count() * 8;
+  ep::return_rows_kernel<<<(int)(want < cap ? want : cap), 128, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(rows), blk_start, src_pos, reinterpret_cast<const unsigned long long*>(peer_ptrs), world, num_blocks, H / 8,
       capacity_rows);
   B2G_CUDA_OK(cudaGetLastError());
   return 0;
 }
 
-extern "C" int b2g_ep_peer_plan(const int32_t* counts, int world, int num_experts, int rank, int32_t* my_start, int32_t* dest_base,
-                                int32_t* blk_start, int32_t* src_pos, int32_t* local_sizes, int32_t* local_offsets, void* stream) {
+extern "C" int b2g_ep_peer_plan(const int32_t* counts, int64_t count_stride, int world, int num_experts, int rank, int32_t* my_start,
+                                int32_t* dest_base, int32_t* blk_start, int32_t* src_pos, int32_t* local_sizes, int32_t* local_offsets,
+                                int64_t capacity_rows, int* status, void* stream) {
   B2G_REQUIRE(world >= 1 && world <= ep::kPlanMaxRanks && num_experts >= world && num_experts <= ep::kPlanMaxExperts &&
                   num_experts % world == 0, "ep_peer_plan: %d experts over %d ranks is outside what one CTA plans (<= %d experts, <= %d ranks)",
               num_experts, world, ep::kPlanMaxExperts, ep::kPlanMaxRanks);
   B2G_REQUIRE(rank >= 0 && rank < world, "ep_peer_plan: rank %d of %d", rank, world);
   B2G_REQUIRE(counts && my_start && dest_base && blk_start && src_pos && local_sizes && local_offsets, "ep_peer_plan: null pointer");
-  ep::peer_plan_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(counts, world, num_experts, rank, my_start, dest_base, blk_start,
-                                                                         src_pos, local_sizes, local_offsets);
+  B2G_REQUIRE(count_stride >= num_experts && capacity_rows >= 0 && capacity_rows < (1ll << 31), "ep_peer_plan: bad count stride or capacity");
+  ep::peer_plan_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(counts, count_stride, world, num_experts, rank, my_start, dest_base,
+                                                                         blk_start, src_pos, local_sizes, local_offsets, capacity_rows, status);
   B2G_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -223,8 +223,12 @@ __global__ void __launch_bounds__(128) lora_wgrad_kernel(const __nv_bfloat16* __
     rows = m_total - row0 < rows_per_split ? m_total - row0 : rows_per_split;
     if (rows < 0) rows = 0;
   } else {
+    // offsets that overrun the operand (a receive buffer that was too small) are clamped to it
     row0 = segi > 0 ? offsets[segi - 1] : 0;
-    rows = offsets[segi] - row0;
+    int64_t end = offsets[segi];
+    if (row0 > m_total) row0 = m_total;
+    if (end > m_total) end = m_total;
+    rows = end > row0 ? end - row0 : 0;
   }
   float acc[4][4];
 #pragma unroll
@@ -380,7 +384,9 @@ static int lora_down_launch(const void* x, const void* x1, const void* w, int w_
   if (M == 0) return 0;
   B2G_REQUIRE(x && w && (out_plain || out_scaled), "%s: null pointer", what);
   B2G_REQUIRE(aligned16(x) && (!x1 || aligned16(x1)), "%s: activations must be 16-byte aligned", what);
-  B2G_REQUIRE(w_is_cr || (reinterpret_cast<uintptr_t>(w) & 3) == 0, "%s: weight must be 4-byte aligned", what);
+  // [r, C] rows are streamed with 16-byte cp.async (C % 8 == 0 keeps every row on a 16-byte boundary once the base is);
+  // [C, r] rows are read with scalar loads, with a checked vector fast path
+  B2G_REQUIRE(w_is_cr || aligned16(w), "%s: a weight given as [r, C] must be 16-byte aligned", what);
   const size_t smem = (size_t)lora::kDownStages * lora::kDownStageBytes;
   int grid = sm_count() * 2;       // two resident CTAs per SM
   int dense_rows = 0;

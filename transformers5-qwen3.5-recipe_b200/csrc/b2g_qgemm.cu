@@ -1058,8 +1058,12 @@ int check_common(const Launch& L, const char* what) {
 }
 
 // ---- grouped tile table ------------------------------------------------------------------------
+// Offsets are clamped to [0, total_rows] and kept monotone, and no more entries are written than the table holds, so that a
+// caller whose offsets overrun the activation matrix (an expert-parallel receive buffer that was too small) gets tiles that
+// stay inside it; status 904 reports the overrun.
 __global__ void __launch_bounds__(256) schedule_kernel(const int64_t* __restrict__ expert_indices, const int32_t* __restrict__ offsets,
-                                                       int G, int rows_per_tile, int4* __restrict__ tiles) {
+                                                       int G, int rows_per_tile, int total_rows, int max_tiles, int4* __restrict__ tiles,
+                                                       int* __restrict__ status) {
   __shared__ int scan[256];
   __shared__ int carry;
   if (threadIdx.x == 0) carry = 0;
@@ -1069,7 +1073,14 @@ __global__ void __launch_bounds__(256) schedule_kernel(const int64_t* __restrict
     int begin = 0, rows = 0;
     if (g < G) {
       begin = g > 0 ? offsets[g - 1] : 0;
-      rows = offsets[g] - begin;
+      int end = offsets[g];
+      if (end > total_rows || begin > total_rows) {
+        if (status) atomicCAS(status, 0, 904);
+        end = end > total_rows ? total_rows : end;
+        begin = begin > total_rows ? total_rows : begin;
+      }
+      if (begin < 0) begin = 0;
+      rows = end - begin;
       if (rows < 0) rows = 0;
     }
     const int nt = (rows + rows_per_tile - 1) / rows_per_tile;
@@ -1084,7 +1095,7 @@ __global__ void __launch_bounds__(256) schedule_kernel(const int64_t* __restrict
     const int first = carry + scan[threadIdx.x] - nt;
     if (g < G) {
       const int e = static_cast<int>(expert_indices[g]);
-      for (int i = 0; i < nt; ++i) {
+      for (int i = 0; i < nt && first + i < max_tiles; ++i) {
         const int r0 = begin + i * rows_per_tile;
         const int left = rows - i * rows_per_tile;
         tiles[1 + first + i] = make_int4(e, r0, left < rows_per_tile ? left : rows_per_tile, g);
@@ -1094,7 +1105,7 @@ __global__ void __launch_bounds__(256) schedule_kernel(const int64_t* __restrict
     if (threadIdx.x == 255) carry += scan[255];
     __syncthreads();
   }
-  if (threadIdx.x == 0) tiles[0] = make_int4(carry, rows_per_tile, G, 0);
+  if (threadIdx.x == 0) tiles[0] = make_int4(carry < max_tiles ? carry : max_tiles, rows_per_tile, G, 0);
 }
 
 }  // namespace qg
@@ -1127,18 +1138,17 @@ extern "C" int b2g_qlinear_dgrad(int qtype, const void* dy, const void* payload,
   return qg::launch_mode<qg::kDgrad>(L);
 }
 
-extern "C" int64_t b2g_grouped_tiles_bytes(int64_t R, int G) {
-  const int64_t rows_per_tile = qg::kTileRows;
-  return (1 + R / rows_per_tile + G + 1) * (int64_t)sizeof(int4);
-}
+static int64_t grouped_max_tiles(int64_t R, int G) { return R / qg::kTileRows + G + 1; }   // every expert may end in one partial tile
+
+extern "C" int64_t b2g_grouped_tiles_bytes(int64_t R, int G) { return (1 + grouped_max_tiles(R, G)) * (int64_t)sizeof(int4); }
 
 extern "C" int b2g_grouped_schedule(const int64_t* expert_indices, const int32_t* offsets, int G, int64_t R, int32_t* tiles,
-                                    void* stream) {
-  B2G_REQUIRE(G >= 0 && R >= 0 && tiles, "bad arguments");
+                                    int* status, void* stream) {
+  B2G_REQUIRE(G >= 0 && R >= 0 && R < (1ll << 31) && tiles, "bad arguments");
   B2G_REQUIRE(aligned16(tiles), "tile table must be 16-byte aligned");
   B2G_REQUIRE(G == 0 || (expert_indices && offsets), "null pointer");
-  qg::schedule_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(expert_indices, offsets, G, qg::kTileRows,
-                                                                       reinterpret_cast<int4*>(tiles));
+  qg::schedule_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(expert_indices, offsets, G, qg::kTileRows, (int)R,
+                                                                       (int)grouped_max_tiles(R, G), reinterpret_cast<int4*>(tiles), status);
   B2G_CUDA_OK(cudaGetLastError());
   return 0;
 }

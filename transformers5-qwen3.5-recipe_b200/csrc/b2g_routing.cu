@@ -73,7 +73,7 @@ __device__ __forceinline__ int load_id(const void* p, int64_t i) {
 
 template <bool kIdx64>
 __global__ void __launch_bounds__(256) plan_hist_kernel(const void* __restrict__ ids, int64_t R, int E, int32_t* __restrict__ ws,
-                                                        int* __restrict__ bad) {
+                                                        int* __restrict__ status) {
   extern __shared__ int32_t sh[];  // [warps][E]
   const int warp_in_block = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int32_t* cnt = sh + warp_in_block * E;
@@ -85,7 +85,10 @@ __global__ void __launch_bounds__(256) plan_hist_kernel(const void* __restrict__
     const int64_t end = begin + kChunk < R ? begin + kChunk : R;
     for (int64_t i = begin + lane; i < end; i += 32) {
       const int e = load_id<kIdx64>(ids, i);
-      if (e < 0 || e >= E) { *bad = 1; continue; }
+      if (e < 0 || e >= E) {              // not counted, not placed: reported through the status word
+        if (status) atomicCAS(status, 0, 903);
+        continue;
+      }
       atomicAdd(&cnt[e], 1);  // shared-memory counter private to this warp: order does not matter
     }
     __syncwarp();
@@ -312,8 +315,18 @@ __global__ void __launch_bounds__(256) combine_bwd_kernel(const uint4* __restric
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
 
+// `live_rows` (nullable): device count of the rows that hold data, of `pairs_per_row` bf16 pairs each; the rest of the
+// tensors (the unused tail of an expert-parallel receive buffer) is neither read nor written.
+__device__ __forceinline__ int64_t live_pairs(int64_t npairs, const int32_t* live_rows, int64_t pairs_per_row) {
+  if (!live_rows) return npairs;
+  const int64_t n = static_cast<int64_t>(*live_rows) * pairs_per_row;
+  return n < npairs ? (n > 0 ? n : 0) : npairs;
+}
+
 __global__ void __launch_bounds__(256) swiglu_fwd_kernel(const uint32_t* __restrict__ gate, const uint32_t* __restrict__ up,
-                                                         uint32_t* __restrict__ z, int64_t npairs, float limit) {
+                                                         uint32_t* __restrict__ z, int64_t npairs, float limit,
+                                                         const int32_t* __restrict__ live_rows, int64_t pairs_per_row) {
+  npairs = live_pairs(npairs, live_rows, pairs_per_row);
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < npairs; i += (int64_t)gridDim.x * blockDim.x) {
     const uint32_t g2 = gate[i], u2 = up[i];
     float g[2] = {dev::bf16_lo(g2), dev::bf16_hi(g2)}, u[2] = {dev::bf16_lo(u2), dev::bf16_hi(u2)}, o[2];
@@ -329,7 +342,9 @@ __global__ void __launch_bounds__(256) swiglu_fwd_kernel(const uint32_t* __restr
 
 __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const uint32_t* __restrict__ gate, const uint32_t* __restrict__ up,
                                                          const uint32_t* __restrict__ dz, uint32_t* __restrict__ dgate,
-                                                         uint32_t* __restrict__ dup, int64_t npairs, float limit) {
+                                                         uint32_t* __restrict__ dup, int64_t npairs, float limit,
+                                                         const int32_t* __restrict__ live_rows, int64_t pairs_per_row) {
+  npairs = live_pairs(npairs, live_rows, pairs_per_row);
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < npairs; i += (int64_t)gridDim.x * blockDim.x) {
     const uint32_t g2 = gate[i], u2 = up[i], d2 = dz[i];
     const float g[2] = {dev::bf16_lo(g2), dev::bf16_hi(g2)}, u[2] = {dev::bf16_lo(u2), dev::bf16_hi(u2)};
@@ -395,7 +410,7 @@ extern "C" int64_t b2g_route_plan_workspace_bytes(int64_t R, int E) {
 
 extern "C" int b2g_route_plan(const void* topk_idx, int idx_dtype, int64_t T, int top_k, int E, int64_t* sorted_expert,
                               int64_t* perm, int64_t* inv_perm, int32_t* group_sizes, int32_t* offsets, void* workspace,
-                              int64_t workspace_bytes, void* stream) {
+                              int64_t workspace_bytes, int* status, void* stream) {
   B2G_REQUIRE(idx_dtype == 0 || idx_dtype == 1, "idx_dtype must be 0 (int32) or 1 (int64)");
   B2G_REQUIRE(E >= 1 && E <= 1024, "E=%d outside 1..1024", E);
   B2G_REQUIRE(T >= 0 && top_k >= 1, "bad T/top_k");
@@ -407,15 +422,13 @@ extern "C" int b2g_route_plan(const void* topk_idx, int idx_dtype, int64_t T, in
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int64_t nchunks = (R + kChunk - 1) / kChunk;
   int32_t* ws = static_cast<int32_t*>(workspace);
-  int* bad = ws + nchunks * E;  // one flag after the table; cleared here, set on an out-of-range id
-  B2G_CUDA_OK(cudaMemsetAsync(bad, 0, sizeof(int), s));
   const int warps = 8;
   const size_t smem = (size_t)warps * E * sizeof(int32_t);
   const int blocks = static_cast<int>((nchunks + warps - 1) / warps);
   if (R > 0) {
     B2G_REQUIRE(topk_idx && sorted_expert && perm && inv_perm, "null pointer");
-    if (idx_dtype) plan_hist_kernel<true><<<blocks, warps * 32, smem, s>>>(topk_idx, R, E, ws, bad);
-    else plan_hist_kernel<false><<<blocks, warps * 32, smem, s>>>(topk_idx, R, E, ws, bad);
+    if (idx_dtype) plan_hist_kernel<true><<<blocks, warps * 32, smem, s>>>(topk_idx, R, E, ws, status);
+    else plan_hist_kernel<false><<<blocks, warps * 32, smem, s>>>(topk_idx, R, E, ws, status);
   }
   plan_scan_kernel<<<(E + 7) / 8, 256, 0, s>>>(ws, nchunks, E, group_sizes);
   plan_offsets_kernel<<<1, 1024, 0, s>>>(group_sizes, E, offsets);
@@ -489,28 +502,31 @@ extern "C" int b2g_route_combine_bwd(const void* expert_out, const void* weights
   return 0;
 }
 
-extern "C" int b2g_swiglu_fwd(const void* gate, const void* up, void* z, int64_t n, float limit, void* stream) {
+extern "C" int b2g_swiglu_fwd(const void* gate, const void* up, void* z, int64_t n, float limit, const int32_t* live_rows, int64_t cols,
+                              void* stream) {
   B2G_REQUIRE(n >= 0 && n % 2 == 0, "element count must be even");
+  B2G_REQUIRE(live_rows == nullptr || (cols > 0 && cols % 2 == 0 && n % cols == 0), "a live row count needs an even row width that divides n");
   if (n == 0) return 0;
   B2G_REQUIRE(gate && up && z, "null pointer");
   const int64_t pairs = n / 2;
   const int64_t want = (pairs + 255) / 256, cap = (int64_t)sm_count() * 16;
   swiglu_fwd_kernel<<<(int)(want < cap ? want : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint32_t*>(gate), static_cast<const uint32_t*>(up), static_cast<uint32_t*>(z), pairs, limit);
+      static_cast<const uint32_t*>(gate), static_cast<const uint32_t*>(up), static_cast<uint32_t*>(z), pairs, limit, live_rows, cols / 2);
   B2G_CUDA_OK(cudaGetLastError());
   return 0;
 }
 
 extern "C" int b2g_swiglu_bwd(const void* gate, const void* up, const void* dz, void* dgate, void* dup, int64_t n, float limit,
-                              void* stream) {
+                              const int32_t* live_rows, int64_t cols, void* stream) {
   B2G_REQUIRE(n >= 0 && n % 2 == 0, "element count must be even");
+  B2G_REQUIRE(live_rows == nullptr || (cols > 0 && cols % 2 == 0 && n % cols == 0), "a live row count needs an even row width that divides n");
   if (n == 0) return 0;
   B2G_REQUIRE(gate && up && dz && dgate && dup, "null pointer");
   const int64_t pairs = n / 2;
   const int64_t want = (pairs + 255) / 256, cap = (int64_t)sm_count() * 16;
   swiglu_bwd_kernel<<<(int)(want < cap ? want : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint32_t*>(gate), static_cast<const uint32_t*>(up), static_cast<const uint32_t*>(dz),
-      static_cast<uint32_t*>(dgate), static_cast<uint32_t*>(dup), pairs, limit);
+      static_cast<uint32_t*>(dgate), static_cast<uint32_t*>(dup), pairs, limit, live_rows, cols / 2);
   B2G_CUDA_OK(cudaGetLastError());
   return 0;
 }
