@@ -37,6 +37,9 @@ SCALING = ALPHA / RANK
 Q4_K = 12
 SEED = 19260817 + 1
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# dram__bytes_read.sum + dram__bytes_write.sum of one qgemm_kernel<Q4_K, forward> launch at N=4096, K=2048, keyed by M
+# (ncu captures summarised under profiles/)
+DRAM_TRAFFIC_BYTES = {16384: 161.3e6}
 
 
 def flops_per_step(m: int) -> float:
@@ -193,120 +196,331 @@ def run_cpu(steps: int, warmup: int, budget_s: float, m_full: int) -> dict:
 
 
 # ---------------------------------------------------------------------------------------------
-# MoE workload: the 16384-token grouped configuration on one GPU and its 65536-token variant (skewed router,
-# experts sharded over the ranks, NCCL all-to-all dispatch / combine) when launched on several.
+# MoE workloads: the grouped Q4_K expert layer (256 experts, top-8, hidden 2048, intermediate 512, r = 16)
+#   "qwen16k"  16384 tokens on one GPU, unbiased router                       (configuration 2 of the benchmark specification)
+#   "skew64k"  65536 tokens in total, router logits N(0,1) + a per-expert bias N(0,0.5): on one GPU, or expert-parallel
+#              over N ranks with the experts sharded 256/N per GPU              (configuration 4)
+#   "deepseek" 8192 tokens, 256 IQ2_XXS experts top-6 (hidden 4096, intermediate 2048, r = 8, clamped SwiGLU) plus the Q8_0
+#              shared expert, one GPU                                            (configuration 3)
 # ---------------------------------------------------------------------------------------------
-def run_moe(args) -> int:
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    if args.impl == "reference":
-        if rank == 0:
-            print(json.dumps({"impl": "reference", "unavailable": "the MoE workload has no bounded CPU sample in this harness; use the dense workload"}))
-        return 0
-    import torch.distributed as dist
+MOE = {"E": 256, "H": 2048, "I": 512, "K": 8, "R": 16, "Q": 12}
+DSK = {"E": 256, "H": 4096, "I": 2048, "K": 6, "R": 8, "Q": 16, "limit": 7.0}
 
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    os.environ.setdefault("MASTER_PORT", "29531")
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
-    from b2g import _lib, ep, ep_peer, gguf_quant, ops
 
-    E, H, I, TOPK, R_LORA = 256, 2048, 512, 8, 16
-    t_total = args.tokens if args.tokens != 32768 else (16384 if world == 1 else 65536)
-    skew = world > 1 or t_total == 65536
-    t_local = t_total // world
-    e_local = E // world
-    lo = rank * e_local
-    gen = torch.Generator(device=dev).manual_seed(SEED + 1 + rank)
+def moe_flops(tokens: int, g=MOE, shared: bool = False) -> float:
+    rows = tokens * g["K"]
+    f = 4.0 * rows * 3 * g["H"] * g["I"] + 6.0 * rows * g["R"] * ((g["H"] + 2 * g["I"]) + (g["I"] + g["H"]))
+    if shared:
+        f += 3 * (4.0 * tokens * g["H"] * g["I"] + 6.0 * tokens * g["R"] * (g["H"] + g["I"]))
+    return f
 
-    def packed(shape, seed):
-        out = []
+
+def _expert_payload(dev, qtype: int, shape, seed: int):
+    """One expert's packed weight, the same bytes whichever rank builds it: N(0, 0.02) through the Q4_K encoder, or seeded
+    random valid blocks of that spread for the types without an encoder."""
+    from b2g import gguf_quant
+
+    if qtype == 12:
         g = torch.Generator(device=dev).manual_seed(seed)
-        for s0 in range(0, shape[0], 32):
-            n = min(32, shape[0] - s0)
-            out.append(gguf_quant.quantize_q4_k(torch.randn(n, *shape[1:], generator=g, device=dev) * 0.02))
-        return torch.cat(out, 0).reshape(-1)
+        return gguf_quant.quantize_q4_k(torch.randn(*shape, generator=g, device=dev) * 0.02)
+    return gguf_quant.random_payload(qtype, shape, seed, device=dev)
 
-    gate_p, up_p, down_p = packed((e_local, I, H), 100 + rank), packed((e_local, I, H), 200 + rank), packed((e_local, H, I), 300 + rank)
-    lora = {"gate_up_a": (torch.randn(e_local, R_LORA, H, generator=gen, device=dev) / 16).bfloat16().requires_grad_(True),
-            "gate_up_b": (torch.randn(e_local, 2 * I, R_LORA, generator=gen, device=dev) * 0.01).bfloat16().requires_grad_(True),
-            "down_a": (torch.randn(e_local, R_LORA, I, generator=gen, device=dev) / 16).bfloat16().requires_grad_(True),
-            "down_b": (torch.randn(e_local, H, R_LORA, generator=gen, device=dev) * 0.01).bfloat16().requires_grad_(True)}
+
+def _expert_bank(dev, qtype: int, expert_ids, rows: int, cols: int, base_seed: int):
+    return torch.stack([_expert_payload(dev, qtype, (rows, cols), base_seed + int(e)) for e in expert_ids]).reshape(-1)
+
+
+def _moe_factors(dev, expert_ids, g, seed: int, requires_grad=True):
+    out = {"gate_up_a": [], "gate_up_b": [], "down_a": [], "down_b": []}
+    for e in expert_ids:
+        gen = torch.Generator(device=dev).manual_seed(seed + int(e))
+        out["gate_up_a"].append(torch.randn(g["R"], g["H"], generator=gen, device=dev) / 16)
+        out["gate_up_b"].append(torch.randn(2 * g["I"], g["R"], generator=gen, device=dev) * 0.01)
+        out["down_a"].append(torch.randn(g["R"], g["I"], generator=gen, device=dev) / 16)
+        out["down_b"].append(torch.randn(g["H"], g["R"], generator=gen, device=dev) * 0.01)
+    return {n: torch.stack(v).bfloat16().requires_grad_(requires_grad) for n, v in out.items()}
+
+
+def _time_steps(step, steps: int, barrier) -> float:
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    return e0.elapsed_time(e1) / steps
+
+
+def measure_moe(kind: str, args, dev, dist, rank: int, world: int, steps: int, warmup: int, cpu_baseline: bool = True) -> dict:
+    """One MoE workload in this process (all ranks call it together); returns the object rank 0 prints."""
+    from b2g import _lib, autograd as ag, ep_peer, ops, routing
+
+    g = DSK if kind == "deepseek" else MOE
+    E, H, I, TOPK, QT = g["E"], g["H"], g["I"], g["K"], g["Q"]
+    scaling = 2.0
+    limit = g.get("limit", 0.0)
+    t_total = {"qwen16k": 16384, "skew64k": 65536, "deepseek": 8192}[kind]
+    skew = kind == "skew64k"
+    t_local = t_total // world
+    gen = torch.Generator(device=dev).manual_seed(SEED + 1 + rank)
     hidden = torch.randn(t_local, H, generator=gen, device=dev).bfloat16()
     g_out = torch.randn(t_local, H, generator=gen, device=dev).bfloat16()
     logits = torch.randn(t_local, E, generator=gen, device=dev)
     if skew:
-        bias = torch.randn(E, generator=torch.Generator(device=dev).manual_seed(SEED + 4), device=dev) * 0.5   # same on every rank
-        logits = logits + bias
+        logits = logits + torch.randn(E, generator=torch.Generator(device=dev).manual_seed(SEED + 4), device=dev) * 0.5   # same bias on every rank
 
-    use_peer = world > 1 and args.ep == "peer"
-    xchg = ep_peer.PeerExchange(t_local * TOPK, H, E, device=dev) if use_peer else None
+    # expert load of this batch (what a static placement is fitted to) and the placement
+    idx0 = ops.router_topk(logits, TOPK, None, False)
+    load = torch.bincount(idx0.flatten(), minlength=E).double()
+    if world > 1:
+        dist.all_reduce(load)
+    contiguous = ep_peer.contiguous_placement(E)
+    placement = ep_peer.balanced_placement(load, world) if (world > 1 and args.placement == "balanced") else contiguous
+    loads = ep_peer.rank_loads(load, placement, world)
+    loads_contiguous = ep_peer.rank_loads(load, contiguous, world)
+    mine = ep_peer.experts_of_rank(placement, rank, world).tolist()
+    gate_p, up_p, down_p = (_expert_bank(dev, QT, mine, I, H, 1000), _expert_bank(dev, QT, mine, I, H, 2000), _expert_bank(dev, QT, mine, H, I, 3000))
+    lora = _moe_factors(dev, mine, g, 4000)
+    ids = torch.arange(E // world, device=dev, dtype=torch.int64)
+    shared = None
+    if kind == "deepseek":
+        from b2g.gguf_types import GGUFQuantizedTensor
+        from b2g.moe_block import SharedExpertLora
+        from b2g import gguf_quant
+
+        sg = torch.Generator(device=dev).manual_seed(SEED + 7)
+        sp = [gguf_quant.quantize_q8_0(torch.randn(*shape, generator=sg, device=dev) * 0.02) for shape in ((I, H), (I, H), (H, I))]
+        shared = SharedExpertLora(*(GGUFQuantizedTensor(p, quant_type=8, logical_shape=shape) for p, shape in zip(sp, ((I, H), (I, H), (H, I)))),
+                                  r=g["R"], lora_alpha=2 * g["R"], swiglu_limit=limit)
+        with torch.no_grad():
+            for name in ("gate", "up", "down"):
+                shared.lora_B[name].normal_(std=0.01, generator=sg)
+    xchg = None
+    if world > 1:
+        xchg = ep_peer.PeerExchange(t_local * TOPK, H, E, device=dev, chunks=args.chunks, placement=None if placement is contiguous else placement)
+
+    def layer(h, lg):
+        idx = ops.router_topk(lg, TOPK, None, False)
+        wts = torch.softmax(lg.gather(1, idx), dim=-1)
+        if xchg is not None:
+            return ep_peer.peer_moe_layer(xchg, h, idx, wts, gate_p, up_p, down_p, QT, I, lora, scaling)
+        plan = routing.build_plan(h, idx, wts, E)
+        out_e = ag.grouped_lora_experts(plan.selected_hidden_states, gate_p, up_p, down_p, QT, QT, I, ids, plan.group_offsets, plan.group_offsets,
+                                        lora["gate_up_a"], lora["gate_up_b"], lora["down_a"], lora["down_b"], scaling, limit)
+        out = routing.combine(out_e, plan)
+        return out if shared is None else out + shared(h)
+
+    def zero_grads():
+        for v in lora.values():
+            v.grad = None
+        if shared is not None:
+            shared.zero_grad(set_to_none=True)
 
     def step():
         h = hidden.detach().requires_grad_(True)
-        for v in lora.values():
-            v.grad = None
-        idx = ops.router_topk(logits, TOPK, None, False)
-        wts = torch.softmax(logits.gather(1, idx), dim=-1)
-        if use_peer:
-            out = ep_peer.peer_moe_layer(xchg, h, idx, wts, gate_p, up_p, down_p, Q4_K, I, lora, SCALING)
-        else:
-            out = ep.cuda_moe_layer(h, idx, wts, gate_p, up_p, down_p, Q4_K, I, E, lora, SCALING)
+        zero_grads()
+        out = layer(h, logits)
         out.backward(g_out)
         return out, h.grad
 
     def barrier():
-        dist.barrier()
+        if world > 1:
+            dist.barrier()
         torch.cuda.synchronize()
 
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    for _ in range(max(3, args.warmup)):
+    for _ in range(max(3, warmup)):
         step()
     barrier()
     ops.check_status()
     _lib.COUNT_LAUNCHES, _lib.LAUNCHES = True, 0
-    barrier()
-    sampler.begin()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    torch.cuda.profiler.start()                   # `ncu --profile-from-start off` then sees only the timed steps (all threads)
-    for _ in range(args.steps):
+    ms = _time_steps(step, steps, barrier)
+    launches = _lib.LAUNCHES // max(1, steps)
+    _lib.COUNT_LAUNCHES = False
+
+    # per-kernel device times of a few more steps (CUDA events around the entry points, on the launching stream)
+    kernel_ms: dict[str, float] = {}
+    _lib.TIMED = {"b2g_grouped_fwd", "b2g_grouped_dgrad", "b2g_route_gather", "b2g_route_gather_bwd", "b2g_route_combine", "b2g_route_combine_bwd",
+                  "b2g_ep_scatter_rows", "b2g_ep_return_rows"}
+    _lib.EVENTS.clear()
+    prof_steps = 3
+    if xchg is not None:
+        xchg.profile, xchg.trace = True, []
+    for _ in range(prof_steps):
         step()
     torch.cuda.synchronize()
-    torch.cuda.profiler.stop()
-    e1.record()
+    for name, key, a, b in _lib.EVENTS:
+        label = name[4:] + ("" if name not in ("b2g_grouped_fwd", "b2g_grouped_dgrad") else f"[N={key[0]},K={key[1]}]")
+        kernel_ms[label] = kernel_ms.get(label, 0.0) + a.elapsed_time(b) / prof_steps
+    _lib.TIMED = set()
+    _lib.EVENTS.clear()
+    phases = None
+    if xchg is not None:
+        phases = {k: v / prof_steps for k, v in xchg.phase_ms().items()}
+        xchg.profile, xchg.trace = False, []
     barrier()
-    sampler.end()
-    ms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
-    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    launches = _lib.LAUNCHES
-    _lib.COUNT_LAUNCHES = False
-    if world == 1:
-        sampler.extend(step, torch.cuda.synchronize)        # (a multi-rank step holds collectives: never run it on one rank alone)
-    clocks = sampler.stop() if rank == 0 else {}
+
+    # end to end: hidden states, router logits and the output cotangent from pinned host memory, output and token gradient back
+    pins = [t.cpu().pin_memory() for t in (hidden, logits, g_out)]
+    stage = [torch.empty_like(t) for t in (hidden, logits, g_out)]
+    back = [torch.empty(t_local, H, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+
+    def step_e2e():
+        for dst, src in zip(stage, pins):
+            dst.copy_(src, non_blocking=True)
+        h = stage[0].detach().requires_grad_(True)
+        zero_grads()
+        out = layer(h, stage[1])
+        out.backward(stage[2])
+        back[0].copy_(out.detach(), non_blocking=True)
+        back[1].copy_(h.grad, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(2):
+        step_e2e()
+    ms_e2e = _time_steps(step_e2e, max(3, min(steps, 10)), barrier)
+    if world > 1:
+        t = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = float(t[0]), float(t[1])
+        if phases:
+            names = sorted(phases)
+            pt = torch.tensor([phases[n] for n in names], device=dev, dtype=torch.float64)
+            dist.all_reduce(pt, op=dist.ReduceOp.MAX)
+            phases = {n: float(v) for n, v in zip(names, pt)}
     ops.check_status()
+    del xchg
+
+    peaks, peak_src = load_peaks()
+    peak_tf = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+    hbm = float(peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
+    flops = moe_flops(t_total, g, shared is not None)
+    rows_local = t_local * TOPK
+    out = {"workload": {"qwen16k": "grouped MoE Q4_K LoRA, 256 experts top-8, hidden 2048, intermediate 512, r=16, 16384 tokens (configuration 2 of the benchmark specification)",
+                        "skew64k": "the same experts, 65536 tokens in total, router logits N(0,1) + per-expert bias N(0,0.5) (configuration 4)",
+                        "deepseek": "grouped MoE IQ2_XXS LoRA, 256 experts top-6, hidden 4096, intermediate 2048, r=8, clamped SwiGLU, plus the Q8_0 shared expert, 8192 tokens (configuration 3)"}[kind],
+           "n_gpus": world, "tokens_total": t_total, "scaling": "strong" if skew else "weak", "steps": steps,
+           "parallelism": "1 GPU" if world == 1 else f"ep{world}: {E // world} experts per GPU, peer-store dispatch / combine over NVLink, {args.chunks} token chunks on an exchange stream, {args.placement} placement",
+           "ms_per_step": ms, "tokens_per_s": t_total / (ms * 1e-3), "step_tflops": flops / (ms * 1e-3) / 1e12,
+           "frac_of_tensor_peak_all_gpus": flops / (ms * 1e-3) / 1e12 / (peak_tf * world), "peak_source": peak_src,
+           "max_over_mean_rows": float(loads.max() / loads.mean()), "max_over_mean_rows_contiguous_blocks": float(loads_contiguous.max() / loads_contiguous.mean()),
+           "kernel_ms_per_step": {k: round(v, 4) for k, v in sorted(kernel_ms.items())}, "gpu_launches_per_step": launches,
+           "e2e": {"value": t_total / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                   "h2d_bytes_per_step": sum(p.numel() * p.element_size() for p in pins), "d2h_bytes_per_step": 2 * t_local * H * 2,
+                   "result": "layer output and token gradient"}}
+    if phases:
+        out["phases_ms_max_over_ranks"] = {k: round(v, 4) for k, v in phases.items()}
+    pair = kernel_ms.get(f"grouped_fwd[N={I},K={H}]")
+    if pair:
+        achieved = 2.0 * rows_local * (2 * I) * H / (pair * 1e-3) / 1e12       # this rank's rows x both payloads; ragged rows counted once
+        out["roofline"] = {"bound": "tensor", "kernel": f"qgemm_kernel grouped forward, gate|up pair, rows={rows_local} (this rank: mean over ranks), N=2x{I}, K={H}",
+                           "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf, "kernel_ms": pair, "traffic": None}
+    perm_ms = sum(kernel_ms.get(n, 0.0) for n in ("route_gather", "route_gather_bwd", "route_combine", "route_combine_bwd"))
+    if perm_ms and world == 1:
+        nbytes = 2.0 * H * (5 * rows_local + 4 * t_local)
+        out["permute_roofline"] = {"bound": "hbm", "kernels": "gather, combine and their backwards", "achieved": nbytes / (perm_ms * 1e-3) / 1e9, "peak": hbm,
+                                   "unit": "GB/s", "frac": nbytes / (perm_ms * 1e-3) / 1e9 / hbm, "kernels_ms": perm_ms, "traffic": None}
+    if cpu_baseline and rank == 0 and world == 1:
+        res = run_cpu_moe(kind, budget_s=12.0)
+        out["cpu_baseline"] = {"value": res["tokens_per_s"], "unit": "tokens/s", "cores": res["cores"], "kind": "port", "sample": res["sample"]}
+    return out
+
+
+def run_cpu_moe(kind: str, budget_s: float = 12.0, steps: int = 2) -> dict:
+    """The reference's CPU path for the MoE layer (per-expert loop of matmuls on dequantised weights, autograd backward:
+    ``oracle/moe_ref.moe_layer``) on a bounded sample: 1/8 (Qwen shape) or 1/32 (DeepSeek shape) of the experts and the same
+    fraction of the tokens, routed among those experts, so that the work per token and the rows per expert are those of the
+    full layer.  Weights are dequantised once outside the timed region."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    from b2g import gguf_quant
+    from oracle import dense_ref, gguf_oracle as go, moe_ref
+
+    g = DSK if kind == "deepseek" else MOE
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    frac = 32 if kind == "deepseek" else 8
+    e_s = g["E"] // frac
+    t_full = {"qwen16k": 16384, "skew64k": 65536, "deepseek": 8192}[kind]
+    t_s = t_full // frac
+    qt = g["Q"]
+    gen = torch.Generator().manual_seed(SEED + 11)
+    shapes = ((e_s, g["I"], g["H"]), (e_s, g["I"], g["H"]), (e_s, g["H"], g["I"]))
+    payloads = [gguf_quant.random_payload(qt, s, 50 + j).numpy() for j, s in enumerate(shapes)]
+    with ThreadPoolExecutor(max_workers=min(threads, e_s)) as ex:
+        weights = [torch.stack(list(ex.map(lambda one: dense_ref.dequant_bf16(one, qt), list(p)))) for p in payloads]
+    lora = {"gate_up_a": (torch.randn(e_s, g["R"], g["H"], generator=gen) / 16).bfloat16(), "gate_up_b": (torch.randn(e_s, 2 * g["I"], g["R"], generator=gen) * 0.01).bfloat16(),
+            "down_a": (torch.randn(e_s, g["R"], g["I"], generator=gen) / 16).bfloat16(), "down_b": (torch.randn(e_s, g["H"], g["R"], generator=gen) * 0.01).bfloat16()}
+    hidden = torch.randn(t_s, g["H"], generator=gen).bfloat16()
+    gout = torch.randn(t_s, g["H"], generator=gen).bfloat16()
+    logits = torch.randn(t_s, e_s, generator=gen)
+    idx = logits.topk(g["K"], 1).indices
+    wts = torch.softmax(logits.gather(1, idx), -1)
+
+    def step():
+        moe_ref.moe_layer(hidden, idx, wts, *weights, lora, 2.0, gout, torch.bfloat16, swiglu_limit=g.get("limit"))
+
+    t0 = time.perf_counter()
+    step()
+    first = time.perf_counter() - t0
+    steps = max(1, min(steps, int(budget_s / max(first, 1e-3))))
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - t0)
+    sec = statistics.median(times)
+    return {"tokens_per_s": t_s / sec, "ms_per_step": 1e3 * sec, "cores": threads,
+            "sample": f"{t_s} of {t_full} tokens routed top-{g['K']} among {e_s} of {g['E']} experts (same rows per expert and work per token as the full layer"
+                      f"{', routed experts only: the shared expert is left out' if kind == 'deepseek' else ''}), weights dequantised once outside the timed region, "
+                      f"{steps} timed steps after one warm-up, torch {torch.get_num_threads()} threads"}
+
+
+def run_moe(args) -> int:
+    """`--workload moe` (qwen16k on one GPU / skew64k expert-parallel on several), `--workload moe64k`, `--workload moe3`."""
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    kind = {"moe": "qwen16k" if world == 1 else "skew64k", "moe64k": "skew64k", "moe3": "deepseek"}[args.workload]
+    if args.impl == "reference":
+        if rank == 0:
+            res = run_cpu_moe(kind, budget_s=120.0, steps=max(1, args.steps))
+            print(json.dumps({"impl": "reference", "metric": "quantized MoE fwd+bwd tokens/s", "value": res["tokens_per_s"], "unit": "tokens/s",
+                              "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
+                              "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": {"workload": kind},
+                              "cpu_baseline": {"value": res["tokens_per_s"], "unit": "tokens/s", "cores": res["cores"], "kind": "port", "sample": res["sample"]},
+                              "e2e": {"value": res["tokens_per_s"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return 0
+    if kind == "deepseek" and world > 1:
+        if rank == 0:
+            print(json.dumps({"error": "the DeepSeek-shaped workload is measured on one GPU"}))
+        return 1
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+    sampler = ClockSampler(local_rank)
     if rank == 0:
-        peaks, peak_src = load_peaks()
-        ms_step = float(ms) / args.steps
-        rows = t_total * TOPK
-        flops = 4.0 * rows * 3 * H * I + 6.0 * rows * R_LORA * ((H + 2 * I) + (I + H))
-        peak_tf = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
-        print(json.dumps({
-            "metric": "quantized MoE (grouped Q4_K experts + LoRA) fwd+bwd tokens/s", "value": t_total / (ms_step * 1e-3), "unit": "tokens/s",
-            "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
-            "scaling": "strong" if world > 1 or t_total == 65536 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "grouped MoE Q4_K LoRA, 256 experts top-8, hidden 2048, intermediate 512 (configuration %d of the benchmark specification)" % (4 if skew else 2),
-                       "tokens_total": t_total, "experts_per_gpu": e_local, "skewed_router": skew,
-                       "parallelism": (f"ep{world} (experts sharded, " + ("peer-store dispatch/combine over NVLink)" if use_peer else "NCCL all-to-all dispatch/combine)"))
-                       if world > 1 else "1 GPU",
-                       "l2": "routed rows 2 GiB, larger than L2"},
-            "step_tflops": flops / (ms_step * 1e-3) / 1e12, "step_frac_of_tensor_peak_all_gpus": flops / (ms_step * 1e-3) / 1e12 / (peak_tf * world),
-            "peak_source": peak_src, "clocks": clocks, "gpu_launches": launches}))
-    dist.destroy_process_group()
+        sampler.start()
+        sampler.begin()
+    torch.cuda.profiler.start()                   # `ncu --profile-from-start off` then skips set-up
+    res = measure_moe(kind, args, dev, dist, rank, world, args.steps, args.warmup, cpu_baseline=not args.no_cpu_baseline)
+    torch.cuda.profiler.stop()
+    if rank == 0:
+        sampler.end()
+        clocks = sampler.stop()
+        print(json.dumps({"metric": "quantized MoE (grouped experts + LoRA) fwd+bwd tokens/s", "value": res["tokens_per_s"], "unit": "tokens/s",
+                          "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": res["ms_per_step"],
+                          "higher_is_better": True, "scaling": res["scaling"], "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                          "config": {"workload": res["workload"], "parallelism": res["parallelism"], "l2": "routed rows far larger than L2"},
+                          "clocks": clocks, "gpu_launches": res["gpu_launches_per_step"] * args.steps, **{k: v for k, v in res.items() if k not in ("workload", "parallelism")}}))
+    if dist is not None:
+        dist.destroy_process_group()
     return 0
 
 
@@ -401,12 +615,16 @@ def main() -> int:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--tokens", type=int, default=32768, help="M: tokens per step and per GPU")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--ep", default="peer", choices=["peer", "nccl"],
-                    help="MoE workload at N>1: row exchange by peer stores over NVLink (default) or by NCCL all-to-all")
-    ap.add_argument("--workload", default="dense", choices=["dense", "moe", "formats", "fixed", "lmhead"],
-                    help="dense: the Q4_K attention-shape linears (default, replicas at N>1); moe: grouped Q4_K experts, expert-parallel at N>1; formats / fixed / lmhead: single-GPU side measurements (see run_side)")
+    ap.add_argument("--workload", default="dense", choices=["dense", "moe", "moe64k", "moe3", "formats", "fixed", "lmhead"],
+                    help="dense: the Q4_K attention-shape linears plus a `moe` object (default; dense replicas and the expert-parallel MoE layer at N>1); "
+                         "moe: grouped Q4_K experts alone, 16384 tokens on one GPU / 65536 tokens expert-parallel at N>1; moe64k: the 65536-token "
+                         "layer at any N; moe3: the DeepSeek-shaped IQ2_XXS layer with its shared expert; formats / fixed / lmhead: single-GPU side measurements (see run_side)")
+    ap.add_argument("--chunks", type=int, default=2, help="expert-parallel MoE: token chunks whose exchanges overlap the expert products")
+    ap.add_argument("--placement", default="balanced", choices=["balanced", "contiguous"],
+                    help="expert-parallel MoE: experts placed over the ranks by measured load (default) or in contiguous blocks")
+    ap.add_argument("--no-moe", action="store_true", help="dense workload: leave the `moe` object out")
     args = ap.parse_args()
-    if args.workload == "moe":
+    if args.workload in ("moe", "moe64k", "moe3"):
         return run_moe(args)
     if args.workload in ("formats", "fixed", "lmhead"):
         return run_side(args)
@@ -428,6 +646,12 @@ def main() -> int:
                 "config": config,
                 "cpu_baseline": {"value": res["tokens_per_s"], "unit": "tokens/s", "cores": res["cores"], "kind": "port", "sample": res["sample"]},
                 "e2e": {"value": res["tokens_per_s"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        if not args.no_moe:
+            # the same CPU path for the MoE layers of the `moe` object of the other arm (the sample has the per-token work of
+            # both the 16384- and the 65536-token layer: same experts, same top-8)
+            cpu_moe = run_cpu_moe("qwen16k", budget_s=20.0, steps=3)
+            line["moe"] = {"cpu_tokens_per_s": cpu_moe["tokens_per_s"], "ms_per_step": cpu_moe["ms_per_step"], "cores": cpu_moe["cores"],
+                           "kind": "port", "sample": cpu_moe["sample"]}
         print(json.dumps(line))
         return 0
 
@@ -573,9 +797,10 @@ def main() -> int:
             roof = {"bound": "tensor", "kernel": "qgemm_kernel<Q4_K, forward> M=%d N=%d K=%d" % (m, n_big, K_DIM),
                     "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
                     "peak_source": f"{peak_src} burst cuBLAS bf16", "kernel_ms": kernel_ms,
-                    # dram__bytes_read + dram__bytes_write of this kernel: 161.3 MB per launch in an ncu capture at M=16384;
-                    # the traffic is activations in and out (the packed weight stays in L2), so it scales with M
-                    "traffic": 161.3e6 * m / 16384, "traffic_unit": "bytes/launch"}
+                    # dram__bytes_read + dram__bytes_write of one launch, from an ncu capture of this kernel at the size named
+                    # (profiles/); no figure is quoted for a size that was not captured
+                    "traffic": DRAM_TRAFFIC_BYTES.get(m), "traffic_unit": "bytes/launch",
+                    "algorithmic_bytes": 2.0 * m * (K_DIM + n_big) + n_big * K_DIM * 0.5625}
         line = {"metric": "quantized LoRA-linear fwd+bwd tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world,
                 "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
@@ -583,10 +808,26 @@ def main() -> int:
                 "step_frac_of_tensor_peak": flops / (ms_step * 1e-3) / 1e12 / peak_tf,
                 "roofline": roof, "clocks": clocks, "gpu_launches": launches,
                 "e2e": {"value": world * m / (ms_e2e / e2e_steps * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-                        "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / e2e_steps}}
+                        "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / e2e_steps,
+                        "result": "adapter gradients dA, dB of the three layers (what the optimizer step reads); Y and dX stay on the device "
+                                  "for the neighbouring layers"}}
         if world == 1 and not args.no_cpu_baseline:
-            res = run_cpu(3, 1, budget_s=24.0, m_full=m)
+            res = run_cpu(5, 2, budget_s=24.0, m_full=m)
             line["cpu_baseline"] = {"value": res["tokens_per_s"], "unit": "tokens/s", "cores": res["cores"], "kind": "port", "sample": res["sample"]}
+    # ---- the MoE layer, in the same process: the path that shards over the GPUs ----
+    moe = None
+    if not args.no_moe:
+        del x_dev, dys_dev, x_stage, dys_stage, x_pin, dys_pin
+        torch.cuda.empty_cache()
+        moe_steps = max(3, min(args.steps, 10))
+        if world == 1:
+            moe = {"one_gpu_16k_tokens": measure_moe("qwen16k", args, dev, dist, rank, world, moe_steps, args.warmup, cpu_baseline=not args.no_cpu_baseline),
+                   "one_gpu_64k_tokens_skewed": measure_moe("skew64k", args, dev, dist, rank, world, moe_steps, args.warmup, cpu_baseline=False)}
+        else:
+            moe = {"expert_parallel_64k_tokens_skewed": measure_moe("skew64k", args, dev, dist, rank, world, moe_steps, args.warmup, cpu_baseline=False)}
+    if rank == 0:
+        if moe is not None:
+            line["moe"] = moe
         print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
