@@ -7,8 +7,10 @@ Every rank holds its own tokens and its own experts.  The layer is evaluated thr
   4. peer stores again with the token range in two chunks (exchange stream beside the compute stream) and the experts
      placed over the ranks by load instead of in contiguous blocks.
 1 and 2 run the same kernels on the same rows in the same order and must agree bit for bit.  Against 3 the outputs
-and token gradients of 1 and 4 are compared exactly (a row's result does not depend on which rows share its tile) and
-the factor gradients within rel-L2 1e-2 (their sums over rows run in a different order).
+and token gradients are compared exactly (a row's result does not depend on which rows share its tile) and the factor
+gradients within rel-L2 1e-2 (their sums over rows run in a different order).  Under a placement the token gradient adds a
+token's routes in another order (the permute backward rounds to bf16 after every add, in sorted-position order), so 4
+is run twice: chunks alone, exact; chunks and placement, token gradients to rounding.
 Prints one line "rank R: OK" or raises.
 """
 import os
@@ -97,11 +99,21 @@ def main() -> int:
     order = ep_peer.experts_of_rank(placement, rank, world).to(dev)
     pk_placed = [p.reshape(e, -1).index_select(0, order).reshape(-1) for p in all_pk]
     lora_placed = {n: v.index_select(0, order) for n, v in all_lora.items()}
+    xchg_c = ep_peer.PeerExchange(t * k, h, e, device=dev, chunks=2)
+    for _ in range(2):
+        chunked = run(lambda hh, ll: ep_peer.peer_moe_layer(xchg_c, hh, idx, wts, *flat, q4k, i, ll, 2.0), hidden, lora, gout)
+        assert torch.equal(chunked[0], whole[0][rows]), "chunked outputs differ from the single-device layer"
+        assert torch.equal(chunked[1], whole[1][rows]), "chunked token gradients differ from the single-device layer"
+        for got, want, name in zip(chunked[2:], whole[2:], lora):
+            want = want[mine].float()
+            err = float((got.float() - want).norm() / want.norm().clamp_min(1e-20))
+            assert err <= 1e-2, (name, err)
     xchg2 = ep_peer.PeerExchange(t * k, h, e, device=dev, chunks=2, placement=placement)
     for _ in range(2):
         placed = run(lambda hh, ll: ep_peer.peer_moe_layer(xchg2, hh, idx, wts, *pk_placed, q4k, i, ll, 2.0), hidden, lora_placed, gout)
         assert torch.equal(placed[0], whole[0][rows]), "chunked / placed outputs differ from the single-device layer"
-        assert torch.equal(placed[1], whole[1][rows]), "chunked / placed token gradients differ from the single-device layer"
+        d = float((placed[1].float() - whole[1][rows].float()).norm() / whole[1][rows].float().norm())
+        assert d < 5e-3, ("token gradients under a placement", d)
         for got, want, name in zip(placed[2:], whole[2:], lora):
             want = want.index_select(0, order).float()
             err = float((got.float() - want).norm() / want.norm().clamp_min(1e-20))

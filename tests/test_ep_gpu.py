@@ -68,27 +68,39 @@ def test_single_rank_expert_parallel_equals_local_layer(cuda):
         routing.combine(ex.detach(), plan).backward(gout)
         assert torch.equal(w3.grad, w2.grad)
 
-        # the token range in three chunks on two streams (exchange beside the expert products) and the experts placed by load:
-        # outputs and token gradients are the same bits (a row's result does not depend on its neighbours), factor gradients
-        # are sums over rows taken chunk by chunk
+        # the token range in three chunks on two streams (exchange beside the expert products): outputs and token gradients are
+        # the same bits (a row's result does not depend on its neighbours), factor gradients are sums over rows taken chunk by chunk
+        xchg3 = ep_peer.PeerExchange(t * k, h, e, device=cuda, chunks=3)
+        assert xchg3.token_bounds(t) == [(0, 100), (100, 200), (200, 300)] and xchg3.token_bounds(7) == [(0, 3), (3, 5), (5, 7)]
+        xchg3.profile = True
+        for _ in range(2):
+            h4 = hidden.clone().requires_grad_(True)
+            l4 = {n: v.clone().requires_grad_(True) for n, v in lora.items()}
+            out4 = ep_peer.peer_moe_layer(xchg3, h4, idx, wts, *pk, go.Q4_K, i, l4, 2.0)
+            out4.backward(gout)
+            assert torch.equal(out4, out2) and torch.equal(h4.grad, h2.grad)
+            for n in lora:
+                err = float((l4[n].grad.float() - l2[n].grad.float()).norm() / l2[n].grad.float().norm())
+                assert err < 1e-2, (n, err)
+
+        # experts placed by load: the router's ids go through the placement table, each rank holds the experts it was given.
+        # Outputs stay the same bits (the combine adds a token's routes in router order); the token gradient adds them in
+        # sorted-position order with a bf16 rounding per add, and the placement changes that order, so it agrees to rounding
         load = torch.bincount(idx.flatten().cpu(), minlength=e).float()
         placement = ep_peer.balanced_placement(load, 1)
         order = ep_peer.experts_of_rank(placement, 0, 1).to(cuda)
         pk_placed = [p.reshape(e, -1).index_select(0, order).reshape(-1) for p in pk]
         lora_placed = {n: v.index_select(0, order) for n, v in lora.items()}
-        xchg3 = ep_peer.PeerExchange(t * k, h, e, device=cuda, chunks=3, placement=placement)
-        assert xchg3.token_bounds(t) == [(0, 100), (100, 200), (200, 300)] and xchg3.token_bounds(7) == [(0, 3), (3, 5), (5, 7)]
-        xchg3.profile = True
-        for _ in range(2):
-            h4 = hidden.clone().requires_grad_(True)
-            l4 = {n: v.clone().requires_grad_(True) for n, v in lora_placed.items()}
-            out4 = ep_peer.peer_moe_layer(xchg3, h4, idx, wts, *pk_placed, go.Q4_K, i, l4, 2.0)
-            out4.backward(gout)
-            assert torch.equal(out4, out2) and torch.equal(h4.grad, h2.grad)
-            for n in lora:
-                want = l2[n].grad.index_select(0, order).float()
-                err = float((l4[n].grad.float() - want).norm() / want.norm())
-                assert err < 1e-2, (n, err)
+        xchg4 = ep_peer.PeerExchange(t * k, h, e, device=cuda, chunks=2, placement=placement)
+        h7 = hidden.clone().requires_grad_(True)
+        l7 = {n: v.clone().requires_grad_(True) for n, v in lora_placed.items()}
+        out7 = ep_peer.peer_moe_layer(xchg4, h7, idx, wts, *pk_placed, go.Q4_K, i, l7, 2.0)
+        out7.backward(gout)
+        assert torch.equal(out7, out2)
+        assert float((h7.grad.float() - h2.grad.float()).norm() / h2.grad.float().norm()) < 5e-3
+        for n in lora:
+            want = l2[n].grad.index_select(0, order).float()
+            assert float((l7[n].grad.float() - want).norm() / want.norm()) < 1e-2, n
         phases = xchg3.phase_ms()
         assert {"dispatch", "experts_forward", "return", "combine", "experts_backward", "gather_backward"} <= set(phases)
 
