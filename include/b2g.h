@@ -185,10 +185,11 @@ B2G_API int b2g_route_combine_bwd(const void* expert_out, const void* weights, i
  * expert_indices[G] int64, offsets[G] int32 cumulative ends (the pair produced by
  * GGUFExperts._prepare_expert_execution, fast_moe_lora.py:709-719).  `tiles` is int32 scratch of
  * b2g_grouped_tiles_bytes(R, G) bytes that the grouped calls below consume.  Offsets beyond R are clamped to R (no
- * tile ever reaches past the R activation rows, nor past the table) and set status 904. */
+ * tile ever reaches past the R activation rows, nor past the table) and set status 904.  first_row (device int32, nullable):
+ * where the first listed expert's rows begin (0 when null), for a table over a sub-range of a larger sorted buffer. */
 B2G_API int64_t b2g_grouped_tiles_bytes(int64_t R, int G);
-B2G_API int b2g_grouped_schedule(const int64_t* expert_indices, const int32_t* offsets, int G, int64_t R, int32_t* tiles,
-                         int* status, void* stream);
+B2G_API int b2g_grouped_schedule(const int64_t* expert_indices, const int32_t* offsets, const int32_t* first_row, int G, int64_t R,
+                         int32_t* tiles, int* status, void* stream);
 
 /* One persistent launch over the ragged expert segments:
  *   Y0[rows_g, N] = X[rows_g, K] . deq(W0[e_g])^T   and, when payload1 != NULL, Y1 likewise from W1.
@@ -218,10 +219,11 @@ B2G_API int b2g_grouped_lora_down(const void* x, const void* x1, const void* w, 
 
 /* Per-expert LoRA factor gradients over all E experts (zero rows -> exactly zero output):
  *   G[e][r,C] = scale * S[rows_e,16]^T . T[rows_e, C], stored [E,r,C] or (transpose_out) [E,C,r].
- * `offsets_full` is the cumulative-end array over ALL E experts (fast_moe_lora.py:663-672).
+ * `offsets_full` is the cumulative-end array over ALL E experts (fast_moe_lora.py:663-672); first_row (device int32,
+ * nullable) is where the first expert's rows begin (0 when null).
  * Replaces AITER ptgmm via _aiter_weight_grad (fast_moe_lora.py:76-87,132-139). */
-B2G_API int b2g_grouped_lora_wgrad(const void* s, const void* t, float scale, const int32_t* offsets_full, void* out,
-                           int transpose_out, int64_t R, int64_t C, int r, int num_experts, int64_t out_col_offset,
+B2G_API int b2g_grouped_lora_wgrad(const void* s, const void* t, float scale, const int32_t* offsets_full, const int32_t* first_row,
+                           void* out, int transpose_out, int64_t R, int64_t C, int r, int num_experts, int64_t out_col_offset,
                            int64_t out_cols_total, void* stream);
 
 /* Per-expert up-projection from the rank: Y[rows_e, N] = P[rows_e, :r] . W[e]^T with P of row stride
@@ -234,25 +236,28 @@ B2G_API int b2g_grouped_lora_up(const void* p, int64_t ldp, const void* w, int w
 /* ---- expert-parallel row exchange over peer memory (new design: the reference is single-GPU,
  *      docs/plan_qwen3.5.md:23) -------------------------------------------------------------------------- */
 
-/* Source side.  For every routed row s (rows sorted by global expert id, sorted_expert[R]) copy the row into the
- * receive buffer of the expert's owner rank: peer_ptrs[owner] (device array of one base address per rank, NVLink
- * peer pointers of a symmetric allocation) at row dest_base[e] + (s - my_start[e]).  With perm != NULL the row is
- * gathered from the token matrix (row perm[s] / top_k of src): the token permute of _route_gather_forward_kernel
- * (fast_moe_routing.py:101-123) and the inter-GPU dispatch in one pass; with perm == NULL row s of src is sent.
- * A slot at or beyond capacity_rows is never written; the status word is set to 901 instead (b2g_ep_peer_plan clamps the
- * owner's segments to the same capacity, so the rows that were dropped are not read either).  The walk over the rows
- * starts at the first row of expert first_expert (a global id below the expert count) and wraps around: callers give every
- * rank a different owner's first expert so that the ranks do not all store to the same owner at once. */
+/* Source side.  For every routed row s (rows sorted by global expert id, sorted_expert[R]) whose local expert index
+ * (id modulo experts_per_rank) lies in [group_lo, group_hi), copy the row into the receive buffer of the expert's owner rank:
+ * peer_ptrs[owner] (device array of one base address per rank, NVLink peer pointers of a symmetric allocation) at row
+ * dest_base[e] + (s - my_start[e]).  With perm != NULL the row is gathered from the token matrix (row perm[s] / top_k of
+ * src): the token permute of _route_gather_forward_kernel (fast_moe_routing.py:101-123) and the inter-GPU dispatch in one
+ * pass; with perm == NULL row s of src is sent.  A slot at or beyond capacity_rows is never written; the status word is set to
+ * 901 instead (b2g_ep_peer_plan clamps the owner's segments to the same capacity, so the rows that were dropped are not read
+ * either).  The owners are visited in the order rank+1, rank+2, ..., so that the ranks do not all store to the same owner at
+ * once.  One launch per expert group lets the caller overlap a group's transfer with another group's expert products:
+ * ctas_per_sm = 1 makes the kernel small enough to share every SM with the quantized GEMM (128 threads of 32 registers, no
+ * shared memory); an exchange that runs alone takes 8 for bandwidth. */
 B2G_API int b2g_ep_scatter_rows(const void* src, const int64_t* perm, int top_k, const int64_t* sorted_expert,
                         const int32_t* my_start, const int32_t* dest_base, const uint64_t* peer_ptrs, int experts_per_rank,
-                        int64_t R, int H, int64_t capacity_rows, int first_expert, int* status, void* stream);
+                        int world, int rank, int group_lo, int group_hi, int64_t R, int H, int64_t capacity_rows, int ctas_per_sm,
+                        int* status, void* stream);
 
 /* Owner side, the inverse: rows of the grouped buffer (blocks ordered by (local expert, source rank), block b
  * spanning rows [blk_start[b], blk_start[b+1]), source rank b % world) go back to their source rank at row
- * src_pos[b] + offset inside the block.  Pairs with the weighted un-permute of fast_moe_routing.py:162-194 on the
- * source rank. */
+ * src_pos[b] + offset inside the block; the call moves the blocks [block_lo, block_hi) (whole experts: multiples of world).
+ * Pairs with the weighted un-permute of fast_moe_routing.py:162-194 on the source rank. */
 B2G_API int b2g_ep_return_rows(const void* rows, const int32_t* blk_start, const int32_t* src_pos, const uint64_t* peer_ptrs,
-                       int world, int num_blocks, int H, int64_t capacity_rows, void* stream);
+                       int world, int block_lo, int block_hi, int H, int64_t capacity_rows, int ctas_per_sm, void* stream);
 
 /* Slots of the two exchange kernels for rank `rank`, from the all-gathered histograms counts[world][num_experts]
  * (int32, row g = rows of rank g per global expert, rows count_stride elements apart; rank g owns experts
@@ -271,12 +276,13 @@ B2G_API int b2g_ep_peer_plan(const int32_t* counts, int64_t count_stride, int wo
 /* SwiGLU between the two grouped products: z = silu(g) * u (optionally clamped as the DeepSeek
  * experts do: g <= limit, |u| <= limit; limit <= 0 disables).  Replaces GGUFExperts._apply_split_gate
  * (called at fast_moe_lora.py:747; clamp semantics at test_deepseek_v4_moe_lora.py:194-196).  n = elements of each tensor.
- * live_rows (nullable, device int32): only the first *live_rows rows of `cols` elements are processed, for tensors that are
- * the partly filled receive buffer of an expert-parallel exchange, whose fill count never visits the host. */
-B2G_API int b2g_swiglu_fwd(const void* gate, const void* up, void* z, int64_t n, float limit, const int32_t* live_rows, int64_t cols,
-                   void* stream);
+ * row_begin / row_end (nullable, device int32): only the rows [*row_begin, *row_end) of `cols` elements are processed (0 and
+ * all rows when null), for tensors that are the partly filled receive buffer of an expert-parallel exchange, whose fill
+ * counts never visit the host. */
+B2G_API int b2g_swiglu_fwd(const void* gate, const void* up, void* z, int64_t n, float limit, const int32_t* row_begin,
+                   const int32_t* row_end, int64_t cols, void* stream);
 B2G_API int b2g_swiglu_bwd(const void* gate, const void* up, const void* dz, void* dgate, void* dup, int64_t n, float limit,
-                   const int32_t* live_rows, int64_t cols, void* stream);
+                   const int32_t* row_begin, const int32_t* row_end, int64_t cols, void* stream);
 
 #ifdef __cplusplus
 }

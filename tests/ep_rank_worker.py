@@ -4,13 +4,13 @@ Every rank holds its own tokens and its own experts.  The layer is evaluated thr
   1. peer stores over NVLink (b2g/ep_peer.py), twice, so that the second call reuses the symmetric buffers;
   2. NCCL all-to-all (b2g/ep.py);
   3. on one device: all ranks' tokens and all experts gathered onto this rank, plain single-GPU layer;
-  4. peer stores again with the token range in two chunks (exchange stream beside the compute stream) and the experts
-     placed over the ranks by load instead of in contiguous blocks.
+  4. peer stores again with every rank's experts in two groups (one group's exchange beside another group's products) and
+     the experts placed over the ranks by load instead of in contiguous blocks.
 1 and 2 run the same kernels on the same rows in the same order and must agree bit for bit.  Against 3 the outputs
 and token gradients are compared exactly (a row's result does not depend on which rows share its tile) and the factor
 gradients within rel-L2 1e-2 (their sums over rows run in a different order).  Under a placement the token gradient adds a
 token's routes in another order (the permute backward rounds to bf16 after every add, in sorted-position order), so 4
-is run twice: chunks alone, exact; chunks and placement, token gradients to rounding.
+is run twice: groups alone, exact; groups and placement, token gradients to rounding.
 Prints one line "rank R: OK" or raises.
 """
 import os

@@ -68,10 +68,10 @@ def test_single_rank_expert_parallel_equals_local_layer(cuda):
         routing.combine(ex.detach(), plan).backward(gout)
         assert torch.equal(w3.grad, w2.grad)
 
-        # the token range in three chunks on two streams (exchange beside the expert products): outputs and token gradients are
-        # the same bits (a row's result does not depend on its neighbours), factor gradients are sums over rows taken chunk by chunk
+        # the experts in three groups on two streams (one group's exchange beside another group's products): the same kernels
+        # on the same rows in the same order, so every result is the same bits
         xchg3 = ep_peer.PeerExchange(t * k, h, e, device=cuda, chunks=3)
-        assert xchg3.token_bounds(t) == [(0, 100), (100, 200), (200, 300)] and xchg3.token_bounds(7) == [(0, 3), (3, 5), (5, 7)]
+        assert xchg3.groups == [(0, 6), (6, 11), (11, 16)]
         xchg3.profile = True
         for _ in range(2):
             h4 = hidden.clone().requires_grad_(True)
@@ -80,8 +80,7 @@ def test_single_rank_expert_parallel_equals_local_layer(cuda):
             out4.backward(gout)
             assert torch.equal(out4, out2) and torch.equal(h4.grad, h2.grad)
             for n in lora:
-                err = float((l4[n].grad.float() - l2[n].grad.float()).norm() / l2[n].grad.float().norm())
-                assert err < 1e-2, (n, err)
+                assert torch.equal(l4[n].grad, l2[n].grad), n
 
         # experts placed by load: the router's ids go through the placement table, each rank holds the experts it was given.
         # Outputs stay the same bits (the combine adds a token's routes in router order); the token gradient adds them in
@@ -115,8 +114,8 @@ def test_single_rank_expert_parallel_equals_local_layer(cuda):
         out5 = ep_peer.peer_moe_layer(small, h5, idx, wts, *pk, go.Q4_K, i, {n: v.clone().requires_grad_(True) for n, v in lora.items()}, 2.0)
         out5.backward(gout)
         torch.cuda.synchronize()
-        assert int(small.plans[0].local_offsets[-1]) == small.capacity and int(small.plans[0].blk_start[-1]) == small.capacity
-        assert int(small.plans[0].local_sizes.sum()) == small.capacity
+        assert int(small.plan.local_offsets[-1]) == small.capacity and int(small.plan.blk_start[-1]) == small.capacity
+        assert int(small.plan.local_sizes.sum()) == small.capacity
         with pytest.raises(Exception, match="901"):
             ops.check_status()
         h6 = hidden.clone().requires_grad_(True)

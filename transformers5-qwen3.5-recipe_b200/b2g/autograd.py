@@ -308,7 +308,7 @@ def expert_block_forward(sel, gate_p, up_p, down_p, quant_gu, quant_down, inter_
         gate, up = ops.grouped_fwd(sel, gate_p.reshape(-1), up_p.reshape(-1), quant_gu, inter_dim, e, tiles)
     # the last cumulative end = rows that hold data; an expert-parallel receive buffer is larger than that
     live = offsets_full[-1:] if offsets_full is not None and offsets_full.numel() else None
-    z = ops.swiglu_fwd(gate, up, swiglu_limit, live)
+    z = ops.swiglu_fwd(gate, up, swiglu_limit, None, live)
     if has_lora:
         za, zas = ops.grouped_lora_down(z, None, down_a.contiguous(), False, scaling, r, tiles, zero=False)
         out = ops.grouped_fwd(z, down_p.reshape(-1), None, quant_down, hidden, e, tiles, zas, ops.pad_rank_cols(down_b))
@@ -340,7 +340,7 @@ def expert_block_backward(saved, d_out):
     else:
         dz = ops.grouped_dgrad(d_out, None, down_p.reshape(-1), None, quant_down, inter_dim, e, tiles)
     live = offsets_full[-1:] if offsets_full is not None and offsets_full.numel() else None
-    d_gate, d_up = ops.swiglu_bwd(gate, up, dz, limit, live)
+    d_gate, d_up = ops.swiglu_bwd(gate, up, dz, limit, None, live)
     if has_lora:
         # gate|up: dX = dG.deq(Wg) + dU.deq(Wu) + s.([dG|dU].Bgu).Agu
         dgb, dgbs = ops.grouped_lora_down(d_gate, d_up, gu_b.transpose(1, 2).contiguous(), False, scaling, r, tiles, zero=False)

@@ -8,16 +8,19 @@ the same arithmetic as tensor ops, kept as the checkable statement of it), so no
 is regrouped afterwards.  Every rank starts its scatter at a different owner's experts, so that the ranks do not all store
 to one GPU at a time.
 
-Overlap.  The rank's tokens are cut into ``chunks`` ranges.  The exchanges run on a stream of their own, the expert
-products on the caller's stream, and events hand the chunks over, so that chunk ``c+1`` crosses NVLink while chunk ``c``
-computes, in both directions of both passes:
+Overlap.  Every rank's experts are cut into ``chunks`` EXPERT GROUPS (the same ranges of local expert indices on every
+rank).  The rows of one group are exchanged by one launch; the exchanges run on a stream of their own, the expert products
+on the caller's stream, and events hand the groups over, so that group ``c+1`` crosses NVLink while group ``c`` computes, in
+both directions of both passes:
 
-    exchange stream :  scatter 0 | scatter 1 |            | return 0 | return 1 |
-    compute stream  :            | experts 0 | experts 1  |          | combine 0 | combine 1
+    exchange stream :  scatter 0 | scatter 1 | scatter 2 |  return 0 | return 1  | return 2 |
+    compute stream  :            | experts 0 | experts 1 | experts 2 |           |          | combine
 
-The exchange kernels are small enough (128 threads, 48 registers, no shared memory) to sit on the same SMs as the GEMM's
-CTA.  The whole layer is ONE autograd node whose backward is written out by hand in the mirrored order, because autograd
-would enqueue the two chunks' backward kernels one chunk after the other and undo the overlap.
+Cutting by experts rather than by tokens keeps every expert's rows together (its packed weight is unpacked once per 512 rows
+whatever the number of groups), needs one routing plan per step, and lets each group write its own rows of shared
+activation buffers and its own experts' factor gradients.  The exchange kernels are small enough (128 threads, 32 registers,
+no shared memory, one CTA per SM) to sit on the same SMs as the GEMM's CTA.  The whole layer is ONE autograd node whose
+backward is written out by hand in the mirrored order.
 
 Buffers are symmetric allocations (one per rank, same size, mapped into every rank): two receive buffers (activations
 forward, output gradients backward) and two return buffers of the rank's own routed-row count.  By default a receive
@@ -170,36 +173,42 @@ class PeerExchange:
         if num_experts % self.world:
             raise ValueError(f"{num_experts} experts do not divide over {self.world} ranks")
         self.experts_per_rank = num_experts // self.world
-        self.chunks = max(1, int(chunks))
+        self.chunks = max(1, min(int(chunks), self.experts_per_rank))
         self.placement = None if placement is None else placement.to(device=self.device, dtype=torch.int64).contiguous()
-        # rows per chunk are bounded by ceil(rows_local / chunks) rounded up to a whole token; the receive side of a chunk holds,
-        # in the worst case, that many rows from every rank
-        self.chunk_rows = -(-self.rows_local // self.chunks)
+        # expert groups: equal parts of the local expert range, the first (experts_per_rank % chunks) one expert longer
+        base, extra = divmod(self.experts_per_rank, self.chunks)
+        self.groups, lo = [], 0
+        for c in range(self.chunks):
+            hi = lo + base + (1 if c < extra else 0)
+            self.groups.append((lo, hi))
+            lo = hi
+        # a receive buffer holds, in the worst case, the routed rows of every rank
         factor = float(self.world) if capacity_factor is None else float(capacity_factor)
-        cap = int(self.chunk_rows * min(factor, float(self.world)))
+        cap = int(self.rows_local * min(factor, float(self.world)))
         row_bytes = 2 * hidden
-        budget_rows = (self.MAX_BUFFER_BYTES // row_bytes - 2 * self.rows_local) // (2 * self.chunks)
+        budget_rows = (self.MAX_BUFFER_BYTES // row_bytes - 2 * self.rows_local) // 2
         cap = max(512, min(cap, budget_rows))
-        self.capacity = (cap + 511) // 512 * 512                  # rows of ONE chunk's receive buffer
+        self.capacity = (cap + 511) // 512 * 512
         self.recv, self.ret, self._recv_ptrs, self._ret_ptrs = [], [], [], []
         for _ in range(2):
-            for store, ptrs, rows in ((self.recv, self._recv_ptrs, self.capacity * self.chunks), (self.ret, self._ret_ptrs, max(1, self.rows_local))):
+            for store, ptrs, rows in ((self.recv, self._recv_ptrs, self.capacity), (self.ret, self._ret_ptrs, max(1, self.rows_local))):
                 t = symm.empty((rows, hidden), dtype=torch.bfloat16, device=self.device)
                 h = symm.rendezvous(t, self.group)
                 store.append(t)
-                ptrs.append([int(p) for p in h.buffer_ptrs])
+                ptrs.append(torch.tensor([int(p) for p in h.buffer_ptrs], dtype=torch.int64, device=self.device))
         self._flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.stream = torch.cuda.Stream(device=self.device, priority=-1)
-        words = _plan_words(self.world, num_experts)
-        self._plan_buf = torch.empty(self.chunks, words, dtype=torch.int32, device=self.device)
-        self.plans = [_plan_views(self._plan_buf[c], self.world, num_experts) for c in range(self.chunks)]
-        self.counts_mine = torch.zeros(self.chunks, num_experts, dtype=torch.int32, device=self.device)
-        self.counts_all = torch.zeros(self.world, self.chunks, num_experts, dtype=torch.int32, device=self.device)
+        self.plan = _plan_views(torch.empty(_plan_words(self.world, num_experts), dtype=torch.int32, device=self.device), self.world, num_experts)
+        self.counts_mine = torch.zeros(num_experts, dtype=torch.int32, device=self.device)
+        self.counts_all = torch.zeros(self.world, num_experts, dtype=torch.int32, device=self.device)
         self.local_ids = torch.arange(self.experts_per_rank, device=self.device, dtype=torch.int64)
-        self._ptr_cache: dict[tuple[int, int, int], torch.Tensor] = {}
+        # first row and end row of every group inside the receive buffer: one-element views of the plan's cumulative ends
+        off = self.plan.local_offsets
+        self.group_first = [None if lo == 0 else off[lo - 1:lo] for lo, _ in self.groups]
+        self.group_end = [off[hi - 1:hi] for _, hi in self.groups]
         self.events = {name: [torch.cuda.Event() for _ in range(self.chunks)] for name in
-                       ("sent", "computed", "returned", "g_ready", "g_sent", "g_computed", "g_returned")}
-        self.ev_plan = torch.cuda.Event()
+                       ("sent", "computed", "returned", "g_sent", "g_computed", "g_returned")}
+        self.ev_plan, self.ev_ready = torch.cuda.Event(), torch.cuda.Event()
         self.profile = False
         self.trace: list = []
 
@@ -211,62 +220,39 @@ class PeerExchange:
             out[name] = out.get(name, 0.0) + a.elapsed_time(b)
         return out
 
-    # -- geometry ---------------------------------------------------------------------------------------------------------
-    def token_bounds(self, tokens: int) -> list[tuple[int, int]]:
-        """Token range of every chunk: equal parts, the first ``tokens % chunks`` one token longer."""
-        base, extra = divmod(tokens, self.chunks)
-        out, t0 = [], 0
-        for c in range(self.chunks):
-            t1 = t0 + base + (1 if c < extra else 0)
-            out.append((t0, t1))
-            t0 = t1
-        return out
-
-    def recv_view(self, which: int, chunk: int) -> torch.Tensor:
-        return self.recv[which][chunk * self.capacity:(chunk + 1) * self.capacity]
-
-    def _peer_table(self, kind: int, which: int, row0: int) -> torch.Tensor:
-        """Device array of every rank's address of row ``row0`` of a buffer (kind 0 = receive, 1 = return)."""
-        key = (kind, which, row0)
-        t = self._ptr_cache.get(key)
-        if t is None:
-            base = (self._recv_ptrs if kind == 0 else self._ret_ptrs)[which]
-            t = torch.tensor([p + row0 * self.hidden * 2 for p in base], dtype=torch.int64, device=self.device)
-            self._ptr_cache[key] = t
-        return t
-
     # -- pieces (each runs on the CURRENT stream) ---------------------------------------------------------------------------
     def sync(self) -> None:
         """All ranks' earlier work on this stream is complete before any rank continues on it."""
         dist.all_reduce(self._flag, group=self.group)
 
-    def gather_counts(self) -> None:
-        dist.all_gather_into_tensor(self.counts_all.view(-1), self.counts_mine.view(-1), group=self.group)
+    def make_plan(self) -> PeerPlan:
+        """All-gather of the per-rank expert histograms (``counts_mine``) and the slot plan from them, one launch each."""
+        dist.all_gather_into_tensor(self.counts_all.view(-1), self.counts_mine, group=self.group)
+        _launch_plan(self.counts_all, self.num_experts, self.world, self.num_experts, self.rank, self.plan, self.capacity)
+        return self.plan
 
-    def plan_chunk(self, chunk: int) -> PeerPlan:
-        _launch_plan(self.counts_all[0, chunk], self.chunks * self.num_experts, self.world, self.num_experts, self.rank, self.plans[chunk],
-                     self.capacity)
-        return self.plans[chunk]
+    ALONE, BESIDE = 8, 1             # CTAs per SM of an exchange that nothing computes beside / that shares the SMs with the GEMM
 
-    def scatter(self, src: torch.Tensor, perm: Optional[torch.Tensor], top_k: int, sorted_expert: torch.Tensor, chunk: int, which: int):
-        """Rows of ``src`` (gathered through ``perm`` when given) into the owners' receive buffers of this chunk."""
-        rows = sorted_expert.numel()
-        plan = self.plans[chunk]
-        peers = self._peer_table(0, which, chunk * self.capacity)
+    def scatter(self, src: torch.Tensor, perm: Optional[torch.Tensor], top_k: int, sorted_expert: torch.Tensor, chunk: int, which: int) -> None:
+        """Rows of ``src`` (gathered through ``perm`` when given) that belong to expert group ``chunk`` into the owners' receive
+        buffers.  The first group's scatter has nothing to hide behind (the experts wait for it), so it takes the whole GPU; the
+        others run beside the previous group's expert products."""
+        lo, hi = self.groups[chunk]
         with torch.cuda.device(self.device):
             _lib.call("b2g_ep_scatter_rows", C.c_void_p(src.data_ptr()), None if perm is None else C.c_void_p(perm.data_ptr()), int(top_k),
-                      C.c_void_p(sorted_expert.data_ptr()), C.c_void_p(plan.my_start.data_ptr()), C.c_void_p(plan.dest_base.data_ptr()),
-                      C.c_void_p(peers.data_ptr()), self.experts_per_rank, rows, self.hidden, self.capacity,
-                      ((self.rank + 1) % self.world) * self.experts_per_rank,      # start with the next rank's experts
+                      C.c_void_p(sorted_expert.data_ptr()), C.c_void_p(self.plan.my_start.data_ptr()), C.c_void_p(self.plan.dest_base.data_ptr()),
+                      C.c_void_p(self._recv_ptrs[which].data_ptr()), self.experts_per_rank, self.world, self.rank, lo, hi,
+                      sorted_expert.numel(), self.hidden, self.capacity, self.ALONE if chunk == 0 else self.BESIDE,
                       C.c_void_p(ops.status_word(self.device).data_ptr()), C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
 
-    def give_back(self, rows: torch.Tensor, chunk: int, which: int, row0: int) -> None:
-        """Rows of this rank's receive-side result back to their sources, at ``row0`` + sorted position of their return buffer."""
-        plan = self.plans[chunk]
-        peers = self._peer_table(1, which, row0)
+    def give_back(self, rows: torch.Tensor, chunk: int, which: int) -> None:
+        """Rows of expert group ``chunk`` of this rank's receive-side result back to their sources' return buffers (the last
+        group's return runs after all expert products, alone)."""
+        lo, hi = self.groups[chunk]
         with torch.cuda.device(self.device):
-            _lib.call("b2g_ep_return_rows", C.c_void_p(rows.data_ptr()), C.c_void_p(plan.blk_start.data_ptr()), C.c_void_p(plan.src_pos.data_ptr()),
-                      C.c_void_p(peers.data_ptr()), self.world, self.experts_per_rank * self.world, self.hidden, self.capacity,
+            _lib.call("b2g_ep_return_rows", C.c_void_p(rows.data_ptr()), C.c_void_p(self.plan.blk_start.data_ptr()),
+                      C.c_void_p(self.plan.src_pos.data_ptr()), C.c_void_p(self._ret_ptrs[which].data_ptr()), self.world, lo * self.world,
+                      hi * self.world, self.hidden, self.capacity, self.ALONE if chunk == self.chunks - 1 else self.BESIDE,
                       C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
 
 
@@ -274,7 +260,7 @@ class _Span:
     """Optional timing of one phase on one stream: a pair of timing events appended to ``xchg.trace`` while
     ``xchg.profile`` is set (the benchmark's phase table); free otherwise."""
 
-    def __init__(self, xchg: "PeerExchange", name: str, stream: torch.cuda.Stream):
+    def __init__(self, xchg: PeerExchange, name: str, stream: torch.cuda.Stream):
         self.on = xchg.profile
         if self.on:
             self.xchg, self.name, self.stream = xchg, name, stream
@@ -290,139 +276,152 @@ class _Span:
             self.xchg.trace.append((self.name, self.a, self.b))
 
 
+def _bf16(rows: int, cols: int, dev) -> torch.Tensor:
+    return torch.empty(rows, cols, dtype=torch.bfloat16, device=dev)
+
+
 class _PeerMoe(torch.autograd.Function):
-    """The whole expert-parallel layer as one node: chunked, exchanges on their own stream, backward in mirrored order."""
+    """The whole expert-parallel layer as one node: expert groups, exchanges on their own stream, backward in mirrored order."""
 
     @staticmethod
     def forward(ctx, xchg: PeerExchange, hidden, top_k_index, top_k_weights, gate_p, up_p, down_p, quant_type, inter_dim, scaling,
                 gu_a, gu_b, down_a, down_b):
-        from . import autograd as ag
-
         tokens, top_k = top_k_index.shape
-        if tokens * top_k > xchg.rows_local or hidden.shape[1] != xchg.hidden:
-            raise ValueError(f"the exchange buffers hold {xchg.rows_local} routed rows of width {xchg.hidden}; got {tokens * top_k} x {hidden.shape[1]}")
+        rows = tokens * top_k
+        if rows > xchg.rows_local or hidden.shape[1] != xchg.hidden:
+            raise ValueError(f"the exchange buffers hold {xchg.rows_local} routed rows of width {xchg.hidden}; got {rows} x {hidden.shape[1]}")
         dev = hidden.device
         cs, xs, ev = torch.cuda.current_stream(dev), xchg.stream, xchg.events
-        bounds = xchg.token_bounds(tokens)
         hidden = hidden.contiguous()
         weights = top_k_weights.contiguous()
         ids = top_k_index if xchg.placement is None else xchg.placement[top_k_index.long()]
+        e_local, cap, plan = xchg.experts_per_rank, xchg.capacity, xchg.plan
+        lora = gu_a is not None
+        r = gu_a.shape[1] if lora else 0
 
-        routes = []                                      # per chunk: (sorted expert ids, permutation, inverse, first row of the chunk)
-        row0 = 0
         with _Span(xchg, "plan", cs):
-            for c, (t0, t1) in enumerate(bounds):
-                sorted_e, perm, inverse, sizes, _ = ops.route_plan(ids[t0:t1].contiguous(), xchg.num_experts)
-                xchg.counts_mine[c].copy_(sizes)
-                routes.append((sorted_e, perm, inverse, row0))
-                row0 += (t1 - t0) * top_k
+            sorted_e, perm, inverse, sizes, _ = ops.route_plan(ids.contiguous(), xchg.num_experts)
+            xchg.counts_mine.copy_(sizes)
         xchg.ev_plan.record(cs)
+        # activations of all groups live in shared buffers (every group writes its own rows); allocated on the compute stream
+        gate, up, z, out_e = _bf16(cap, inter_dim, dev), _bf16(cap, inter_dim, dev), _bf16(cap, inter_dim, dev), _bf16(cap, xchg.hidden, dev)
+        xa = xas = za = zas = gu_a_c = gu_b16 = down_a_c = down_b16 = None
+        if lora:
+            xa, xas, za, zas = (_bf16(cap, ops.LORA_PAD, dev) for _ in range(4))
+            gu_a_c, down_a_c = gu_a.contiguous(), down_a.contiguous()
+            gu_b16, down_b16 = ops.pad_rank_cols(gu_b), ops.pad_rank_cols(down_b)
 
         with torch.cuda.stream(xs):
             xs.wait_event(xchg.ev_plan)
             with _Span(xchg, "plan_exchange", xs):
-                xchg.gather_counts()
-                for c in range(xchg.chunks):
-                    xchg.plan_chunk(c)
-            for c, (t0, t1) in enumerate(bounds):
-                sorted_e, perm, _, _ = routes[c]
-                # No wait is needed before writing a receive buffer: its last readers (the previous call's backward) were
+                xchg.make_plan()
+            for c in range(xchg.chunks):
+                # No wait is needed before writing the receive buffer: its last readers (the previous call's backward) were
                 # enqueued before that call's final sync(), which every rank has passed to get here.
                 with _Span(xchg, "dispatch", xs):
-                    xchg.scatter(hidden[t0:t1], perm, top_k, sorted_e, c, 0)
-                    xchg.sync()                          # every source has delivered chunk c
+                    xchg.scatter(hidden, perm, top_k, sorted_e, c, 0)
+                    xchg.sync()                          # every source has delivered group c
                 ev["sent"][c].record(xs)
 
-        lora = gu_a is not None
-        saved, outs = [], []
-        for c in range(xchg.chunks):
+        x = xchg.recv[0]
+        tiles = []
+        for c, (lo, hi) in enumerate(xchg.groups):
             cs.wait_event(ev["sent"][c])
-            plan = xchg.plans[c]
+            first, end = xchg.group_first[c], xchg.group_end[c]
             with _Span(xchg, "experts_forward", cs):
-                out_c, sv = ag.expert_block_forward(xchg.recv_view(0, c), gate_p, up_p, down_p, quant_type, quant_type, inter_dim,
-                                                    xchg.local_ids, plan.local_offsets, plan.local_offsets, gu_a if lora else None,
-                                                    gu_b if lora else None, down_a if lora else None, down_b if lora else None, scaling, 0.0)
+                t = ops.grouped_schedule(xchg.local_ids[lo:hi], plan.local_offsets[lo:hi], cap, first)
+                if lora:
+                    ops.grouped_lora_down(x, None, gu_a_c, False, scaling, r, t, zero=False, out=(xa, xas))
+                ops.grouped_fwd(x, gate_p.reshape(-1), up_p.reshape(-1), quant_type, inter_dim, e_local, t, xas, gu_b16, out0=gate, out1=up)
+                ops.swiglu_fwd(gate, up, 0.0, first, end, out=z)
+                if lora:
+                    ops.grouped_lora_down(z, None, down_a_c, False, scaling, r, t, zero=False, out=(za, zas))
+                ops.grouped_fwd(z, down_p.reshape(-1), None, quant_type, xchg.hidden, e_local, t, zas, down_b16, out0=out_e)
             ev["computed"][c].record(cs)
-            saved.append(sv)
-            outs.append(out_c)
+            tiles.append(t)
 
         with torch.cuda.stream(xs):
             for c in range(xchg.chunks):
                 xs.wait_event(ev["computed"][c])
                 with _Span(xchg, "return", xs):
-                    xchg.give_back(outs[c], c, 0, routes[c][3])
+                    xchg.give_back(out_e, c, 0)
                     xchg.sync()
                 ev["returned"][c].record(xs)
 
-        out = torch.empty(tokens, xchg.hidden, dtype=torch.bfloat16, device=dev)
-        returned = []
-        for c, (t0, t1) in enumerate(bounds):
-            cs.wait_event(ev["returned"][c])
-            rows_c = xchg.ret[0][routes[c][3]:routes[c][3] + (t1 - t0) * top_k]
-            with _Span(xchg, "combine", cs):
-                ops.route_combine(rows_c, weights[t0:t1], routes[c][2], out=out[t0:t1])
-            returned.append(rows_c)
-        # `outs` were read by the exchange stream; the compute stream has waited for the last of those reads above, so the
-        # allocator may hand their memory to later work of the compute stream
-        ctx.xchg, ctx.saved, ctx.routes, ctx.bounds, ctx.top_k = xchg, saved, routes, bounds, top_k
-        ctx.returned, ctx.weights, ctx.lora = returned, weights, lora
+        cs.wait_event(ev["returned"][-1])                 # the exchange stream is in order: the last group's return is the last
+        returned = xchg.ret[0][:rows]
+        with _Span(xchg, "combine", cs):
+            out = ops.route_combine(returned, weights, inverse)
+        # `out_e` was read by the exchange stream; the compute stream has waited for the last of those reads, so the allocator may
+        # hand its memory to later work of the compute stream
+        ctx.xchg, ctx.geometry, ctx.lora = xchg, (tokens, top_k, int(quant_type), int(inter_dim), float(scaling), r), lora
+        ctx.saved = (sorted_e, perm, inverse, weights, returned, tiles, gate, up, z, xa, za, gate_p, up_p, down_p, gu_a_c, gu_b, down_a_c, down_b)
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
-        from . import autograd as ag
-
-        xchg, routes, bounds, top_k = ctx.xchg, ctx.routes, ctx.bounds, ctx.top_k
+        xchg, lora = ctx.xchg, ctx.lora
+        tokens, top_k, quant_type, inter_dim, scaling, r = ctx.geometry
+        sorted_e, perm, inverse, weights, returned, tiles, gate, up, z, xa, za, gate_p, up_p, down_p, gu_a, gu_b, down_a, down_b = ctx.saved
         dev = grad_out.device
         cs, xs, ev = torch.cuda.current_stream(dev), xchg.stream, xchg.events
-        grad_out = grad_out.contiguous()
-        d_weights = torch.empty_like(ctx.weights)
-        d_rows = []
-        for c, (t0, t1) in enumerate(bounds):
-            with _Span(xchg, "combine_backward", cs):
-                d_out_c, d_w_c = ops.route_combine_bwd(ctx.returned[c], ctx.weights[t0:t1], routes[c][1], grad_out[t0:t1])
-                d_weights[t0:t1].copy_(d_w_c)
-            ev["g_ready"][c].record(cs)
-            d_rows.append(d_out_c)
+        e_local, cap, plan, hid = xchg.experts_per_rank, xchg.capacity, xchg.plan, xchg.hidden
+        with _Span(xchg, "combine_backward", cs):
+            d_rows, d_weights = ops.route_combine_bwd(returned, weights, perm, grad_out.contiguous())
+        xchg.ev_ready.record(cs)
+        dz, d_gate, d_up, d_sel = _bf16(cap, inter_dim, dev), _bf16(cap, inter_dim, dev), _bf16(cap, inter_dim, dev), _bf16(cap, hid, dev)
+        dob = dobs = dgb = dgbs = down_bt = gu_bt = down_a16 = gu_a16 = None
+        grads = [None, None, None, None]
+        if lora:
+            dob, dobs, dgb, dgbs = (_bf16(cap, ops.LORA_PAD, dev) for _ in range(4))
+            down_bt, gu_bt = down_b.transpose(1, 2).contiguous(), gu_b.transpose(1, 2).contiguous()
+            down_a16, gu_a16 = ops.pad_rank_rows(down_a), ops.pad_rank_rows(gu_a)
+            grads = [torch.empty_like(gu_a), torch.empty_like(gu_b), torch.empty_like(down_a), torch.empty_like(down_b)]
 
         with torch.cuda.stream(xs):
+            xs.wait_event(xchg.ev_ready)
             for c in range(xchg.chunks):
-                xs.wait_event(ev["g_ready"][c])
                 with _Span(xchg, "dispatch_backward", xs):
-                    xchg.scatter(d_rows[c], None, 1, routes[c][0], c, 1)
+                    xchg.scatter(d_rows, None, 1, sorted_e, c, 1)
                     xchg.sync()
                 ev["g_sent"][c].record(xs)
 
-        grads, d_sel = [], []
-        for c in range(xchg.chunks):
+        x, d_out = xchg.recv[0], xchg.recv[1]
+        for c, (lo, hi) in enumerate(xchg.groups):
             cs.wait_event(ev["g_sent"][c])
+            first, end, t, offs = xchg.group_first[c], xchg.group_end[c], tiles[c], plan.local_offsets[lo:hi]
             with _Span(xchg, "experts_backward", cs):
-                g = ag.expert_block_backward(ctx.saved[c], xchg.recv_view(1, c))
+                if lora:
+                    # down projection: dZ = dOut.deq(Wd) + s.(dOut.Bd).Ad ; dAd = s.(dOut.Bd)^T.Z ; dBd = s.dOut^T.(Z.Ad^T)
+                    ops.grouped_lora_down(d_out, None, down_bt, False, scaling, r, t, zero=False, out=(dob, dobs))
+                ops.grouped_dgrad(d_out, None, down_p.reshape(-1), None, quant_type, inter_dim, e_local, t, dobs, down_a16, out=dz)
+                if lora:
+                    ops.grouped_lora_wgrad(dob, z, scaling, r, offs, grads[2][lo:hi], False, 0, first)
+                    ops.grouped_lora_wgrad(za, d_out, scaling, r, offs, grads[3][lo:hi], True, 0, first)
+                ops.swiglu_bwd(gate, up, dz, 0.0, first, end, out=(d_gate, d_up))
+                if lora:
+                    # gate|up: dX = dG.deq(Wg) + dU.deq(Wu) + s.([dG|dU].Bgu).Agu
+                    ops.grouped_lora_down(d_gate, d_up, gu_bt, False, scaling, r, t, zero=False, out=(dgb, dgbs))
+                ops.grouped_dgrad(d_gate, d_up, gate_p.reshape(-1), up_p.reshape(-1), quant_type, hid, e_local, t, dgbs, gu_a16, out=d_sel)
+                if lora:
+                    ops.grouped_lora_wgrad(dgb, x, scaling, r, offs, grads[0][lo:hi], False, 0, first)
+                    ops.grouped_lora_wgrad(xa, d_gate, scaling, r, offs, grads[1][lo:hi], True, 0, first)
+                    ops.grouped_lora_wgrad(xa, d_up, scaling, r, offs, grads[1][lo:hi], True, inter_dim, first)
             ev["g_computed"][c].record(cs)
-            d_sel.append(g[0])
-            grads.append(g[1:])
 
         with torch.cuda.stream(xs):
             for c in range(xchg.chunks):
                 xs.wait_event(ev["g_computed"][c])
                 with _Span(xchg, "return_backward", xs):
-                    xchg.give_back(d_sel[c], c, 1, routes[c][3])
+                    xchg.give_back(d_sel, c, 1)
                     xchg.sync()
                 ev["g_returned"][c].record(xs)
 
-        d_hidden = torch.empty(grad_out.shape[0], xchg.hidden, dtype=torch.bfloat16, device=dev)
-        for c, (t0, t1) in enumerate(bounds):
-            cs.wait_event(ev["g_returned"][c])
-            rows_c = xchg.ret[1][routes[c][3]:routes[c][3] + (t1 - t0) * top_k]
-            with _Span(xchg, "gather_backward", cs):
-                ops.route_gather_bwd(rows_c, routes[c][2], t1 - t0, top_k, out=d_hidden[t0:t1])
-        factor_grads = [None, None, None, None]
-        if ctx.lora:
-            factor_grads = list(grads[0])
-            for more in grads[1:]:
-                factor_grads = [a + b for a, b in zip(factor_grads, more)]
+        cs.wait_event(ev["g_returned"][-1])
+        with _Span(xchg, "gather_backward", cs):
+            d_hidden = ops.route_gather_bwd(xchg.ret[1][:tokens * top_k], inverse, tokens, top_k)
         ctx.saved = None
-        return (None, d_hidden, None, d_weights, None, None, None, None, None, None, *factor_grads)
+        return (None, d_hidden, None, d_weights, None, None, None, None, None, None, *grads)
 
 
 def peer_moe_layer(xchg: PeerExchange, hidden: torch.Tensor, top_k_index: torch.Tensor, top_k_weights: torch.Tensor,

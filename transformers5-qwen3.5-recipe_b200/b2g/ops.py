@@ -468,31 +468,34 @@ def route_combine_bwd(expert_out: torch.Tensor, weights: torch.Tensor, perm: tor
     return d_out, d_w
 
 
-def swiglu_fwd(gate: torch.Tensor, up: torch.Tensor, limit: float = 0.0, live_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``silu(gate) * up`` (clamped when ``limit > 0``).  ``live_rows``: one-element int32 device tensor, the number of
-    leading rows that hold data (the rest is left untouched)."""
+def swiglu_fwd(gate: torch.Tensor, up: torch.Tensor, limit: float = 0.0, row_begin: Optional[torch.Tensor] = None,
+               row_end: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``silu(gate) * up`` (clamped when ``limit > 0``).  ``row_begin`` / ``row_end``: one-element int32 device tensors; only the
+    rows in between are computed (the rest of ``out`` is left untouched)."""
     _need(gate, torch.bfloat16, "gate")
     _need(up, torch.bfloat16, "up")
-    z = torch.empty_like(gate)
+    z = torch.empty_like(gate) if out is None else out
     with _DeviceCtx(gate):
-        _lib.call("b2g_swiglu_fwd", _p(gate), _p(up), _p(z), gate.numel(), float(limit), _p(live_rows), gate.shape[-1], _stream(gate))
+        _lib.call("b2g_swiglu_fwd", _p(gate), _p(up), _p(z), gate.numel(), float(limit), _p(row_begin), _p(row_end), gate.shape[-1], _stream(gate))
     return z
 
 
-def swiglu_bwd(gate: torch.Tensor, up: torch.Tensor, dz: torch.Tensor, limit: float = 0.0, live_rows: Optional[torch.Tensor] = None):
+def swiglu_bwd(gate: torch.Tensor, up: torch.Tensor, dz: torch.Tensor, limit: float = 0.0, row_begin: Optional[torch.Tensor] = None,
+               row_end: Optional[torch.Tensor] = None, out: Optional[tuple[torch.Tensor, torch.Tensor]] = None):
     _need(dz, torch.bfloat16, "dz")
-    dg, du = torch.empty_like(gate), torch.empty_like(up)
+    dg, du = (torch.empty_like(gate), torch.empty_like(up)) if out is None else out
     with _DeviceCtx(gate):
-        _lib.call("b2g_swiglu_bwd", _p(gate), _p(up), _p(dz), _p(dg), _p(du), gate.numel(), float(limit), _p(live_rows), gate.shape[-1],
-                  _stream(gate))
+        _lib.call("b2g_swiglu_bwd", _p(gate), _p(up), _p(dz), _p(dg), _p(du), gate.numel(), float(limit), _p(row_begin), _p(row_end),
+                  gate.shape[-1], _stream(gate))
     return dg, du
 
 
 # --------------------------------------------------------------------------------------
 # grouped (MoE) path
 # --------------------------------------------------------------------------------------
-def grouped_schedule(expert_indices: torch.Tensor, offsets: torch.Tensor, total_rows: int) -> torch.Tensor:
-    """Tile table (int32 scratch) for the active experts ``expert_indices`` with cumulative ends ``offsets``."""
+def grouped_schedule(expert_indices: torch.Tensor, offsets: torch.Tensor, total_rows: int, first_row: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Tile table (int32 scratch) for the active experts ``expert_indices`` with cumulative ends ``offsets``; ``first_row`` (a
+    one-element int32 device tensor) is where the first listed expert's rows begin when that is not row 0."""
     _need(expert_indices, torch.int64, "expert_indices")
     _need(offsets, torch.int32, "expert_offsets")
     g = expert_indices.numel()
@@ -501,13 +504,14 @@ def grouped_schedule(expert_indices: torch.Tensor, offsets: torch.Tensor, total_
     nbytes = _lib.query("b2g_grouped_tiles_bytes", total_rows, g)
     tiles = torch.empty(nbytes // 4, dtype=torch.int32, device=offsets.device)
     with _DeviceCtx(offsets):
-        _lib.call("b2g_grouped_schedule", _p(expert_indices), _p(offsets), g, total_rows, _p(tiles), _p(status_word(offsets.device)),
-                  _stream(offsets))
+        _lib.call("b2g_grouped_schedule", _p(expert_indices), _p(offsets), _p(first_row), g, total_rows, _p(tiles),
+                  _p(status_word(offsets.device)), _stream(offsets))
     return tiles
 
 
 def grouped_fwd(x: torch.Tensor, payload0: torch.Tensor, payload1: Optional[torch.Tensor], qtype: int, n: int, num_experts: int,
-                tiles: torch.Tensor, xas: Optional[torch.Tensor] = None, lora_b16: Optional[torch.Tensor] = None):
+                tiles: torch.Tensor, xas: Optional[torch.Tensor] = None, lora_b16: Optional[torch.Tensor] = None,
+                out0: Optional[torch.Tensor] = None, out1: Optional[torch.Tensor] = None):
     """Grouped Y = X . deq(W_e)^T for one payload, or (Y0, Y1) for two.  ``lora_b16`` is [E, rows, 16]
     with rows = n (single) or 2n (pair: first n rows for Y0, next n for Y1)."""
     _need(x, torch.bfloat16, "x")
@@ -523,8 +527,11 @@ def grouped_fwd(x: torch.Tensor, payload0: torch.Tensor, payload1: Optional[torc
         if tuple(xas.shape) != (r, LORA_PAD) or lora_b16.shape[0] != num_experts or lora_b16.shape[2] != LORA_PAD \
                 or lora_rows != n * (2 if payload1 is not None else 1):
             raise ValueError("bad LoRA operand shapes for the grouped forward")
-    y0 = torch.empty(r, n, dtype=torch.bfloat16, device=x.device)
-    y1 = torch.empty(r, n, dtype=torch.bfloat16, device=x.device) if payload1 is not None else None
+    y0 = torch.empty(r, n, dtype=torch.bfloat16, device=x.device) if out0 is None else out0
+    y1 = (torch.empty(r, n, dtype=torch.bfloat16, device=x.device) if out1 is None else out1) if payload1 is not None else None
+    for t in (y0, y1):
+        if t is not None and (t.dtype != torch.bfloat16 or tuple(t.shape) != (r, n) or not t.is_contiguous()):
+            raise ValueError("grouped_fwd: an output buffer must be a contiguous bf16 [rows, n] tensor")
     payload0, qarg = _tma_payload(payload0, qtype, num_experts * n, k)
     if payload1 is not None:
         payload1, _ = _tma_payload(payload1, qtype, num_experts * n, k)
@@ -536,7 +543,7 @@ def grouped_fwd(x: torch.Tensor, payload0: torch.Tensor, payload1: Optional[torc
 
 def grouped_dgrad(dy0: torch.Tensor, dy1: Optional[torch.Tensor], payload0: torch.Tensor, payload1: Optional[torch.Tensor],
                   qtype: int, k: int, num_experts: int, tiles: torch.Tensor, dybs: Optional[torch.Tensor] = None,
-                  lora_a16: Optional[torch.Tensor] = None) -> torch.Tensor:
+                  lora_a16: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     _need(dy0, torch.bfloat16, "dy")
     r, n = dy0.shape
     _check_payload(payload0, qtype, num_experts * n, k, "payload")
@@ -548,7 +555,9 @@ def grouped_dgrad(dy0: torch.Tensor, dy1: Optional[torch.Tensor], payload0: torc
         _need(lora_a16, torch.bfloat16, "lora_a16")
         if tuple(dybs.shape) != (r, LORA_PAD) or tuple(lora_a16.shape) != (num_experts, LORA_PAD, k):
             raise ValueError("bad LoRA operand shapes for the grouped input gradient")
-    dx = torch.empty(r, k, dtype=torch.bfloat16, device=dy0.device)
+    dx = torch.empty(r, k, dtype=torch.bfloat16, device=dy0.device) if out is None else out
+    if dx.dtype != torch.bfloat16 or tuple(dx.shape) != (r, k) or not dx.is_contiguous():
+        raise ValueError("grouped_dgrad: the output buffer must be a contiguous bf16 [rows, k] tensor")
     payload0, qarg = _tma_payload(payload0, qtype, num_experts * n, k)
     if payload1 is not None:
         payload1, _ = _tma_payload(payload1, qtype, num_experts * n, k)
@@ -559,7 +568,8 @@ def grouped_dgrad(dy0: torch.Tensor, dy1: Optional[torch.Tensor], payload0: torc
 
 
 def grouped_lora_down(x: torch.Tensor, x1: Optional[torch.Tensor], w: torch.Tensor, w_is_cr: bool, scale: float, r: int,
-                      tiles: torch.Tensor, plain: bool = True, scaled: bool = True, zero: bool = True):
+                      tiles: torch.Tensor, plain: bool = True, scaled: bool = True, zero: bool = True,
+                      out: Optional[tuple[Optional[torch.Tensor], Optional[torch.Tensor]]] = None):
     """Per-expert projection onto the rank.  ``w`` is [E, r, C] or (w_is_cr) [E, C(or 2C), r].
     The kernel writes only rows that belong to a tile of the table, so the outputs start zeroed unless the caller says that
     nobody reads the other rows (``zero=False``: the fused expert block, whose consumers walk the same table)."""
@@ -568,8 +578,11 @@ def grouped_lora_down(x: torch.Tensor, x1: Optional[torch.Tensor], w: torch.Tens
     rows, c = x.shape
     e = w.shape[0]
     make = torch.zeros if zero else torch.empty
-    o_plain = make(rows, LORA_PAD, dtype=torch.bfloat16, device=x.device) if plain else None
-    o_scaled = make(rows, LORA_PAD, dtype=torch.bfloat16, device=x.device) if scaled else None
+    if out is not None:
+        o_plain, o_scaled = out
+    else:
+        o_plain = make(rows, LORA_PAD, dtype=torch.bfloat16, device=x.device) if plain else None
+        o_scaled = make(rows, LORA_PAD, dtype=torch.bfloat16, device=x.device) if scaled else None
     with _DeviceCtx(x):
         _lib.call("b2g_grouped_lora_down", _p(x), _p(x1), _p(w), int(w_is_cr), float(scale), _p(tiles), _p(o_plain), _p(o_scaled),
                   rows, c, int(r), int(e), _stream(x))
@@ -577,7 +590,7 @@ def grouped_lora_down(x: torch.Tensor, x1: Optional[torch.Tensor], w: torch.Tens
 
 
 def grouped_lora_wgrad(s16: torch.Tensor, t: torch.Tensor, scale: float, r: int, offsets_full: torch.Tensor, out: torch.Tensor,
-                       transpose_out: bool, out_col_offset: int = 0) -> torch.Tensor:
+                       transpose_out: bool, out_col_offset: int = 0, first_row: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Per-expert factor gradient into ``out`` ([E, r, Ctot] or, transposed, [E, Ctot, r])."""
     _need(s16, torch.bfloat16, "s")
     _need(t, torch.bfloat16, "t")
@@ -587,7 +600,7 @@ def grouped_lora_wgrad(s16: torch.Tensor, t: torch.Tensor, scale: float, r: int,
     e = offsets_full.numel()
     ctot = out.shape[1] if transpose_out else out.shape[2]
     with _DeviceCtx(t):
-        _lib.call("b2g_grouped_lora_wgrad", _p(s16), _p(t), float(scale), _p(offsets_full), _p(out), int(transpose_out), rows, c,
+        _lib.call("b2g_grouped_lora_wgrad", _p(s16), _p(t), float(scale), _p(offsets_full), _p(first_row), _p(out), int(transpose_out), rows, c,
                   int(r), int(e), int(out_col_offset), int(ctot), _stream(t))
     return out
 

@@ -3,6 +3,9 @@
 #include "b2g_common.cuh"
 
 #include <mutex>
+#include <unordered_map>
+
+#include <mutex>
 
 namespace b2g {
 
@@ -36,8 +39,53 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// Encoded tensor maps are kept per (base address, geometry): a training step presents the same tensors at the same addresses
+// again and again (frozen payloads always, activations as often as the caching allocator returns the same block), and a map
+// depends on nothing else.  The table is bounded; when it is full it is emptied and refills.
+namespace {
+struct TmapKey {
+  const void* base; uint64_t inner, rows, pitch; uint32_t box_inner, box_rows; int dt, sw, dev;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && inner == o.inner && rows == o.rows && pitch == o.pitch && box_inner == o.box_inner && box_rows == o.box_rows &&
+           dt == o.dt && sw == o.sw && dev == o.dev;
+  }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    uint64_t h = reinterpret_cast<uintptr_t>(k.base) * 0x9E3779B97F4A7C15ull;
+    for (uint64_t v : {k.inner, k.rows, k.pitch, (uint64_t)k.box_inner << 32 | k.box_rows, (uint64_t)k.dt << 40 | (uint64_t)k.sw << 20 | (uint64_t)k.dev})
+      h = (h ^ v) * 0x100000001B3ull;
+    return static_cast<size_t>(h ^ (h >> 29));
+  }
+};
+std::mutex g_tmap_mu;
+std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> g_tmaps;
+constexpr size_t kTmapCacheEntries = 8192;
+}  // namespace
+
+static int encode_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t inner, uint64_t rows,
+                          uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle sw);
+
 int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t inner,
                  uint64_t rows, uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle sw) {
+  int dev = 0;
+  B2G_CUDA_OK(cudaGetDevice(&dev));
+  const TmapKey key{base, inner, rows, pitch_bytes, box_inner, box_rows, (int)dt, (int)sw, dev};
+  {
+    std::lock_guard<std::mutex> lock(g_tmap_mu);
+    auto it = g_tmaps.find(key);
+    if (it != g_tmaps.end()) { *out = it->second; return 0; }
+  }
+  int rc = encode_tmap_2d(out, base, dt, elem_bytes, inner, rows, pitch_bytes, box_inner, box_rows, sw);
+  if (rc) return rc;
+  std::lock_guard<std::mutex> lock(g_tmap_mu);
+  if (g_tmaps.size() >= kTmapCacheEntries) g_tmaps.clear();
+  g_tmaps.emplace(key, *out);
+  return 0;
+}
+
+static int encode_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t inner, uint64_t rows,
+                          uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle sw) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return fail(B2G_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   if (!aligned16(base)) return fail(B2G_E_ARG, "tensor base %p is not 16-byte aligned", base);

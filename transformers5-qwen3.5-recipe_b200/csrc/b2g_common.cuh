@@ -12,6 +12,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -47,6 +48,33 @@ inline int fail(int code, const char* fmt, ...) {
   } while (0)
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// Per-kernel function attributes, set once per kernel and device instead of before every launch.
+//   B2G_KERNEL_SMEM(kernel, bytes): opt in to `bytes` of dynamic shared memory.
+//   B2G_KERNEL_MAX_SHARED(kernel) : ask for the largest shared-memory partition of the SM.  The split between L1 and shared
+//     memory is an SM-wide setting that cannot change while any CTA is resident; every kernel of this library asks for the same
+//     (largest) partition, so that the GEMM, which needs nearly all of it, can start on an SM where a small copy or element-wise
+//     kernel of another stream is still resident.  None of these kernels relies on the L1 (they stream).
+inline bool first_use_on_device(std::atomic<uint64_t>& seen) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
+  const uint64_t bit = 1ull << dev;
+  return (seen.fetch_or(bit, std::memory_order_acq_rel) & bit) == 0;
+}
+#define B2G_KERNEL_SMEM(kernel, bytes)                                                                              \
+  do {                                                                                                              \
+    static std::atomic<uint64_t> seen_{0};                                                                          \
+    if (::b2g::first_use_on_device(seen_)) {                                                                        \
+      B2G_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(bytes)));         \
+      B2G_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared)); \
+    }                                                                                                               \
+  } while (0)
+#define B2G_KERNEL_MAX_SHARED(kernel)                                                                               \
+  do {                                                                                                              \
+    static std::atomic<uint64_t> seen_{0};                                                                          \
+    if (::b2g::first_use_on_device(seen_))                                                                          \
+      B2G_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared)); \
+  } while (0)
 
 // Number of SMs of the current device (cached per device id).
 int sm_count();

@@ -3,6 +3,8 @@
 // Every rank maps the receive buffers of all ranks (NVLink peer pointers of a symmetric allocation).
 //   scatter: for each routed row, sorted by global expert id on the SOURCE rank, copy the token's row straight
 //            into the OWNER rank's receive buffer, at the slot that groups rows by (local expert, source rank).
+//            One launch moves one EXPERT GROUP (a range of local expert indices, the same on every owner), so that
+//            the experts of one group can compute while the next group's rows are still crossing NVLink.
 //            With `perm` the source row is gathered from the token matrix on the fly (dispatch of activations);
 //            without it rows are taken in order (dispatch of output gradients).
 //   return : the inverse on the OWNER rank: each row of the grouped buffer goes back to its source rank, to the
@@ -11,10 +13,13 @@
 // stores only: no multicast, no waits inside the kernels (ranks synchronise between the two phases on the
 // stream, outside these kernels).
 //
-// The two copy kernels are built to run BESIDE the quantized GEMM on the same SMs: 128 threads of at most 48
-// registers and no shared memory fit next to the GEMM's 736-thread CTA (which leaves about 6.6 K registers
-// and 25 KB of shared memory per SM), so an exchange of one token chunk on its own stream proceeds while the
-// expert products of another chunk compute.
+// The two copy kernels are built to run BESIDE the quantized GEMM on the same SMs, so that an exchange of one
+// token chunk on its own stream proceeds while the expert products of another chunk compute.  The GEMM's CTA
+// (23 warps of 80 registers) takes six warps' worth of registers in three of the SM's four register files and
+// five in the fourth, which leaves 1024 registers in each of the three: room for exactly one warp of 32
+// registers per file.  Hence 128 threads (one warp per file), at most 32 registers, no shared memory, one CTA
+// per SM, and the largest shared-memory partition requested so that the SM need not be re-partitioned (which
+// it cannot be while a CTA is resident) when the GEMM moves in.
 //
 // A receive buffer that is too small is CONTAINED, not only reported: the plan kernel clamps every segment
 // of the rows this rank receives to the buffer's capacity (and sets status 901), so that the grouped
@@ -25,77 +30,70 @@
 namespace b2g {
 namespace ep {
 
-__global__ void __launch_bounds__(128, 10) scatter_rows_kernel(const uint4* __restrict__ src, const int64_t* __restrict__ perm, int top_k,
-                                                           const int64_t* __restrict__ sorted_expert, const int32_t* __restrict__ my_start,
-                                                           const int32_t* __restrict__ dest_base, const unsigned long long* __restrict__ peers,
-                                                           int experts_per_rank, int64_t R, int vec_per_row, int64_t capacity, int* status,
-                                                           int first_expert) {
+// One warp copies one row: four 16-byte vectors per lane in flight (the register budget of 32 allows no more).
+__device__ __forceinline__ void copy_row(const uint4* __restrict__ in, uint4* __restrict__ out, int vec_per_row, int lane) {
+  for (int v0 = lane; v0 < vec_per_row; v0 += 128) {
+    uint4 buf[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (v0 + 32 * i < vec_per_row) buf[i] = __ldcs(in + v0 + 32 * i);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (v0 + 32 * i < vec_per_row) out[v0 + 32 * i] = buf[i];
+  }
+}
+
+// Scatter of the rows whose LOCAL expert index (global id modulo experts_per_rank) lies in [group_lo, group_hi): one expert group
+// of every owner.  Rows are sorted by global expert id, so the group is one contiguous range of sorted positions per owner;
+// the owners are visited one after the other, starting with the rank after this one, so that the ranks of a job do not all
+// store to the same GPU at the same time (one NVLink port would take everything while the others idle).
+__global__ void __launch_bounds__(128, 16) scatter_rows_kernel(const uint4* __restrict__ src, const int64_t* __restrict__ perm, int top_k,
+                                                               const int64_t* __restrict__ sorted_expert, const int32_t* __restrict__ my_start,
+                                                               const int32_t* __restrict__ dest_base, const unsigned long long* __restrict__ peers,
+                                                               int experts_per_rank, int world, int rank, int group_lo, int group_hi, int64_t R,
+                                                               int vec_per_row, int64_t capacity, int* status) {
   const int lane = threadIdx.x & 31;
   const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-  // Rows are sorted by expert, hence by owner rank.  Walking them from row 0 on every rank would aim all ranks at the
-  // same owner at the same time (one NVLink port takes everything while the others idle), so each rank starts at the
-  // first row of a different owner's experts and wraps around.
-  const int64_t start = my_start[first_expert];
-  for (int64_t s0 = warp; s0 < R; s0 += nwarps) {
-    const int64_t s = s0 + start < R ? s0 + start : s0 + start - R;
-    const int e = static_cast<int>(sorted_expert[s]);
-    const int owner = e / experts_per_rank;
-    const int64_t slot = static_cast<int64_t>(dest_base[e]) + (s - my_start[e]);
-    if (slot >= capacity) {
-      if (lane == 0 && status) atomicCAS(status, 0, 901);   // receive buffer too small: report, never write past it
-      continue;
-    }
-    const int64_t from = perm ? perm[s] / top_k : s;
-    const uint4* in = src + from * vec_per_row;
-    uint4* out = reinterpret_cast<uint4*>(peers[owner]) + slot * vec_per_row;
-    for (int v0 = 0; v0 < vec_per_row; v0 += 256) {
-      uint4 buf[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int v = v0 + lane + 32 * i;
-        if (v < vec_per_row) buf[i] = in[v];
+  for (int step = 1; step <= world; ++step) {
+    const int owner = (rank + step) % world;
+    const int e_first = owner * experts_per_rank + group_lo, e_end = owner * experts_per_rank + group_hi;
+    const int64_t s_begin = my_start[e_first];
+    const int64_t s_end = e_end < world * experts_per_rank ? static_cast<int64_t>(my_start[e_end]) : R;
+    uint4* const base = reinterpret_cast<uint4*>(peers[owner]);
+    for (int64_t s = s_begin + warp; s < s_end; s += nwarps) {
+      const int e = static_cast<int>(sorted_expert[s]);
+      const int64_t slot = static_cast<int64_t>(dest_base[e]) + (s - my_start[e]);
+      if (slot >= capacity) {
+        if (lane == 0 && status) atomicCAS(status, 0, 901);   // receive buffer too small: report, never write past it
+        continue;
       }
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int v = v0 + lane + 32 * i;
-        if (v < vec_per_row) out[v] = buf[i];
-      }
+      const int64_t from = perm ? perm[s] / top_k : s;
+      copy_row(src + from * vec_per_row, base + slot * vec_per_row, vec_per_row, lane);
     }
   }
 }
 
-__global__ void __launch_bounds__(128, 10) return_rows_kernel(const uint4* __restrict__ rows, const int32_t* __restrict__ blk_start,
-                                                          const int32_t* __restrict__ src_pos, const unsigned long long* __restrict__ peers,
-                                                          int world, int num_blocks, int vec_per_row, int64_t capacity) {
+// The inverse on the owner: the rows of the blocks [block_lo, block_hi) (block b = local expert b / world, source rank b % world;
+// an expert group is a contiguous range of blocks and of rows) go back to their sources.
+__global__ void __launch_bounds__(128, 16) return_rows_kernel(const uint4* __restrict__ rows, const int32_t* __restrict__ blk_start,
+                                                              const int32_t* __restrict__ src_pos, const unsigned long long* __restrict__ peers,
+                                                              int world, int block_lo, int block_hi, int vec_per_row, int64_t capacity) {
   const int lane = threadIdx.x & 31;
   const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-  const int64_t total = blk_start[num_blocks];
+  const int64_t first = blk_start[block_lo];
+  const int64_t total = blk_start[block_hi];
   const int64_t live = total < capacity ? total : capacity;
-  for (int64_t j = warp; j < live; j += nwarps) {
-    // block (local expert, source rank) that holds row j: last b with blk_start[b] <= j
-    int lo = 0, hi = num_blocks - 1;
+  for (int64_t j = first + warp; j < live; j += nwarps) {
+    // block (local expert, source rank) that holds row j: last b in the range with blk_start[b] <= j
+    int lo = block_lo, hi = block_hi - 1;
     while (lo < hi) {
       const int mid = (lo + hi + 1) >> 1;
       if (blk_start[mid] <= j) lo = mid; else hi = mid - 1;
     }
     const int64_t pos = static_cast<int64_t>(src_pos[lo]) + (j - blk_start[lo]);
-    const uint4* in = rows + j * vec_per_row;
-    uint4* out = reinterpret_cast<uint4*>(peers[lo % world]) + pos * vec_per_row;
-    for (int v0 = 0; v0 < vec_per_row; v0 += 256) {
-      uint4 buf[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int v = v0 + lane + 32 * i;
-        if (v < vec_per_row) buf[i] = in[v];
-      }
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int v = v0 + lane + 32 * i;
-        if (v < vec_per_row) out[v] = buf[i];
-      }
-    }
+    copy_row(rows + j * vec_per_row, reinterpret_cast<uint4*>(peers[lo % world]) + pos * vec_per_row, vec_per_row, lane);
   }
 }
 
@@ -171,32 +169,43 @@ __global__ void __launch_bounds__(256) peer_plan_kernel(const int32_t* __restric
 using namespace b2g;
 
 extern "C" int b2g_ep_scatter_rows(const void* src, const int64_t* perm, int top_k, const int64_t* sorted_expert, const int32_t* my_start,
-                                   const int32_t* dest_base, const uint64_t* peer_ptrs, int experts_per_rank, int64_t R, int H,
-                                   int64_t capacity_rows, int first_expert, int* status, void* stream) {
+                                   const int32_t* dest_base, const uint64_t* peer_ptrs, int experts_per_rank, int world, int rank,
+                                   int group_lo, int group_hi, int64_t R, int H, int64_t capacity_rows, int ctas_per_sm, int* status,
+                                   void* stream) {
   B2G_REQUIRE(H > 0 && H % 8 == 0, "ep_scatter_rows: row width %d must be a positive multiple of 8", H);
   B2G_REQUIRE(experts_per_rank >= 1 && capacity_rows >= 0 && R >= 0, "ep_scatter_rows: bad sizes");
+  B2G_REQUIRE(world >= 1 && rank >= 0 && rank < world, "ep_scatter_rows: rank %d of %d", rank, world);
+  B2G_REQUIRE(group_lo >= 0 && group_lo < group_hi && group_hi <= experts_per_rank, "ep_scatter_rows: expert group [%d, %d) outside 0..%d",
+              group_lo, group_hi, experts_per_rank);
   B2G_REQUIRE(perm == nullptr || top_k >= 1, "ep_scatter_rows: top_k must be positive when rows are gathered");
-  B2G_REQUIRE(first_expert >= 0, "ep_scatter_rows: first_expert %d is negative", first_expert);
   if (R == 0) return 0;
   B2G_REQUIRE(src && sorted_expert && my_start && dest_base && peer_ptrs && aligned16(src), "ep_scatter_rows: null or misaligned pointer");
-  const int64_t want = (R + 3) / 4, cap = (int64_t)sm_count() * 8;
+  B2G_REQUIRE(ctas_per_sm >= 1 && ctas_per_sm <= 16, "ep_scatter_rows: ctas_per_sm %d outside 1..16", ctas_per_sm);
+  // ctas_per_sm = 1 for an exchange that runs beside expert products: one CTA of this kernel fits next to the GEMM's CTA, two
+  // do not leave the GEMM room, and a kernel that finds the SMs idle would otherwise fill them and hold the next GEMM launch
+  // back until the whole exchange is done.  More CTAs per SM (more rows in flight) for an exchange that nothing waits beside.
+  const int64_t want = (R + 3) / 4, cap = (int64_t)sm_count() * ctas_per_sm;
+  B2G_KERNEL_MAX_SHARED(ep::scatter_rows_kernel);
   ep::scatter_rows_kernel<<<(int)(want < cap ? want : cap), 128, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(src), perm, top_k, sorted_expert, my_start, dest_base, reinterpret_cast<const unsigned long long*>(peer_ptrs),
-      experts_per_rank, R, H / 8, capacity_rows, status, first_expert);
+      experts_per_rank, world, rank, group_lo, group_hi, R, H / 8, capacity_rows, status);
   B2G_CUDA_OK(cudaGetLastError());
   return 0;
 }
 
 extern "C" int b2g_ep_return_rows(const void* rows, const int32_t* blk_start, const int32_t* src_pos, const uint64_t* peer_ptrs, int world,
-                                  int num_blocks, int H, int64_t capacity_rows, void* stream) {
+                                  int block_lo, int block_hi, int H, int64_t capacity_rows, int ctas_per_sm, void* stream) {
   B2G_REQUIRE(H > 0 && H % 8 == 0, "ep_return_rows: row width %d must be a positive multiple of 8", H);
-  B2G_REQUIRE(world >= 1 && num_blocks >= 1 && num_blocks % world == 0, "ep_return_rows: %d blocks do not split over %d ranks", num_blocks, world);
+  B2G_REQUIRE(world >= 1 && block_lo >= 0 && block_lo < block_hi && block_lo % world == 0 && block_hi % world == 0,
+              "ep_return_rows: blocks [%d, %d) are not whole experts of %d ranks", block_lo, block_hi, world);
   if (capacity_rows == 0) return 0;
   B2G_REQUIRE(rows && blk_start && src_pos && peer_ptrs && aligned16(rows), "ep_return_rows: null or misaligned pointer");
-  const int64_t want = (capacity_rows + 3) / 4, cap = (int64_t)sm_count() * 8;
+  B2G_REQUIRE(ctas_per_sm >= 1 && ctas_per_sm <= 16, "ep_return_rows: ctas_per_sm %d outside 1..16", ctas_per_sm);
+  const int64_t want = (capacity_rows + 3) / 4, cap = (int64_t)sm_count() * ctas_per_sm;      // as in the scatter
+  B2G_KERNEL_MAX_SHARED(ep::return_rows_kernel);
   ep::return_rows_kernel<<<(int)(want < cap ? want : cap), 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(rows), blk_start, src_pos, reinterpret_cast<const unsigned long long*>(peer_ptrs), world, num_blocks, H / 8,
-      capacity_rows);
+      static_cast<const uint4*>(rows), blk_start, src_pos, reinterpret_cast<const unsigned long long*>(peer_ptrs), world, block_lo, block_hi,
+      H / 8, capacity_rows);
   B2G_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -210,6 +219,7 @@ extern "C" int b2g_ep_peer_plan(const int32_t* counts, int64_t count_stride, int
   B2G_REQUIRE(rank >= 0 && rank < world, "ep_peer_plan: rank %d of %d", rank, world);
   B2G_REQUIRE(counts && my_start && dest_base && blk_start && src_pos && local_sizes && local_offsets, "ep_peer_plan: null pointer");
   B2G_REQUIRE(count_stride >= num_experts && capacity_rows >= 0 && capacity_rows < (1ll << 31), "ep_peer_plan: bad count stride or capacity");
+  B2G_KERNEL_MAX_SHARED(ep::peer_plan_kernel);
   ep::peer_plan_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(counts, count_stride, world, num_experts, rank, my_start, dest_base,
                                                                          blk_start, src_pos, local_sizes, local_offsets, capacity_rows, status);
   B2G_CUDA_OK(cudaGetLastError());

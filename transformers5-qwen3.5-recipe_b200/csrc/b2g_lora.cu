@@ -211,7 +211,8 @@ template <bool kPartial>
 __global__ void __launch_bounds__(128) lora_wgrad_kernel(const __nv_bfloat16* __restrict__ s, const __nv_bfloat16* __restrict__ t, float scale,
                                                          const int32_t* __restrict__ offsets, int64_t m_total, int rows_per_split,
                                                          int C, int r, float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
-                                                         int transpose_out, int64_t out_col_offset, int64_t out_cols_total) {
+                                                         int transpose_out, int64_t out_col_offset, int64_t out_cols_total,
+                                                         const int32_t* __restrict__ first_row) {
   extern __shared__ __align__(16) uint8_t sm[];
   const uint32_t sbase = dev::smem_u32(sm);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -224,7 +225,7 @@ __global__ void __launch_bounds__(128) lora_wgrad_kernel(const __nv_bfloat16* __
     if (rows < 0) rows = 0;
   } else {
     // offsets that overrun the operand (a receive buffer that was too small) are clamped to it
-    row0 = segi > 0 ? offsets[segi - 1] : 0;
+    row0 = segi > 0 ? offsets[segi - 1] : (first_row ? *first_row : 0);
     int64_t end = offsets[segi];
     if (row0 > m_total) row0 = m_total;
     if (end > m_total) end = m_total;
@@ -403,10 +404,10 @@ static int lora_down_launch(const void* x, const void* x1, const void* w, int w_
   auto* os = static_cast<__nv_bfloat16*>(out_scaled);
   auto* tl = reinterpret_cast<const int4*>(tiles);
   if (w_is_cr) {
-    B2G_CUDA_OK(cudaFuncSetAttribute(lora::lora_down_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    B2G_KERNEL_SMEM(lora::lora_down_kernel<true>, smem);
     lora::lora_down_kernel<true><<<grid, 128, smem, s>>>(xb, x1b, wb, scale, tl, op, os, M, (int)C, r, dense_rows);
   } else {
-    B2G_CUDA_OK(cudaFuncSetAttribute(lora::lora_down_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    B2G_KERNEL_SMEM(lora::lora_down_kernel<false>, smem);
     lora::lora_down_kernel<false><<<grid, 128, smem, s>>>(xb, x1b, wb, scale, tl, op, os, M, (int)C, r, dense_rows);
   }
   B2G_CUDA_OK(cudaGetLastError());
@@ -443,10 +444,11 @@ extern "C" int b2g_lora_wgrad(const void* s, const void* t, float scale, void* o
   const int chunks = (int)((C + lora::kWgCols - 1) / lora::kWgCols);
   const size_t smem = (size_t)lora::kWgStages * lora::kWgStageBytes;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  B2G_CUDA_OK(cudaFuncSetAttribute(lora::lora_wgrad_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  B2G_KERNEL_SMEM(lora::lora_wgrad_kernel<true>, smem);
+  B2G_KERNEL_MAX_SHARED(lora::lora_wgrad_reduce_kernel);
   lora::lora_wgrad_kernel<true><<<dim3(chunks, splits), 128, smem, st>>>(
       static_cast<const __nv_bfloat16*>(s), static_cast<const __nv_bfloat16*>(t), scale, nullptr, M, rows_per_split, (int)C, r,
-      static_cast<float*>(workspace), nullptr, 0, 0, 0);
+      static_cast<float*>(workspace), nullptr, 0, 0, 0, nullptr);
   B2G_CUDA_OK(cudaGetLastError());
   const int64_t n = (int64_t)r * C;
   lora::lora_wgrad_reduce_kernel<<<(int)((n + 63) / 64), 64, 0, st>>>(static_cast<const float*>(workspace), splits, (int)C, r, scale,
@@ -455,9 +457,9 @@ extern "C" int b2g_lora_wgrad(const void* s, const void* t, float scale, void* o
   return 0;
 }
 
-extern "C" int b2g_grouped_lora_wgrad(const void* s, const void* t, float scale, const int32_t* offsets_full, void* out, int transpose_out,
-                                      int64_t R, int64_t C, int r, int num_experts, int64_t out_col_offset, int64_t out_cols_total,
-                                      void* stream) {
+extern "C" int b2g_grouped_lora_wgrad(const void* s, const void* t, float scale, const int32_t* offsets_full, const int32_t* first_row,
+                                      void* out, int transpose_out, int64_t R, int64_t C, int r, int num_experts, int64_t out_col_offset,
+                                      int64_t out_cols_total, void* stream) {
   B2G_REQUIRE(r >= 1 && r <= lora::kRankPad, "grouped_lora_wgrad: rank %d outside 1..16", r);
   B2G_REQUIRE(C > 0 && C % 8 == 0 && R >= 0, "grouped_lora_wgrad: bad shape");
   B2G_REQUIRE(num_experts >= 1 && num_experts <= 65535, "grouped_lora_wgrad: bad expert count %d", num_experts);
@@ -467,10 +469,10 @@ extern "C" int b2g_grouped_lora_wgrad(const void* s, const void* t, float scale,
   const int chunks = (int)((C + lora::kWgCols - 1) / lora::kWgCols);
   const size_t smem = (size_t)lora::kWgStages * lora::kWgStageBytes;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  B2G_CUDA_OK(cudaFuncSetAttribute(lora::lora_wgrad_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  B2G_KERNEL_SMEM(lora::lora_wgrad_kernel<false>, smem);
   lora::lora_wgrad_kernel<false><<<dim3(chunks, num_experts), 128, smem, st>>>(
       static_cast<const __nv_bfloat16*>(s), static_cast<const __nv_bfloat16*>(t), scale, offsets_full, R, 0, (int)C, r, nullptr,
-      static_cast<__nv_bfloat16*>(out), transpose_out, out_col_offset, out_cols_total);
+      static_cast<__nv_bfloat16*>(out), transpose_out, out_col_offset, out_cols_total, first_row);
   B2G_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -978,7 +978,7 @@ int launch_impl(const Launch& L) {
   // entry point and fails with CUDA_ERROR_INVALID_CONTEXT on a thread that has made no runtime call yet (an autograd
   // worker whose first CUDA work is this launch).
   auto kern = qgemm_kernel<QT, MODE>;
-  B2G_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+  B2G_KERNEL_SMEM(kern, C::kSmemBytes);
   CUtensorMap tm_a0, tm_a1, tm_w0, tm_w1, tm_la, tm_lb;
   int rc;
   const uint64_t a_pitch = (uint64_t)(L.lda ? L.lda : red_cols) * 2;
@@ -1062,8 +1062,8 @@ int check_common(const Launch& L, const char* what) {
 // caller whose offsets overrun the activation matrix (an expert-parallel receive buffer that was too small) gets tiles that
 // stay inside it; status 904 reports the overrun.
 __global__ void __launch_bounds__(256) schedule_kernel(const int64_t* __restrict__ expert_indices, const int32_t* __restrict__ offsets,
-                                                       int G, int rows_per_tile, int total_rows, int max_tiles, int4* __restrict__ tiles,
-                                                       int* __restrict__ status) {
+                                                       const int32_t* __restrict__ first_row, int G, int rows_per_tile, int total_rows,
+                                                       int max_tiles, int4* __restrict__ tiles, int* __restrict__ status) {
   __shared__ int scan[256];
   __shared__ int carry;
   if (threadIdx.x == 0) carry = 0;
@@ -1072,7 +1072,7 @@ __global__ void __launch_bounds__(256) schedule_kernel(const int64_t* __restrict
     const int g = g0 + threadIdx.x;
     int begin = 0, rows = 0;
     if (g < G) {
-      begin = g > 0 ? offsets[g - 1] : 0;
+      begin = g > 0 ? offsets[g - 1] : (first_row ? *first_row : 0);
       int end = offsets[g];
       if (end > total_rows || begin > total_rows) {
         if (status) atomicCAS(status, 0, 904);
@@ -1142,13 +1142,15 @@ static int64_t grouped_max_tiles(int64_t R, int G) { return R / qg::kTileRows + 
 
 extern "C" int64_t b2g_grouped_tiles_bytes(int64_t R, int G) { return (1 + grouped_max_tiles(R, G)) * (int64_t)sizeof(int4); }
 
-extern "C" int b2g_grouped_schedule(const int64_t* expert_indices, const int32_t* offsets, int G, int64_t R, int32_t* tiles,
-                                    int* status, void* stream) {
+extern "C" int b2g_grouped_schedule(const int64_t* expert_indices, const int32_t* offsets, const int32_t* first_row, int G, int64_t R,
+                                    int32_t* tiles, int* status, void* stream) {
   B2G_REQUIRE(G >= 0 && R >= 0 && R < (1ll << 31) && tiles, "bad arguments");
   B2G_REQUIRE(aligned16(tiles), "tile table must be 16-byte aligned");
   B2G_REQUIRE(G == 0 || (expert_indices && offsets), "null pointer");
-  qg::schedule_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(expert_indices, offsets, G, qg::kTileRows, (int)R,
-                                                                       (int)grouped_max_tiles(R, G), reinterpret_cast<int4*>(tiles), status);
+  B2G_KERNEL_MAX_SHARED(qg::schedule_kernel);
+  qg::schedule_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(expert_indices, offsets, first_row, G, qg::kTileRows,
+                                                                       (int)R, (int)grouped_max_tiles(R, G),
+                                                                       reinterpret_cast<int4*>(tiles), status);
   B2G_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -315,19 +315,23 @@ __global__ void __launch_bounds__(256) combine_bwd_kernel(const uint4* __restric
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
 
-// `live_rows` (nullable): device count of the rows that hold data, of `pairs_per_row` bf16 pairs each; the rest of the
-// tensors (the unused tail of an expert-parallel receive buffer) is neither read nor written.
-__device__ __forceinline__ int64_t live_pairs(int64_t npairs, const int32_t* live_rows, int64_t pairs_per_row) {
-  if (!live_rows) return npairs;
-  const int64_t n = static_cast<int64_t>(*live_rows) * pairs_per_row;
-  return n < npairs ? (n > 0 ? n : 0) : npairs;
+// `row_begin` / `row_end` (device, nullable): the rows [*row_begin, *row_end) of `pairs_per_row` bf16 pairs each are the only
+// ones that hold data (one expert group inside an expert-parallel receive buffer); nothing else is read or written.
+__device__ __forceinline__ void live_pairs(int64_t npairs, const int32_t* row_begin, const int32_t* row_end, int64_t pairs_per_row,
+                                           int64_t& first, int64_t& last) {
+  first = row_begin ? static_cast<int64_t>(*row_begin) * pairs_per_row : 0;
+  last = row_end ? static_cast<int64_t>(*row_end) * pairs_per_row : npairs;
+  if (first < 0) first = 0;
+  if (last > npairs) last = npairs;
 }
 
 __global__ void __launch_bounds__(256) swiglu_fwd_kernel(const uint32_t* __restrict__ gate, const uint32_t* __restrict__ up,
                                                          uint32_t* __restrict__ z, int64_t npairs, float limit,
-                                                         const int32_t* __restrict__ live_rows, int64_t pairs_per_row) {
-  npairs = live_pairs(npairs, live_rows, pairs_per_row);
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < npairs; i += (int64_t)gridDim.x * blockDim.x) {
+                                                         const int32_t* __restrict__ row_begin, const int32_t* __restrict__ row_end,
+                                                         int64_t pairs_per_row) {
+  int64_t first, last;
+  live_pairs(npairs, row_begin, row_end, pairs_per_row, first, last);
+  for (int64_t i = first + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < last; i += (int64_t)gridDim.x * blockDim.x) {
     const uint32_t g2 = gate[i], u2 = up[i];
     float g[2] = {dev::bf16_lo(g2), dev::bf16_hi(g2)}, u[2] = {dev::bf16_lo(u2), dev::bf16_hi(u2)}, o[2];
 #pragma unroll
@@ -343,9 +347,11 @@ __global__ void __launch_bounds__(256) swiglu_fwd_kernel(const uint32_t* __restr
 __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const uint32_t* __restrict__ gate, const uint32_t* __restrict__ up,
                                                          const uint32_t* __restrict__ dz, uint32_t* __restrict__ dgate,
                                                          uint32_t* __restrict__ dup, int64_t npairs, float limit,
-                                                         const int32_t* __restrict__ live_rows, int64_t pairs_per_row) {
-  npairs = live_pairs(npairs, live_rows, pairs_per_row);
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < npairs; i += (int64_t)gridDim.x * blockDim.x) {
+                                                         const int32_t* __restrict__ row_begin, const int32_t* __restrict__ row_end,
+                                                         int64_t pairs_per_row) {
+  int64_t first, last;
+  live_pairs(npairs, row_begin, row_end, pairs_per_row, first, last);
+  for (int64_t i = first + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < last; i += (int64_t)gridDim.x * blockDim.x) {
     const uint32_t g2 = gate[i], u2 = up[i], d2 = dz[i];
     const float g[2] = {dev::bf16_lo(g2), dev::bf16_hi(g2)}, u[2] = {dev::bf16_lo(u2), dev::bf16_hi(u2)};
     const float d[2] = {dev::bf16_lo(d2), dev::bf16_hi(d2)};
@@ -449,6 +455,7 @@ extern "C" int b2g_route_gather(const void* hidden, const int64_t* perm, void* s
   const int64_t R = T * top_k;
   if (R == 0) return 0;
   B2G_REQUIRE(hidden && perm && selected && aligned16(hidden) && aligned16(selected), "null or misaligned pointer");
+  B2G_KERNEL_MAX_SHARED(gather_kernel);
   gather_kernel<<<row_grid((R + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint4*>(hidden), perm,
                                                                             static_cast<uint4*>(selected), R, top_k, H / 8);
   B2G_CUDA_OK(cudaGetLastError());
@@ -461,6 +468,7 @@ extern "C" int b2g_route_gather_bwd(const void* grad_selected, const int64_t* in
   if (T == 0) return 0;
   B2G_REQUIRE(grad_selected && inv_perm && grad_hidden && aligned16(grad_selected) && aligned16(grad_hidden),
               "null or misaligned pointer");
+  B2G_KERNEL_MAX_SHARED(gather_bwd_kernel);
   gather_bwd_kernel<<<row_grid(T), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(grad_selected), inv_perm, static_cast<uint4*>(grad_hidden), T, top_k, H / 8);
   B2G_CUDA_OK(cudaGetLastError());
@@ -474,6 +482,8 @@ extern "C" int b2g_route_combine(const void* expert_out, const void* weights, in
   if (T == 0) return 0;
   B2G_REQUIRE(expert_out && weights && inv_perm && out && aligned16(expert_out) && aligned16(out), "null or misaligned pointer");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  B2G_KERNEL_MAX_SHARED(combine_kernel<true>);
+  B2G_KERNEL_MAX_SHARED(combine_kernel<false>);
   if (w_dtype) combine_kernel<true><<<row_grid(T), 256, 0, s>>>(static_cast<const uint4*>(expert_out), weights, inv_perm,
                                                                 static_cast<uint4*>(out), T, top_k, H / 8);
   else combine_kernel<false><<<row_grid(T), 256, 0, s>>>(static_cast<const uint4*>(expert_out), weights, inv_perm,
@@ -492,6 +502,8 @@ extern "C" int b2g_route_combine_bwd(const void* expert_out, const void* weights
   B2G_REQUIRE(expert_out && weights && perm && grad_final && grad_expert_out && grad_weights, "null pointer");
   B2G_REQUIRE(aligned16(expert_out) && aligned16(grad_final) && aligned16(grad_expert_out), "misaligned pointer");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  B2G_KERNEL_MAX_SHARED(combine_bwd_kernel<true>);
+  B2G_KERNEL_MAX_SHARED(combine_bwd_kernel<false>);
   if (w_dtype) combine_bwd_kernel<true><<<row_grid((R + 7) / 8), 256, 0, s>>>(static_cast<const uint4*>(expert_out), weights, perm,
                                                                     static_cast<const uint4*>(grad_final),
                                                                     static_cast<uint4*>(grad_expert_out), grad_weights, R, top_k, H / 8);
@@ -502,31 +514,35 @@ extern "C" int b2g_route_combine_bwd(const void* expert_out, const void* weights
   return 0;
 }
 
-extern "C" int b2g_swiglu_fwd(const void* gate, const void* up, void* z, int64_t n, float limit, const int32_t* live_rows, int64_t cols,
-                              void* stream) {
+extern "C" int b2g_swiglu_fwd(const void* gate, const void* up, void* z, int64_t n, float limit, const int32_t* row_begin,
+                              const int32_t* row_end, int64_t cols, void* stream) {
   B2G_REQUIRE(n >= 0 && n % 2 == 0, "element count must be even");
-  B2G_REQUIRE(live_rows == nullptr || (cols > 0 && cols % 2 == 0 && n % cols == 0), "a live row count needs an even row width that divides n");
+  B2G_REQUIRE((row_begin == nullptr && row_end == nullptr) || (cols > 0 && cols % 2 == 0 && n % cols == 0),
+              "a row range needs an even row width that divides n");
   if (n == 0) return 0;
   B2G_REQUIRE(gate && up && z, "null pointer");
   const int64_t pairs = n / 2;
   const int64_t want = (pairs + 255) / 256, cap = (int64_t)sm_count() * 16;
+  B2G_KERNEL_MAX_SHARED(swiglu_fwd_kernel);
   swiglu_fwd_kernel<<<(int)(want < cap ? want : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint32_t*>(gate), static_cast<const uint32_t*>(up), static_cast<uint32_t*>(z), pairs, limit, live_rows, cols / 2);
+      static_cast<const uint32_t*>(gate), static_cast<const uint32_t*>(up), static_cast<uint32_t*>(z), pairs, limit, row_begin, row_end, cols / 2);
   B2G_CUDA_OK(cudaGetLastError());
   return 0;
 }
 
 extern "C" int b2g_swiglu_bwd(const void* gate, const void* up, const void* dz, void* dgate, void* dup, int64_t n, float limit,
-                              const int32_t* live_rows, int64_t cols, void* stream) {
+                              const int32_t* row_begin, const int32_t* row_end, int64_t cols, void* stream) {
   B2G_REQUIRE(n >= 0 && n % 2 == 0, "element count must be even");
-  B2G_REQUIRE(live_rows == nullptr || (cols > 0 && cols % 2 == 0 && n % cols == 0), "a live row count needs an even row width that divides n");
+  B2G_REQUIRE((row_begin == nullptr && row_end == nullptr) || (cols > 0 && cols % 2 == 0 && n % cols == 0),
+              "a row range needs an even row width that divides n");
   if (n == 0) return 0;
   B2G_REQUIRE(gate && up && dz && dgate && dup, "null pointer");
   const int64_t pairs = n / 2;
   const int64_t want = (pairs + 255) / 256, cap = (int64_t)sm_count() * 16;
+  B2G_KERNEL_MAX_SHARED(swiglu_bwd_kernel);
   swiglu_bwd_kernel<<<(int)(want < cap ? want : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint32_t*>(gate), static_cast<const uint32_t*>(up), static_cast<const uint32_t*>(dz),
-      static_cast<uint32_t*>(dgate), static_cast<uint32_t*>(dup), pairs, limit, live_rows, cols / 2);
+      static_cast<uint32_t*>(dgate), static_cast<uint32_t*>(dup), pairs, limit, row_begin, row_end, cols / 2);
   B2G_CUDA_OK(cudaGetLastError());
   return 0;
 }
