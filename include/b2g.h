@@ -86,6 +86,13 @@ B2G_API int b2g_qlinear_fwd(int qtype, const void* x, const void* payload, const
 B2G_API int b2g_qlinear_dgrad(int qtype, const void* dy, const void* payload, const void* dybs, const void* lora_a16,
                       void* dx, int64_t M, int64_t N, int64_t K, int* status, void* stream);
 
+/* TEST HOOK (no counterpart in the reference): b2g_qlinear_fwd without LoRA whose packed-weight producer is held back and whose
+ * bounded waits give up after spin_limit polls (16..65536) instead of the library's 2^22.  The wait for packed bytes runs out,
+ * every role of the kernel drains, TMEM is released, the kernel returns and *status holds 401; Y is unspecified.  It exists so
+ * that the give-up path of the bounded waits can be exercised without a faulting, trapping or hanging GPU. */
+B2G_API int b2g_debug_stalled_qlinear_fwd(int qtype, const void* x, const void* payload, void* y, int64_t M, int64_t N, int64_t K,
+                                  int spin_limit, int* status, void* stream);
+
 /* Fixed groups: Y[M,g,:] = X[M,g,:] . deq(W_g[N,K])^T for g < groups, with X [M, groups, K], the payload
  * [groups, N, row bytes] and Y [M, groups, N] all contiguous: `groups` independent dense products that read and write
  * column blocks of the shared tensors in place (no per-group copies), each the same kernel and the same arithmetic as

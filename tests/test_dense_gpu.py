@@ -208,3 +208,33 @@ def test_fail_closed_arguments(cuda):
         ag.lora_qlinear(torch.zeros(4, 256, dtype=torch.bfloat16, device=cuda), p, 12, 8,
                         torch.zeros(32, 256, device=cuda), torch.zeros(8, 32, device=cuda), 1.0)
     assert ag.mmq(torch.zeros(0, 256, dtype=torch.bfloat16, device=cuda), p, 12, 8).shape == (0, 8)
+
+
+def test_a_bounded_wait_that_runs_out_reports_and_returns(cuda):
+    """The give-up path of the kernel's waits, exercised without faulting or hanging anything: a test entry launches the forward
+    product with its packed-weight producer held back and a short wait limit.  The unpack warps' wait (site 401) runs out, all
+    roles drain, the kernel returns, the status word says which wait gave up, and the next ordinary launch is correct."""
+    import ctypes as C
+
+    from b2g import _lib, gguf_quant, ops
+
+    m, n, k = 1024, 512, 1024
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(m, k, generator=g).bfloat16().to(cuda)
+    payload = gguf_quant.quantize_q4_k(torch.randn(n, k, generator=g) * 0.02).to(cuda).reshape(-1)
+    good = ops.qlinear_fwd(x, payload, go.Q4_K, n)
+    ops.check_status()
+    y = torch.empty(m, n, dtype=torch.bfloat16, device=cuda)
+    status = ops.status_word(cuda)
+    _lib.call("b2g_debug_stalled_qlinear_fwd", go.Q4_K, C.c_void_p(x.data_ptr()), C.c_void_p(payload.data_ptr()), C.c_void_p(y.data_ptr()),
+              m, n, k, 256, C.c_void_p(status.data_ptr()), C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()                                     # the kernel came back
+    assert int(status.item()) == 401
+    with pytest.raises(Exception, match="bounded wait"):
+        ops.check_status()
+    ops.check_status()                                           # the word was cleared by the report
+    again = ops.qlinear_fwd(x, payload, go.Q4_K, n)
+    assert torch.equal(again, good)
+    with pytest.raises(ValueError, match="spin limit"):
+        _lib.call("b2g_debug_stalled_qlinear_fwd", go.Q4_K, C.c_void_p(x.data_ptr()), C.c_void_p(payload.data_ptr()), C.c_void_p(y.data_ptr()),
+                  m, n, k, 1 << 20, C.c_void_p(status.data_ptr()), None)

@@ -19,6 +19,7 @@ SIGNATURES = {
     "b2g_set_iq2s_grid": (_i32, [_vp]),
     "b2g_dequant": (_i32, [_i32, _vp, _i64, _i64, _vp, _vp]),
     "b2g_qlinear_fwd": (_i32, [_i32, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp]),
+    "b2g_debug_stalled_qlinear_fwd": (_i32, [_i32, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp, _vp]),
     "b2g_qlinear_dgrad": (_i32, [_i32, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp]),
     "b2g_fixed_grouped_fwd": (_i32, [_i32, _vp, _vp, _vp, _i64, _i32, _i64, _i64, _vp, _vp]),
     "b2g_fixed_grouped_dgrad": (_i32, [_i32, _vp, _vp, _vp, _i64, _i32, _i64, _i64, _vp, _vp]),

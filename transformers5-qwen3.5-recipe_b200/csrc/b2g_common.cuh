@@ -167,9 +167,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 #define B2G_SPIN_LIMIT (1u << 22)
 #endif
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                          int where) {
+                                          int where, uint32_t limit = B2G_SPIN_LIMIT) {
   if (mbar_try_wait(bar, parity)) return true;
-  for (uint32_t spin = 0; spin < B2G_SPIN_LIMIT; ++spin) {
+  for (uint32_t spin = 0; spin < limit; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((spin & 255u) == 255u && *abort_flag) return false;
   }

@@ -148,6 +148,9 @@ struct Params {
   const uint2* grid;  // IQ2_XXS table in global memory
   int* status;
   int wide_ok;        // output rows and row segments start on 32-byte boundaries
+  uint32_t spin_limit;   // polls the unpack warps' wait for packed bytes (site 401) may take before the kernel gives up; every
+                         // other wait keeps the library's limit and leaves as soon as it sees the CTA's abort flag
+  int hold_weights;      // test hook: the packed-weight producer issues nothing, so the unpack warps' wait (site 401) must run out
 };
 
 struct Tile { int expert, row0, rows, ct; };
@@ -763,7 +766,7 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
     }
   } else if (warp == 6 + kUnpackWarps) {
     // ============================== packed-weight producer ==============================
-    if (lane == 0) {
+    if (lane == 0 && !p.hold_weights) {
       int sp = 0, pp = 0;
       bool ok = true;
       for (int item = pair; item < total_items && ok; item += num_pairs) {
@@ -860,7 +863,7 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
         const int ps = n / P::kSteps;                                // packed slots advance once per P::kSteps steps
         const int sp = ps % C::kPStages, pp = (ps / C::kPStages) & 1;
         const int sb = n % kBStages, pb = (n / kBStages) & 1;
-        ok = dev::mbar_wait(bar(kFullP + sp), pp, abort_flag, p.status, 401);
+        ok = dev::mbar_wait(bar(kFullP + sp), pp, abort_flag, p.status, 401, p.spin_limit);
         if (!ok) break;
         // one (row, column group) per thread: forward 128 rows, dgrad 64 rows x the two 64-column groups of this CTA
         const int drow = MODE == kFwd ? tg : (tg & 63);
@@ -921,6 +924,8 @@ struct Launch {
   const void* bias;
   int* status;
   cudaStream_t stream;
+  uint32_t spin_limit;        // 0 = the library's default
+  int hold_weights;           // test hook, see Params
 };
 
 // Row pitch of a payload: the format's bytes per row, or that rounded up to 16 when the caller padded the rows.
@@ -963,6 +968,8 @@ int launch_impl(const Launch& L) {
   p.out1 = static_cast<__nv_bfloat16*>(L.out1);
   p.bias = static_cast<const __nv_bfloat16*>(L.bias);
   p.status = L.status;
+  p.spin_limit = L.spin_limit ? L.spin_limit : B2G_SPIN_LIMIT;
+  p.hold_weights = L.hold_weights;
   p.wide_ok = (p.ldc % 16 == 0) && (reinterpret_cast<uintptr_t>(L.out0) % 32 == 0) && (reinterpret_cast<uintptr_t>(L.out1) % 32 == 0);
   p.grid = nullptr;
   if (QT == B2G_IQ2_S) {
@@ -1120,6 +1127,26 @@ extern "C" int b2g_qlinear_fwd(int qtype, const void* x, const void* payload, co
   L.m_total = M; L.n = N; L.k = K; L.num_experts = 1; L.lora_rows = N; L.out0 = y; L.bias = bias; L.status = status;
   L.stream = static_cast<cudaStream_t>(stream);
   int rc = qg::check_common(L, "qlinear_fwd");
+  if (rc) return rc;
+  if (M == 0) return 0;
+  return qg::launch_mode<qg::kFwd>(L);
+}
+
+// Test hook for the bounded waits: the forward product with its packed-weight producer held back and a short wait limit.  The
+// unpack warps' wait for packed bytes (site 401) runs out after `spin_limit` polls, the CTA's abort flag stops every other role
+// (their own waits poll that flag),
+// TMEM is freed and the kernel returns with *status = 401 and an unspecified Y.  Nothing faults, traps or hangs; the next launch
+// on the same stream is unaffected.
+extern "C" int b2g_debug_stalled_qlinear_fwd(int qtype, const void* x, const void* payload, void* y, int64_t M, int64_t N, int64_t K,
+                                             int spin_limit, int* status, void* stream) {
+  qg::Launch L{};
+  qg::split_qtype(qtype, L); L.mode = qg::kFwd; L.a0 = x; L.w0 = payload;
+  L.m_total = M; L.n = N; L.k = K; L.num_experts = 1; L.lora_rows = N; L.out0 = y; L.status = status;
+  L.stream = static_cast<cudaStream_t>(stream);
+  L.spin_limit = static_cast<uint32_t>(spin_limit); L.hold_weights = 1;
+  B2G_REQUIRE(spin_limit >= 16 && spin_limit <= (1 << 16), "debug_stalled_qlinear_fwd: spin limit %d outside 16..65536", spin_limit);
+  B2G_REQUIRE(status != nullptr, "debug_stalled_qlinear_fwd: a status word is required");
+  int rc = qg::check_common(L, "debug_stalled_qlinear_fwd");
   if (rc) return rc;
   if (M == 0) return 0;
   return qg::launch_mode<qg::kFwd>(L);
