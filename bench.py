@@ -277,7 +277,7 @@ def measure_moe(kind: str, args, dev, dist, rank: int, world: int, steps: int, w
     if world > 1:
         dist.all_reduce(load)
     contiguous = ep_peer.contiguous_placement(E)
-    placement = ep_peer.balanced_placement(load, world) if (world > 1 and args.placement == "balanced") else contiguous
+    placement = ep_peer.balanced_placement(load, world, args.chunks) if (world > 1 and args.placement == "balanced") else contiguous
     loads = ep_peer.rank_loads(load, placement, world)
     loads_contiguous = ep_peer.rank_loads(load, contiguous, world)
     mine = ep_peer.experts_of_rank(placement, rank, world).tolist()
@@ -299,7 +299,8 @@ def measure_moe(kind: str, args, dev, dist, rank: int, world: int, steps: int, w
                 shared.lora_B[name].normal_(std=0.01, generator=sg)
     xchg = None
     if world > 1:
-        xchg = ep_peer.PeerExchange(t_local * TOPK, H, E, device=dev, chunks=args.chunks, placement=None if placement is contiguous else placement)
+        xchg = ep_peer.PeerExchange(t_local * TOPK, H, E, device=dev, chunks=args.chunks, placement=None if placement is contiguous else placement,
+                                    exchange_tpcs=args.exchange_tpcs)
 
     def layer(h, lg):
         idx = ops.router_topk(lg, TOPK, None, False)
@@ -357,6 +358,12 @@ def measure_moe(kind: str, args, dev, dist, rank: int, world: int, steps: int, w
     _lib.EVENTS.clear()
     phases = None
     if xchg is not None:
+        if args.timeline and rank == 0:
+            spans = xchg.timeline()
+            per_step = len(spans) // prof_steps
+            t0 = spans[-per_step][1]
+            sys.stderr.write("timeline of the last profiled step on rank 0 (ms):\n" + "".join(
+                f"  {name:18s} {a - t0:7.3f} -> {b - t0:7.3f}\n" for name, a, b in spans[-per_step:]))
         phases = {k: v / prof_steps for k, v in xchg.phase_ms().items()}
         xchg.profile, xchg.trace = False, []
     barrier()
@@ -401,7 +408,7 @@ def measure_moe(kind: str, args, dev, dist, rank: int, world: int, steps: int, w
                         "skew64k": "the same experts, 65536 tokens in total, router logits N(0,1) + per-expert bias N(0,0.5) (configuration 4)",
                         "deepseek": "grouped MoE IQ2_XXS LoRA, 256 experts top-6, hidden 4096, intermediate 2048, r=8, clamped SwiGLU, plus the Q8_0 shared expert, 8192 tokens (configuration 3)"}[kind],
            "n_gpus": world, "tokens_total": t_total, "scaling": "strong" if skew else "weak", "steps": steps,
-           "parallelism": "1 GPU" if world == 1 else f"ep{world}: {E // world} experts per GPU, peer-store dispatch / combine over NVLink, {args.chunks} token chunks on an exchange stream, {args.placement} placement",
+           "parallelism": "1 GPU" if world == 1 else f"ep{world}: {E // world} experts per GPU, peer-store dispatch / combine over NVLink, {args.chunks} expert groups pipelined on an exchange stream ({('%d TPCs of its own' % args.exchange_tpcs) if args.exchange_tpcs and args.chunks > 1 else 'sharing the SMs'}), {args.placement} placement",
            "ms_per_step": ms, "tokens_per_s": t_total / (ms * 1e-3), "step_tflops": flops / (ms * 1e-3) / 1e12,
            "frac_of_tensor_peak_all_gpus": flops / (ms * 1e-3) / 1e12 / (peak_tf * world), "peak_source": peak_src,
            "max_over_mean_rows": float(loads.max() / loads.mean()), "max_over_mean_rows_contiguous_blocks": float(loads_contiguous.max() / loads_contiguous.mean()),
@@ -620,9 +627,12 @@ def main() -> int:
                          "moe: grouped Q4_K experts alone, 16384 tokens on one GPU / 65536 tokens expert-parallel at N>1; moe64k: the 65536-token "
                          "layer at any N; moe3: the DeepSeek-shaped IQ2_XXS layer with its shared expert; formats / fixed / lmhead: single-GPU side measurements (see run_side)")
     ap.add_argument("--chunks", type=int, default=2, help="expert-parallel MoE: token chunks whose exchanges overlap the expert products")
+    ap.add_argument("--exchange-tpcs", type=int, default=0,
+                    help="expert-parallel MoE: TPCs (pairs of SMs) set aside for the exchanges that run beside expert products; 0 = they share the GEMM's SMs")
     ap.add_argument("--placement", default="balanced", choices=["balanced", "contiguous"],
                     help="expert-parallel MoE: experts placed over the ranks by measured load (default) or in contiguous blocks")
     ap.add_argument("--no-moe", action="store_true", help="dense workload: leave the `moe` object out")
+    ap.add_argument("--timeline", action="store_true", help="expert-parallel MoE: print rank 0's phase timeline of one step to stderr")
     args = ap.parse_args()
     if args.workload in ("moe", "moe64k", "moe3"):
         return run_moe(args)

@@ -251,12 +251,14 @@ B2G_API int b2g_grouped_lora_up(const void* p, int64_t ldp, const void* w, int w
  * pass; with perm == NULL row s of src is sent.  A slot at or beyond capacity_rows is never written; the status word is set to
  * 901 instead (b2g_ep_peer_plan clamps the owner's segments to the same capacity, so the rows that were dropped are not read
  * either).  The owners are visited in the order rank+1, rank+2, ..., so that the ranks do not all store to the same owner at
- * once.  One launch per expert group lets the caller overlap a group's transfer with another group's expert products:
- * ctas_per_sm = 1 makes the kernel small enough to share every SM with the quantized GEMM (128 threads of 32 registers, no
- * shared memory); an exchange that runs alone takes 8 for bandwidth. */
+ * once.  One launch per expert group lets the caller overlap a group's transfer with another group's expert products.
+ * spread > 0: a small kernel (128 threads of 32 registers, no shared memory) with that many CTAs per SM: 1 shares every SM
+ * with the quantized GEMM, 8 is for an exchange that runs alone.  spread < 0: a wide kernel (1024 threads) as -spread clusters
+ * of two CTAs, which occupy the two SMs of -spread TPCs entirely: for an exchange that runs beside a GEMM told to leave those
+ * SMs free (b2g_set_gemm_sm_margin), so that the two share no SM. */
 B2G_API int b2g_ep_scatter_rows(const void* src, const int64_t* perm, int top_k, const int64_t* sorted_expert,
                         const int32_t* my_start, const int32_t* dest_base, const uint64_t* peer_ptrs, int experts_per_rank,
-                        int world, int rank, int group_lo, int group_hi, int64_t R, int H, int64_t capacity_rows, int ctas_per_sm,
+                        int world, int rank, int group_lo, int group_hi, int64_t R, int H, int64_t capacity_rows, int spread,
                         int* status, void* stream);
 
 /* Owner side, the inverse: rows of the grouped buffer (blocks ordered by (local expert, source rank), block b
@@ -264,7 +266,12 @@ B2G_API int b2g_ep_scatter_rows(const void* src, const int64_t* perm, int top_k,
  * src_pos[b] + offset inside the block; the call moves the blocks [block_lo, block_hi) (whole experts: multiples of world).
  * Pairs with the weighted un-permute of fast_moe_routing.py:162-194 on the source rank. */
 B2G_API int b2g_ep_return_rows(const void* rows, const int32_t* blk_start, const int32_t* src_pos, const uint64_t* peer_ptrs,
-                       int world, int block_lo, int block_hi, int H, int64_t capacity_rows, int ctas_per_sm, void* stream);
+                       int world, int block_lo, int block_hi, int H, int64_t capacity_rows, int spread, void* stream);
+
+/* SMs that every later launch of the persistent quantized GEMM (dense and grouped) leaves free: an even number, 0 by default.
+ * The expert-parallel layer sets it while its exchange kernels run beside the expert products on SMs of their own, and clears
+ * it afterwards.  Process-wide.  This entry has no counterpart in the reference (which is single-GPU, docs/plan_qwen3.5.md:23). */
+B2G_API int b2g_set_gemm_sm_margin(int sms);
 
 /* Slots of the two exchange kernels for rank `rank`, from the all-gathered histograms counts[world][num_experts]
  * (int32, row g = rows of rank g per global expert, rows count_stride elements apart; rank g owns experts

@@ -45,6 +45,7 @@ SIGNATURES = {
     "b2g_grouped_lora_up": (_i32, [_vp, _i64, _vp, _i32, _vp, _vp, _i64, _i64, _i32, _i32, _vp]),
     "b2g_ep_scatter_rows": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i64, _i32, _i64, _i32, _vp, _vp]),
     "b2g_ep_return_rows": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i64, _i32, _vp]),
+    "b2g_set_gemm_sm_margin": (_i32, [_i32]),
     "b2g_ep_peer_plan": (_i32, [_vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp]),
     "b2g_swiglu_fwd": (_i32, [_vp, _vp, _vp, _i64, _f32, _vp, _vp, _i64, _vp]),
     "b2g_swiglu_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _f32, _vp, _vp, _i64, _vp]),

@@ -110,26 +110,53 @@ def build_peer_plan_device(counts: torch.Tensor, rank: int, capacity: Optional[i
 
 
 # ---- static load-aware expert placement ---------------------------------------------------------------------------------
-def balanced_placement(load: torch.Tensor, world: int) -> torch.Tensor:
+def group_ranges(experts_per_rank: int, chunks: int) -> list[tuple[int, int]]:
+    """The expert groups of a rank: ``chunks`` contiguous ranges of local expert indices, equal parts, the first
+    ``experts_per_rank % chunks`` one expert longer."""
+    chunks = max(1, min(int(chunks), experts_per_rank))
+    base, extra = divmod(experts_per_rank, chunks)
+    out, lo = [], 0
+    for c in range(chunks):
+        hi = lo + base + (1 if c < extra else 0)
+        out.append((lo, hi))
+        lo = hi
+    return out
+
+
+def _fill_bins(items: list[int], weights: list[float], capacities: list[int]) -> list[list[int]]:
+    """Longest-processing-time first into bins of fixed capacities: ``items`` (heaviest first) each go to the bin with the least
+    weight so far among those with a free slot; ties to the smaller bin."""
+    load, bins = [0.0] * len(capacities), [[] for _ in capacities]
+    for it in items:
+        b = min((i for i in range(len(capacities)) if len(bins[i]) < capacities[i]), key=lambda i: (load[i], i))
+        bins[b].append(it)
+        load[b] += weights[it]
+    return bins
+
+
+def balanced_placement(load: torch.Tensor, world: int, chunks: int = 1) -> torch.Tensor:
     """Placed id of every expert, int64 [E]: rank ``placed // (E / world)`` owns it as its local expert ``placed % (E / world)``.
 
     ``load[e]`` is the measured number of rows routed to expert ``e`` (a histogram over one or more batches).  Experts are
     taken from the heaviest down and each goes to the rank with the least load so far among the ranks that still have a
-    free slot, every rank ending with exactly ``E / world`` experts.  Deterministic: ties go to the smaller expert id and
-    the smaller rank, so every rank derives the same table from the same (all-reduced) histogram."""
+    free slot, every rank ending with exactly ``E / world`` experts.  Within a rank the same rule spreads its experts over the
+    ``chunks`` expert groups of the exchange pipeline (``group_ranges``), so that the groups carry equal loads too.
+    Deterministic: ties go to the smaller expert id and the smaller bin, so every rank derives the same table from the same
+    (all-reduced) histogram."""
     e = load.numel()
     if e % world:
         raise ValueError(f"{e} experts do not divide over {world} ranks")
     per = e // world
     weights = [float(v) for v in load.detach().cpu().double().tolist()]
     order = sorted(range(e), key=lambda i: (-weights[i], i))
-    rank_load, rank_fill = [0.0] * world, [0] * world
+    ranges = group_ranges(per, chunks)
     placed = [0] * e
-    for ex in order:
-        g = min((r for r in range(world) if rank_fill[r] < per), key=lambda r: (rank_load[r], r))
-        placed[ex] = g * per + rank_fill[g]
-        rank_fill[g] += 1
-        rank_load[g] += weights[ex]
+    for g, members in enumerate(_fill_bins(order, weights, [per] * world)):
+        slot = 0
+        for group in _fill_bins(members, weights, [hi - lo for lo, hi in ranges]):
+            for ex in group:
+                placed[ex] = g * per + slot
+                slot += 1
     return torch.tensor(placed, dtype=torch.int64)
 
 
@@ -161,7 +188,7 @@ class PeerExchange:
     MAX_BUFFER_BYTES = 16 << 30      # all four buffers of a layer together; a worst-case size beyond this is cut down to it
 
     def __init__(self, rows_local: int, hidden: int, num_experts: int, group=None, capacity_factor: Optional[float] = None,
-                 device: Optional[torch.device] = None, chunks: int = 1, placement: Optional[torch.Tensor] = None):
+                 device: Optional[torch.device] = None, chunks: int = 1, placement: Optional[torch.Tensor] = None, exchange_tpcs: int = 0):
         import torch.distributed._symmetric_memory as symm
 
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
@@ -173,15 +200,12 @@ class PeerExchange:
         if num_experts % self.world:
             raise ValueError(f"{num_experts} experts do not divide over {self.world} ranks")
         self.experts_per_rank = num_experts // self.world
-        self.chunks = max(1, min(int(chunks), self.experts_per_rank))
         self.placement = None if placement is None else placement.to(device=self.device, dtype=torch.int64).contiguous()
-        # expert groups: equal parts of the local expert range, the first (experts_per_rank % chunks) one expert longer
-        base, extra = divmod(self.experts_per_rank, self.chunks)
-        self.groups, lo = [], 0
-        for c in range(self.chunks):
-            hi = lo + base + (1 if c < extra else 0)
-            self.groups.append((lo, hi))
-            lo = hi
+        self.groups = group_ranges(self.experts_per_rank, chunks)
+        self.chunks = len(self.groups)
+        # Where an exchange runs while expert products of another group compute: 0 = on the same SMs (a small kernel beside the
+        # GEMM's CTA); n > 0 = on n TPCs (2n SMs) of its own, which the GEMM is told to leave free
+        self.exchange_tpcs = int(exchange_tpcs) if self.chunks > 1 else 0
         # a receive buffer holds, in the worst case, the routed rows of every rank
         factor = float(self.world) if capacity_factor is None else float(capacity_factor)
         cap = int(self.rows_local * min(factor, float(self.world)))
@@ -220,6 +244,14 @@ class PeerExchange:
             out[name] = out.get(name, 0.0) + a.elapsed_time(b)
         return out
 
+    def timeline(self) -> list[tuple[str, float, float]]:
+        """(phase, start ms, end ms) of every recorded span, relative to the first one (synchronises)."""
+        torch.cuda.synchronize(self.device)
+        if not self.trace:
+            return []
+        origin = self.trace[0][1]
+        return [(name, origin.elapsed_time(a), origin.elapsed_time(b)) for name, a, b in self.trace]
+
     # -- pieces (each runs on the CURRENT stream) ---------------------------------------------------------------------------
     def sync(self) -> None:
         """All ranks' earlier work on this stream is complete before any rank continues on it."""
@@ -231,7 +263,16 @@ class PeerExchange:
         _launch_plan(self.counts_all, self.num_experts, self.world, self.num_experts, self.rank, self.plan, self.capacity)
         return self.plan
 
-    ALONE, BESIDE = 8, 1             # CTAs per SM of an exchange that nothing computes beside / that shares the SMs with the GEMM
+    ALONE = 8                        # CTAs per SM of the small kernel for an exchange that nothing computes beside
+
+    def _beside(self) -> int:
+        """Launch shape of an exchange that runs while experts compute: the wide kernel on TPCs of its own, or one small CTA per SM."""
+        return -self.exchange_tpcs if self.exchange_tpcs else 1
+
+    def gemm_margin(self, on: bool) -> None:
+        """The GEMMs launched from here on leave the exchange's SMs free (or, ``on = False``, use the whole GPU again)."""
+        if self.exchange_tpcs:
+            _lib.call("b2g_set_gemm_sm_margin", 2 * self.exchange_tpcs if on else 0)
 
     def scatter(self, src: torch.Tensor, perm: Optional[torch.Tensor], top_k: int, sorted_expert: torch.Tensor, chunk: int, which: int) -> None:
         """Rows of ``src`` (gathered through ``perm`` when given) that belong to expert group ``chunk`` into the owners' receive
@@ -242,7 +283,7 @@ class PeerExchange:
             _lib.call("b2g_ep_scatter_rows", C.c_void_p(src.data_ptr()), None if perm is None else C.c_void_p(perm.data_ptr()), int(top_k),
                       C.c_void_p(sorted_expert.data_ptr()), C.c_void_p(self.plan.my_start.data_ptr()), C.c_void_p(self.plan.dest_base.data_ptr()),
                       C.c_void_p(self._recv_ptrs[which].data_ptr()), self.experts_per_rank, self.world, self.rank, lo, hi,
-                      sorted_expert.numel(), self.hidden, self.capacity, self.ALONE if chunk == 0 else self.BESIDE,
+                      sorted_expert.numel(), self.hidden, self.capacity, self.ALONE if chunk == 0 else self._beside(),
                       C.c_void_p(ops.status_word(self.device).data_ptr()), C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
 
     def give_back(self, rows: torch.Tensor, chunk: int, which: int) -> None:
@@ -252,7 +293,7 @@ class PeerExchange:
         with torch.cuda.device(self.device):
             _lib.call("b2g_ep_return_rows", C.c_void_p(rows.data_ptr()), C.c_void_p(self.plan.blk_start.data_ptr()),
                       C.c_void_p(self.plan.src_pos.data_ptr()), C.c_void_p(self._ret_ptrs[which].data_ptr()), self.world, lo * self.world,
-                      hi * self.world, self.hidden, self.capacity, self.ALONE if chunk == self.chunks - 1 else self.BESIDE,
+                      hi * self.world, self.hidden, self.capacity, self.ALONE if chunk == self.chunks - 1 else self._beside(),
                       C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
 
 
@@ -311,20 +352,37 @@ class _PeerMoe(torch.autograd.Function):
             gu_a_c, down_a_c = gu_a.contiguous(), down_a.contiguous()
             gu_b16, down_b16 = ops.pad_rank_cols(gu_b), ops.pad_rank_cols(down_b)
 
+        n = xchg.chunks
+
+        def send(c):                                     # exchange stream: rows of group c to their owners
+            # No wait is needed before writing the receive buffer: its last readers (the previous call's backward) were
+            # enqueued before that call's final sync(), which every rank has passed to get here.
+            with torch.cuda.stream(xs), _Span(xchg, "dispatch", xs):
+                xchg.scatter(hidden, perm, top_k, sorted_e, c, 0)
+                xchg.sync()                              # every source has delivered group c
+            ev["sent"][c].record(xs)
+
+        def bring_back(c):                               # exchange stream: results of group c back to their sources
+            with torch.cuda.stream(xs):
+                xs.wait_event(ev["computed"][c])
+                with _Span(xchg, "return", xs):
+                    xchg.give_back(out_e, c, 0)
+                    xchg.sync()
+            ev["returned"][c].record(xs)
+
         with torch.cuda.stream(xs):
             xs.wait_event(xchg.ev_plan)
             with _Span(xchg, "plan_exchange", xs):
                 xchg.make_plan()
-            for c in range(xchg.chunks):
-                # No wait is needed before writing the receive buffer: its last readers (the previous call's backward) were
-                # enqueued before that call's final sync(), which every rank has passed to get here.
-                with _Span(xchg, "dispatch", xs):
-                    xchg.scatter(hidden, perm, top_k, sorted_e, c, 0)
-                    xchg.sync()                          # every source has delivered group c
-                ev["sent"][c].record(xs)
-
+        # The exchange stream runs S0 S1 S2 R0 S3 R1 ... R(n-1): while group c computes, group c+1 (already) and c+2 arrive and
+        # group c-1 goes home.  An event must be recorded (host side) before another stream is told to wait for it, hence the
+        # order of the calls below.
+        send(0)
+        if n > 1:
+            send(1)
         x = xchg.recv[0]
         tiles = []
+        xchg.gemm_margin(True)
         for c, (lo, hi) in enumerate(xchg.groups):
             cs.wait_event(ev["sent"][c])
             first, end = xchg.group_first[c], xchg.group_end[c]
@@ -339,14 +397,10 @@ class _PeerMoe(torch.autograd.Function):
                 ops.grouped_fwd(z, down_p.reshape(-1), None, quant_type, xchg.hidden, e_local, t, zas, down_b16, out0=out_e)
             ev["computed"][c].record(cs)
             tiles.append(t)
-
-        with torch.cuda.stream(xs):
-            for c in range(xchg.chunks):
-                xs.wait_event(ev["computed"][c])
-                with _Span(xchg, "return", xs):
-                    xchg.give_back(out_e, c, 0)
-                    xchg.sync()
-                ev["returned"][c].record(xs)
+            if c + 2 < n:
+                send(c + 2)
+            bring_back(c)
+        xchg.gemm_margin(False)
 
         cs.wait_event(ev["returned"][-1])                 # the exchange stream is in order: the last group's return is the last
         returned = xchg.ret[0][:rows]
@@ -378,15 +432,28 @@ class _PeerMoe(torch.autograd.Function):
             down_a16, gu_a16 = ops.pad_rank_rows(down_a), ops.pad_rank_rows(gu_a)
             grads = [torch.empty_like(gu_a), torch.empty_like(gu_b), torch.empty_like(down_a), torch.empty_like(down_b)]
 
-        with torch.cuda.stream(xs):
-            xs.wait_event(xchg.ev_ready)
-            for c in range(xchg.chunks):
-                with _Span(xchg, "dispatch_backward", xs):
-                    xchg.scatter(d_rows, None, 1, sorted_e, c, 1)
-                    xchg.sync()
-                ev["g_sent"][c].record(xs)
+        n = xchg.chunks
 
+        def send(c):
+            with torch.cuda.stream(xs), _Span(xchg, "dispatch_backward", xs):
+                xchg.scatter(d_rows, None, 1, sorted_e, c, 1)
+                xchg.sync()
+            ev["g_sent"][c].record(xs)
+
+        def bring_back(c):
+            with torch.cuda.stream(xs):
+                xs.wait_event(ev["g_computed"][c])
+                with _Span(xchg, "return_backward", xs):
+                    xchg.give_back(d_sel, c, 1)
+                    xchg.sync()
+            ev["g_returned"][c].record(xs)
+
+        xs.wait_event(xchg.ev_ready)
+        send(0)
+        if n > 1:
+            send(1)
         x, d_out = xchg.recv[0], xchg.recv[1]
+        xchg.gemm_margin(True)
         for c, (lo, hi) in enumerate(xchg.groups):
             cs.wait_event(ev["g_sent"][c])
             first, end, t, offs = xchg.group_first[c], xchg.group_end[c], tiles[c], plan.local_offsets[lo:hi]
@@ -408,14 +475,10 @@ class _PeerMoe(torch.autograd.Function):
                     ops.grouped_lora_wgrad(xa, d_gate, scaling, r, offs, grads[1][lo:hi], True, 0, first)
                     ops.grouped_lora_wgrad(xa, d_up, scaling, r, offs, grads[1][lo:hi], True, inter_dim, first)
             ev["g_computed"][c].record(cs)
-
-        with torch.cuda.stream(xs):
-            for c in range(xchg.chunks):
-                xs.wait_event(ev["g_computed"][c])
-                with _Span(xchg, "return_backward", xs):
-                    xchg.give_back(d_sel, c, 1)
-                    xchg.sync()
-                ev["g_returned"][c].record(xs)
+            if c + 2 < n:
+                send(c + 2)
+            bring_back(c)
+        xchg.gemm_margin(False)
 
         cs.wait_event(ev["g_returned"][-1])
         with _Span(xchg, "gather_backward", cs):

@@ -170,3 +170,16 @@ int b2g_set_iq2s_grid(const uint8_t* host_grid_1024x8) {
 }
 
 }  // extern "C"
+
+// SMs that the persistent quantized GEMM leaves free (an even number: it runs on CTA pairs), for kernels of another stream
+// that must not share an SM with it.  Process-wide, read at every GEMM launch.
+namespace b2g {
+static std::atomic<int> g_gemm_sm_margin{0};
+int gemm_sm_margin() { return g_gemm_sm_margin.load(std::memory_order_relaxed); }
+}  // namespace b2g
+
+extern "C" int b2g_set_gemm_sm_margin(int sms) {
+  B2G_REQUIRE(sms >= 0 && sms <= 64 && sms % 2 == 0, "gemm sm margin %d must be an even number between 0 and 64", sms);
+  b2g::g_gemm_sm_margin.store(sms, std::memory_order_relaxed);
+  return 0;
+}

@@ -30,24 +30,35 @@
 namespace b2g {
 namespace ep {
 
-// One warp copies one row: four 16-byte vectors per lane in flight (the register budget of 32 allows no more).
+// One warp copies one row, kVec 16-byte vectors per lane in flight: four in the small variant (its register budget of 32
+// allows no more), eight in the wide one.
+template <int kVec>
 __device__ __forceinline__ void copy_row(const uint4* __restrict__ in, uint4* __restrict__ out, int vec_per_row, int lane) {
-  for (int v0 = lane; v0 < vec_per_row; v0 += 128) {
-    uint4 buf[4];
+  for (int v0 = lane; v0 < vec_per_row; v0 += 32 * kVec) {
+    uint4 buf[kVec];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < kVec; ++i)
       if (v0 + 32 * i < vec_per_row) buf[i] = __ldcs(in + v0 + 32 * i);
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < kVec; ++i)
       if (v0 + 32 * i < vec_per_row) out[v0 + 32 * i] = buf[i];
   }
 }
+
+// Two shapes of each copy kernel:
+//   small: 128 threads, 32 registers, four vectors in flight per lane: fits beside the GEMM's CTA on the same SM;
+//   wide : 1024 threads, 64 registers, eight vectors in flight per lane: fills an SM by itself.  Launched as clusters of two
+//          CTAs, which the hardware places on the two SMs of one TPC, on a few TPCs that the GEMM (itself launched on CTA pairs
+//          and told to leave that many SMs free) does not use: the exchange then shares no SM with the expert products.
+struct Small { static constexpr int kThreads = 128, kMinBlocks = 16, kVec = 4; };
+struct Wide { static constexpr int kThreads = 1024, kMinBlocks = 1, kVec = 8; };
 
 // Scatter of the rows whose LOCAL expert index (global id modulo experts_per_rank) lies in [group_lo, group_hi): one expert group
 // of every owner.  Rows are sorted by global expert id, so the group is one contiguous range of sorted positions per owner;
 // the owners are visited one after the other, starting with the rank after this one, so that the ranks of a job do not all
 // store to the same GPU at the same time (one NVLink port would take everything while the others idle).
-__global__ void __launch_bounds__(128, 16) scatter_rows_kernel(const uint4* __restrict__ src, const int64_t* __restrict__ perm, int top_k,
+template <typename Shape>
+__global__ void __launch_bounds__(Shape::kThreads, Shape::kMinBlocks) scatter_rows_kernel(const uint4* __restrict__ src, const int64_t* __restrict__ perm, int top_k,
                                                                const int64_t* __restrict__ sorted_expert, const int32_t* __restrict__ my_start,
                                                                const int32_t* __restrict__ dest_base, const unsigned long long* __restrict__ peers,
                                                                int experts_per_rank, int world, int rank, int group_lo, int group_hi, int64_t R,
@@ -69,14 +80,15 @@ __global__ void __launch_bounds__(128, 16) scatter_rows_kernel(const uint4* __re
         continue;
       }
       const int64_t from = perm ? perm[s] / top_k : s;
-      copy_row(src + from * vec_per_row, base + slot * vec_per_row, vec_per_row, lane);
+      copy_row<Shape::kVec>(src + from * vec_per_row, base + slot * vec_per_row, vec_per_row, lane);
     }
   }
 }
 
 // The inverse on the owner: the rows of the blocks [block_lo, block_hi) (block b = local expert b / world, source rank b % world;
 // an expert group is a contiguous range of blocks and of rows) go back to their sources.
-__global__ void __launch_bounds__(128, 16) return_rows_kernel(const uint4* __restrict__ rows, const int32_t* __restrict__ blk_start,
+template <typename Shape>
+__global__ void __launch_bounds__(Shape::kThreads, Shape::kMinBlocks) return_rows_kernel(const uint4* __restrict__ rows, const int32_t* __restrict__ blk_start,
                                                               const int32_t* __restrict__ src_pos, const unsigned long long* __restrict__ peers,
                                                               int world, int block_lo, int block_hi, int vec_per_row, int64_t capacity) {
   const int lane = threadIdx.x & 31;
@@ -93,7 +105,7 @@ __global__ void __launch_bounds__(128, 16) return_rows_kernel(const uint4* __res
       if (blk_start[mid] <= j) lo = mid; else hi = mid - 1;
     }
     const int64_t pos = static_cast<int64_t>(src_pos[lo]) + (j - blk_start[lo]);
-    copy_row(rows + j * vec_per_row, reinterpret_cast<uint4*>(peers[lo % world]) + pos * vec_per_row, vec_per_row, lane);
+    copy_row<Shape::kVec>(rows + j * vec_per_row, reinterpret_cast<uint4*>(peers[lo % world]) + pos * vec_per_row, vec_per_row, lane);
   }
 }
 
@@ -168,9 +180,12 @@ __global__ void __launch_bounds__(256) peer_plan_kernel(const int32_t* __restric
 
 using namespace b2g;
 
+// `spread`: > 0 = the small kernel with that many CTAs per SM (1 to run beside the GEMM on the same SMs, more when nothing
+// computes beside the exchange); < 0 = the wide kernel on -spread TPCs (cluster pairs) that the GEMM leaves free.
+
 extern "C" int b2g_ep_scatter_rows(const void* src, const int64_t* perm, int top_k, const int64_t* sorted_expert, const int32_t* my_start,
                                    const int32_t* dest_base, const uint64_t* peer_ptrs, int experts_per_rank, int world, int rank,
-                                   int group_lo, int group_hi, int64_t R, int H, int64_t capacity_rows, int ctas_per_sm, int* status,
+                                   int group_lo, int group_hi, int64_t R, int H, int64_t capacity_rows, int spread, int* status,
                                    void* stream) {
   B2G_REQUIRE(H > 0 && H % 8 == 0, "ep_scatter_rows: row width %d must be a positive multiple of 8", H);
   B2G_REQUIRE(experts_per_rank >= 1 && capacity_rows >= 0 && R >= 0, "ep_scatter_rows: bad sizes");
@@ -178,35 +193,63 @@ extern "C" int b2g_ep_scatter_rows(const void* src, const int64_t* perm, int top
   B2G_REQUIRE(group_lo >= 0 && group_lo < group_hi && group_hi <= experts_per_rank, "ep_scatter_rows: expert group [%d, %d) outside 0..%d",
               group_lo, group_hi, experts_per_rank);
   B2G_REQUIRE(perm == nullptr || top_k >= 1, "ep_scatter_rows: top_k must be positive when rows are gathered");
+  B2G_REQUIRE(spread != 0 && spread >= -64 && spread <= 16, "ep_scatter_rows: spread %d outside -64..-1, 1..16", spread);
   if (R == 0) return 0;
   B2G_REQUIRE(src && sorted_expert && my_start && dest_base && peer_ptrs && aligned16(src), "ep_scatter_rows: null or misaligned pointer");
-  B2G_REQUIRE(ctas_per_sm >= 1 && ctas_per_sm <= 16, "ep_scatter_rows: ctas_per_sm %d outside 1..16", ctas_per_sm);
-  // ctas_per_sm = 1 for an exchange that runs beside expert products: one CTA of this kernel fits next to the GEMM's CTA, two
-  // do not leave the GEMM room, and a kernel that finds the SMs idle would otherwise fill them and hold the next GEMM launch
-  // back until the whole exchange is done.  More CTAs per SM (more rows in flight) for an exchange that nothing waits beside.
-  const int64_t want = (R + 3) / 4, cap = (int64_t)sm_count() * ctas_per_sm;
-  B2G_KERNEL_MAX_SHARED(ep::scatter_rows_kernel);
-  ep::scatter_rows_kernel<<<(int)(want < cap ? want : cap), 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(src), perm, top_k, sorted_expert, my_start, dest_base, reinterpret_cast<const unsigned long long*>(peer_ptrs),
-      experts_per_rank, world, rank, group_lo, group_hi, R, H / 8, capacity_rows, status);
-  B2G_CUDA_OK(cudaGetLastError());
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  auto* peers = reinterpret_cast<const unsigned long long*>(peer_ptrs);
+  if (spread > 0) {
+    const int64_t want = (R + 3) / 4, cap = (int64_t)sm_count() * spread;
+    B2G_KERNEL_MAX_SHARED(ep::scatter_rows_kernel<ep::Small>);
+    ep::scatter_rows_kernel<ep::Small><<<(int)(want < cap ? want : cap), ep::Small::kThreads, 0, st>>>(
+        static_cast<const uint4*>(src), perm, top_k, sorted_expert, my_start, dest_base, peers, experts_per_rank, world, rank, group_lo,
+        group_hi, R, H / 8, capacity_rows, status);
+    B2G_CUDA_OK(cudaGetLastError());
+    return 0;
+  }
+  B2G_KERNEL_MAX_SHARED(ep::scatter_rows_kernel<ep::Wide>);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(2 * -spread);
+  cfg.blockDim = dim3(ep::Wide::kThreads);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  B2G_CUDA_OK(cudaLaunchKernelEx(&cfg, ep::scatter_rows_kernel<ep::Wide>, static_cast<const uint4*>(src), perm, top_k, sorted_expert, my_start,
+                                 dest_base, peers, experts_per_rank, world, rank, group_lo, group_hi, R, H / 8, capacity_rows, status));
   return 0;
 }
 
 extern "C" int b2g_ep_return_rows(const void* rows, const int32_t* blk_start, const int32_t* src_pos, const uint64_t* peer_ptrs, int world,
-                                  int block_lo, int block_hi, int H, int64_t capacity_rows, int ctas_per_sm, void* stream) {
+                                  int block_lo, int block_hi, int H, int64_t capacity_rows, int spread, void* stream) {
   B2G_REQUIRE(H > 0 && H % 8 == 0, "ep_return_rows: row width %d must be a positive multiple of 8", H);
   B2G_REQUIRE(world >= 1 && block_lo >= 0 && block_lo < block_hi && block_lo % world == 0 && block_hi % world == 0,
               "ep_return_rows: blocks [%d, %d) are not whole experts of %d ranks", block_lo, block_hi, world);
+  B2G_REQUIRE(spread != 0 && spread >= -64 && spread <= 16, "ep_return_rows: spread %d outside -64..-1, 1..16", spread);
   if (capacity_rows == 0) return 0;
   B2G_REQUIRE(rows && blk_start && src_pos && peer_ptrs && aligned16(rows), "ep_return_rows: null or misaligned pointer");
-  B2G_REQUIRE(ctas_per_sm >= 1 && ctas_per_sm <= 16, "ep_return_rows: ctas_per_sm %d outside 1..16", ctas_per_sm);
-  const int64_t want = (capacity_rows + 3) / 4, cap = (int64_t)sm_count() * ctas_per_sm;      // as in the scatter
-  B2G_KERNEL_MAX_SHARED(ep::return_rows_kernel);
-  ep::return_rows_kernel<<<(int)(want < cap ? want : cap), 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(rows), blk_start, src_pos, reinterpret_cast<const unsigned long long*>(peer_ptrs), world, block_lo, block_hi,
-      H / 8, capacity_rows);
-  B2G_CUDA_OK(cudaGetLastError());
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  auto* peers = reinterpret_cast<const unsigned long long*>(peer_ptrs);
+  if (spread > 0) {
+    const int64_t want = (capacity_rows + 3) / 4, cap = (int64_t)sm_count() * spread;
+    B2G_KERNEL_MAX_SHARED(ep::return_rows_kernel<ep::Small>);
+    ep::return_rows_kernel<ep::Small><<<(int)(want < cap ? want : cap), ep::Small::kThreads, 0, st>>>(
+        static_cast<const uint4*>(rows), blk_start, src_pos, peers, world, block_lo, block_hi, H / 8, capacity_rows);
+    B2G_CUDA_OK(cudaGetLastError());
+    return 0;
+  }
+  B2G_KERNEL_MAX_SHARED(ep::return_rows_kernel<ep::Wide>);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(2 * -spread);
+  cfg.blockDim = dim3(ep::Wide::kThreads);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  B2G_CUDA_OK(cudaLaunchKernelEx(&cfg, ep::return_rows_kernel<ep::Wide>, static_cast<const uint4*>(rows), blk_start, src_pos, peers, world,
+                                 block_lo, block_hi, H / 8, capacity_rows));
   return 0;
 }
 

@@ -29,6 +29,7 @@
 #include "b2g_formats.cuh"
 
 namespace b2g {
+int gemm_sm_margin();
 int iq2xxs_grid(const uint2** out);
 int iq2s_grid(const uint2** out);
 
@@ -1014,7 +1015,8 @@ int launch_impl(const Launch& L) {
     }
   }
 
-  int pairs = sm_count() / 2;
+  int pairs = (sm_count() - gemm_sm_margin()) / 2;
+  if (pairs < 1) pairs = 1;
   if (!L.tiles) {
     const int64_t items = (int64_t)p.dense_m_tiles * p.num_ct;
     if (items < pairs) pairs = (int)items;
