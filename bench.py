@@ -627,7 +627,7 @@ def main() -> int:
                          "moe: grouped Q4_K experts alone, 16384 tokens on one GPU / 65536 tokens expert-parallel at N>1; moe64k: the 65536-token "
                          "layer at any N; moe3: the DeepSeek-shaped IQ2_XXS layer with its shared expert; formats / fixed / lmhead: single-GPU side measurements (see run_side)")
     ap.add_argument("--chunks", type=int, default=2, help="expert-parallel MoE: token chunks whose exchanges overlap the expert products")
-    ap.add_argument("--exchange-tpcs", type=int, default=0,
+    ap.add_argument("--exchange-tpcs", type=int, default=12,
                     help="expert-parallel MoE: TPCs (pairs of SMs) set aside for the exchanges that run beside expert products; 0 = they share the GEMM's SMs")
     ap.add_argument("--placement", default="balanced", choices=["balanced", "contiguous"],
                     help="expert-parallel MoE: experts placed over the ranks by measured load (default) or in contiguous blocks")

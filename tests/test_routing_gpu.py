@@ -148,3 +148,32 @@ def test_swiglu_forward_backward(cuda):
         z = ops.swiglu_fwd(gate.to(cuda), up.to(cuda), limit)
         dg, du = ops.swiglu_bwd(gate.to(cuda), up.to(cuda), dz.to(cuda), limit)
         assert dense_ref.rel_l2(z, zr) < 2e-3 and dense_ref.rel_l2(du, ur.grad) < 4e-3 and dense_ref.rel_l2(dg, gr.grad) < 1e-2
+
+
+def test_an_expert_id_outside_the_expert_count_is_reported_and_contained(cuda):
+    """One route names expert E (one past the last).  The plan does not count or place it, the status word reports it (903),
+    every index the plan returns stays inside its tensor (the skipped slots keep the zeros they were created with), and the
+    permutes that follow the plan run without touching memory outside their tensors."""
+    from b2g import ops, routing
+
+    e, t, k, h = 256, 64, 8, 2048
+    g = torch.Generator().manual_seed(12)
+    idx = torch.stack([torch.randperm(e, generator=g)[:k] for _ in range(t)]).to(cuda)
+    idx[5, 3] = e
+    hidden = torch.randn(t, h, generator=g).bfloat16().to(cuda)
+    wts = torch.rand(t, k, generator=g).to(cuda)
+    ops.check_status()
+    plan = routing.build_plan(hidden, idx, wts, e)
+    out = routing.combine(plan.selected_hidden_states, plan)
+    torch.cuda.synchronize()
+    assert int(plan.group_sizes.sum()) == t * k - 1
+    for index in (plan.permutation, plan.inverse_permutation):
+        assert int(index.min()) >= 0 and int(index.max()) < t * k
+    assert int(plan.expert_indices.max()) < e and torch.isfinite(out.float()).all()
+    with pytest.raises(Exception, match="903"):
+        ops.check_status()
+    ops.check_status()
+    good = routing.build_plan(hidden, idx.clamp(max=e - 1), wts, e)          # the next plan is unaffected
+    torch.cuda.synchronize()
+    assert int(good.group_sizes.sum()) == t * k
+    ops.check_status()

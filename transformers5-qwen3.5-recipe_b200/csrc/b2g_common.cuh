@@ -52,9 +52,11 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 // Per-kernel function attributes, set once per kernel and device instead of before every launch.
 //   B2G_KERNEL_SMEM(kernel, bytes): opt in to `bytes` of dynamic shared memory.
 //   B2G_KERNEL_MAX_SHARED(kernel) : ask for the largest shared-memory partition of the SM.  The split between L1 and shared
-//     memory is an SM-wide setting that cannot change while any CTA is resident; every kernel of this library asks for the same
-//     (largest) partition, so that the GEMM, which needs nearly all of it, can start on an SM where a small copy or element-wise
-//     kernel of another stream is still resident.  None of these kernels relies on the L1 (they stream).
+//     memory is an SM-wide setting that cannot change while any CTA is resident; the kernels that run between or beside the
+//     GEMMs of an expert block (exchange copies, rank projections, factor gradients, SwiGLU, tile schedule) ask for the same
+//     (largest) partition as the GEMM, so that the GEMM, which needs nearly all of it, can start on an SM where one of them is
+//     still resident.  They stream and do not miss the L1.  The token permute kernels keep the default: they re-read rows
+//     through the L1 (a token's row is gathered once per route) and measured 10-25 % slower with the small L1.
 inline bool first_use_on_device(std::atomic<uint64_t>& seen) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;

@@ -123,7 +123,7 @@ struct Cfg {
   static constexpr int kGridRows = QT == B2G_IQ2_XXS ? 256 : (QT == B2G_IQ2_S ? 1024 : 0);   // magnitude table of the IQ2 types
   static constexpr int kOffGrid = kOffLB + kLoraBTile;
   static constexpr int kOffBar = kOffGrid + 8 * kGridRows;
-  static constexpr int kNumBars = 2 * kAStages + 2 * kBStages + 2 * kPStages + 2 + 2;
+  static constexpr int kNumBars = 2 * kAStages + 2 * kBStages + 2 * kPStages + 2 + 3;
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;                   // tmem slot, abort flag
   static constexpr int kSmemBytes = kOffMisc + 16 + 1024;                   // + alignment slack
   static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
@@ -561,17 +561,16 @@ __device__ __forceinline__ void st_global_v8(void* dst, const uint32_t (&w)[16],
 // registers.  (Staging through shared memory for wider row segments, by hand or by bulk tensor stores, and keeping the
 // next chunk's TMEM load in flight in a second register set all measured slower here.)
 template <int MODE>
-__device__ __forceinline__ void drain_tile(const Params& p, const Tile& t, uint32_t tmem_base, int rank, int q, int lane) {
-  const int nmt = t.rows > kPairRows ? 2 : 1;
+__device__ __forceinline__ void drain_block(const Params& p, const Tile& t, uint32_t tmem_base, int rank, int q, int lane, int m) {
   int seg = 0, col0;
   if (MODE == kFwd) { seg = t.ct / p.ct_per_seg; col0 = (t.ct - seg * p.ct_per_seg) * kBN; }
   else col0 = t.ct * kBN;
   const int ncols = MODE == kFwd ? p.n : p.k;
   __nv_bfloat16* outp = seg ? p.out1 : p.out0;
   const uint32_t acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-  for (int m = 0; m < nmt; ++m) {
+  {
     const int row_first = m * kPairRows + rank * kBM + q * 32;
-    if (row_first >= t.rows) break;              // uniform across the warp
+    if (row_first >= t.rows) return;             // uniform across the warp
     const bool row_ok = row_first + lane < t.rows;   // rows past a ragged expert segment belong to someone else
     __nv_bfloat16* orow = outp + static_cast<int64_t>(t.row0 + row_first + lane) * p.ldc;
 #pragma unroll 1
@@ -619,7 +618,7 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
   // barrier indices.  "Full" barriers of A / B / LoRA and "accumulator empty" are used in the pair's first CTA only.
   constexpr int kFullA = 0, kEmptyA = kFullA + C::kAStages, kFullB = kEmptyA + C::kAStages, kEmptyB = kFullB + kBStages,
                 kFullP = kEmptyB + kBStages, kEmptyP = kFullP + C::kPStages, kFullL = kEmptyP + C::kPStages, kEmptyL = kFullL + 1,
-                kAccFull = kEmptyL + 1, kAccEmpty = kAccFull + 1;
+                kAccFull = kEmptyL + 1, kAccEmpty = kAccFull + 1;   // kAccEmpty + m: accumulator of row block m drained
   auto bar = [&](int i) { return bars + 8u * i; };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + C::kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::kOffMisc + 4);
@@ -635,7 +634,8 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
     dev::mbar_init(bar(kFullL), 1);
     dev::mbar_init(bar(kEmptyL), 1);
     dev::mbar_init(bar(kAccFull), 1);
-    dev::mbar_init(bar(kAccEmpty), 8);   // four epilogue warps in each CTA
+    dev::mbar_init(bar(kAccEmpty), 8);       // four epilogue warps in each CTA, per row block
+    dev::mbar_init(bar(kAccEmpty + 1), 8);
     *abort_flag = 0;
     dev::fence_barrier_init();
     dev::fence_proxy_async_smem();
@@ -709,26 +709,56 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
       for (int item = pair; item < total_items && ok; item += num_pairs) {
         const Tile t = get_tile(p, item);
         const int nmt = t.rows > kPairRows ? 2 : 1;
+        // The two row blocks of a tile have an accumulator each, and the epilogue hands them back one after the other.  The
+        // next tile starts on row block 0 as soon as that one is free; the steps of row block 1 are deferred (at most
+        // kMaxLag of them: every deferred step keeps its A and B stage) until the epilogue has drained it, then caught up.
+        constexpr int kMaxLag = C::kAStages - 1;
         ok = dev::mbar_wait(bar(kAccEmpty), pacc ^ 1, abort_flag, p.status, 201);
         if (!ok) break;
         dev::tc_fence_after();
+        bool acc1 = false;
+        int pending = 0, lag_sa[kMaxLag], lag_sb[kMaxLag], lag_it[kMaxLag];
+        auto issue = [&](int m, int stage_a, int stage_b, int step) {
+          const uint32_t a_base = sA + stage_a * C::kAStage + m * kATile, b_base = sB + stage_b * kBStage;
+#pragma unroll
+          for (int k16 = 0; k16 < 4; ++k16) {
+            const uint64_t bdesc = MODE == kFwd ? dev::make_smem_desc(b_base + k16 * 32, 16, 1024, 2)
+                                                : dev::make_smem_desc(b_base + k16 * 2048, 8192, 1024, 2);
+            const uint64_t adesc = dev::make_smem_desc(a_base + k16 * 32, 16, 1024, 2);
+            dev::umma_bf16_pair(tmem_base + m * kBN, adesc, bdesc, idesc, (step | k16) != 0 ? 1u : 0u);
+          }
+        };
         for (int it = 0; it < p.num_iters; ++it) {
           ok = dev::mbar_wait(bar(kFullA + sa), pa, abort_flag, p.status, 202) &&
                dev::mbar_wait(bar(kFullB + sb), pb, abort_flag, p.status, 203);
           if (!ok) break;
           dev::tc_fence_after();
-          const uint32_t a_base = sA + sa * C::kAStage, b_base = sB + sb * kBStage;
-#pragma unroll
-          for (int k16 = 0; k16 < 4; ++k16) {
-            const uint64_t bdesc = MODE == kFwd ? dev::make_smem_desc(b_base + k16 * 32, 16, 1024, 2)
-                                                : dev::make_smem_desc(b_base + k16 * 2048, 8192, 1024, 2);
-            for (int m = 0; m < nmt; ++m) {
-              const uint64_t adesc = dev::make_smem_desc(a_base + m * kATile + k16 * 32, 16, 1024, 2);
-              dev::umma_bf16_pair(tmem_base + m * kBN, adesc, bdesc, idesc, (it | k16) != 0 ? 1u : 0u);
+          issue(0, sa, sb, it);
+          bool defer = false;
+          if (!acc1) {
+            if (dev::mbar_try_wait(bar(kAccEmpty + 1), pacc ^ 1)) acc1 = true;
+            else if (pending < kMaxLag && it + 1 < p.num_iters) defer = true;
+            else {
+              ok = dev::mbar_wait(bar(kAccEmpty + 1), pacc ^ 1, abort_flag, p.status, 205);
+              if (!ok) break;
+              acc1 = true;
             }
+            if (acc1) dev::tc_fence_after();
           }
-          dev::umma_commit_pair(bar(kEmptyA + sa));
-          dev::umma_commit_pair(bar(kEmptyB + sb));
+          if (defer) {
+            lag_sa[pending] = sa; lag_sb[pending] = sb; lag_it[pending] = it;
+            ++pending;
+          } else {
+            for (int d = 0; d < pending; ++d) {
+              if (nmt > 1) issue(1, lag_sa[d], lag_sb[d], lag_it[d]);
+              dev::umma_commit_pair(bar(kEmptyA + lag_sa[d]));
+              dev::umma_commit_pair(bar(kEmptyB + lag_sb[d]));
+            }
+            pending = 0;
+            if (nmt > 1) issue(1, sa, sb, it);
+            dev::umma_commit_pair(bar(kEmptyA + sa));
+            dev::umma_commit_pair(bar(kEmptyB + sb));
+          }
           if (++sa == C::kAStages) { sa = 0; pa ^= 1; }
           if (++sb == kBStages) { sb = 0; pb ^= 1; }
         }
@@ -759,10 +789,12 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
       ok = dev::mbar_wait(bar(kAccFull), pacc, abort_flag, p.status, 301);
       if (!ok) break;
       dev::tc_fence_after();
-      drain_tile<MODE>(p, t, tmem_base, static_cast<int>(rank), q, lane);
-      dev::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) dev::mbar_arrive_cluster(lead_acc_empty);
+      for (int m = 0; m < kMT; ++m) {            // a tile of one row block frees the second accumulator without reading it
+        drain_block<MODE>(p, t, tmem_base, static_cast<int>(rank), q, lane, m);
+        dev::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) dev::mbar_arrive_cluster(lead_acc_empty + 8u * m);
+      }
       pacc ^= 1;
     }
   } else if (warp == 6 + kUnpackWarps) {

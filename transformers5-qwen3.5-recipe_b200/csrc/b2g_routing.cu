@@ -455,7 +455,6 @@ extern "C" int b2g_route_gather(const void* hidden, const int64_t* perm, void* s
   const int64_t R = T * top_k;
   if (R == 0) return 0;
   B2G_REQUIRE(hidden && perm && selected && aligned16(hidden) && aligned16(selected), "null or misaligned pointer");
-  B2G_KERNEL_MAX_SHARED(gather_kernel);
   gather_kernel<<<row_grid((R + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint4*>(hidden), perm,
                                                                             static_cast<uint4*>(selected), R, top_k, H / 8);
   B2G_CUDA_OK(cudaGetLastError());
@@ -468,7 +467,6 @@ extern "C" int b2g_route_gather_bwd(const void* grad_selected, const int64_t* in
   if (T == 0) return 0;
   B2G_REQUIRE(grad_selected && inv_perm && grad_hidden && aligned16(grad_selected) && aligned16(grad_hidden),
               "null or misaligned pointer");
-  B2G_KERNEL_MAX_SHARED(gather_bwd_kernel);
   gather_bwd_kernel<<<row_grid(T), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(grad_selected), inv_perm, static_cast<uint4*>(grad_hidden), T, top_k, H / 8);
   B2G_CUDA_OK(cudaGetLastError());
@@ -482,8 +480,6 @@ extern "C" int b2g_route_combine(const void* expert_out, const void* weights, in
   if (T == 0) return 0;
   B2G_REQUIRE(expert_out && weights && inv_perm && out && aligned16(expert_out) && aligned16(out), "null or misaligned pointer");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  B2G_KERNEL_MAX_SHARED(combine_kernel<true>);
-  B2G_KERNEL_MAX_SHARED(combine_kernel<false>);
   if (w_dtype) combine_kernel<true><<<row_grid(T), 256, 0, s>>>(static_cast<const uint4*>(expert_out), weights, inv_perm,
                                                                 static_cast<uint4*>(out), T, top_k, H / 8);
   else combine_kernel<false><<<row_grid(T), 256, 0, s>>>(static_cast<const uint4*>(expert_out), weights, inv_perm,
@@ -502,8 +498,6 @@ extern "C" int b2g_route_combine_bwd(const void* expert_out, const void* weights
   B2G_REQUIRE(expert_out && weights && perm && grad_final && grad_expert_out && grad_weights, "null pointer");
   B2G_REQUIRE(aligned16(expert_out) && aligned16(grad_final) && aligned16(grad_expert_out), "misaligned pointer");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  B2G_KERNEL_MAX_SHARED(combine_bwd_kernel<true>);
-  B2G_KERNEL_MAX_SHARED(combine_bwd_kernel<false>);
   if (w_dtype) combine_bwd_kernel<true><<<row_grid((R + 7) / 8), 256, 0, s>>>(static_cast<const uint4*>(expert_out), weights, perm,
                                                                     static_cast<const uint4*>(grad_final),
                                                                     static_cast<uint4*>(grad_expert_out), grad_weights, R, top_k, H / 8);
