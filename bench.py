@@ -215,30 +215,37 @@ def moe_flops(tokens: int, g=MOE, shared: bool = False) -> float:
     return f
 
 
-def _expert_payload(dev, qtype: int, shape, seed: int):
-    """One expert's packed weight, the same bytes whichever rank builds it: N(0, 0.02) through the Q4_K encoder, or seeded
-    random valid blocks of that spread for the types without an encoder."""
+def _expert_bank(dev, qtype: int, expert_ids, num_experts: int, rows: int, cols: int, seed: int):
+    """Packed weights of the experts ``expert_ids`` (in that order), flattened.  The whole bank of ``num_experts`` experts is
+    drawn from one seeded stream in expert-id order, 32 experts at a time, and the wanted ones are kept, so that an expert has
+    the same bytes whichever rank holds it and the set-up costs a few dozen launches: N(0, 0.02) through the Q4_K encoder, or
+    seeded random valid blocks of that spread for the types without an encoder."""
     from b2g import gguf_quant
 
-    if qtype == 12:
-        g = torch.Generator(device=dev).manual_seed(seed)
-        return gguf_quant.quantize_q4_k(torch.randn(*shape, generator=g, device=dev) * 0.02)
-    return gguf_quant.random_payload(qtype, shape, seed, device=dev)
-
-
-def _expert_bank(dev, qtype: int, expert_ids, rows: int, cols: int, base_seed: int):
-    return torch.stack([_expert_payload(dev, qtype, (rows, cols), base_seed + int(e)) for e in expert_ids]).reshape(-1)
+    g = torch.Generator(device=dev).manual_seed(seed)
+    want = torch.as_tensor(list(expert_ids), dtype=torch.int64, device=dev)
+    keep = [None] * len(want)
+    for e0 in range(0, num_experts, 32):
+        n = min(32, num_experts - e0)
+        if qtype == 12:
+            chunk = gguf_quant.quantize_q4_k(torch.randn(n, rows, cols, generator=g, device=dev) * 0.02)
+        else:
+            chunk = gguf_quant.random_payload(qtype, (n, rows, cols), seed + e0, device=dev)
+        for pos, e in enumerate(want.tolist()):
+            if e0 <= e < e0 + n:
+                keep[pos] = chunk[e - e0]
+    return torch.stack(keep).reshape(-1)
 
 
 def _moe_factors(dev, expert_ids, g, seed: int, requires_grad=True):
-    out = {"gate_up_a": [], "gate_up_b": [], "down_a": [], "down_b": []}
-    for e in expert_ids:
-        gen = torch.Generator(device=dev).manual_seed(seed + int(e))
-        out["gate_up_a"].append(torch.randn(g["R"], g["H"], generator=gen, device=dev) / 16)
-        out["gate_up_b"].append(torch.randn(2 * g["I"], g["R"], generator=gen, device=dev) * 0.01)
-        out["down_a"].append(torch.randn(g["R"], g["I"], generator=gen, device=dev) / 16)
-        out["down_b"].append(torch.randn(g["H"], g["R"], generator=gen, device=dev) * 0.01)
-    return {n: torch.stack(v).bfloat16().requires_grad_(requires_grad) for n, v in out.items()}
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    e = g["E"]
+    full = {"gate_up_a": torch.randn(e, g["R"], g["H"], generator=gen, device=dev) / 16,
+            "gate_up_b": torch.randn(e, 2 * g["I"], g["R"], generator=gen, device=dev) * 0.01,
+            "down_a": torch.randn(e, g["R"], g["I"], generator=gen, device=dev) / 16,
+            "down_b": torch.randn(e, g["H"], g["R"], generator=gen, device=dev) * 0.01}
+    mine = torch.as_tensor(list(expert_ids), dtype=torch.int64, device=dev)
+    return {n: v.index_select(0, mine).bfloat16().requires_grad_(requires_grad) for n, v in full.items()}
 
 
 def _time_steps(step, steps: int, barrier) -> float:
@@ -281,7 +288,7 @@ def measure_moe(kind: str, args, dev, dist, rank: int, world: int, steps: int, w
     loads = ep_peer.rank_loads(load, placement, world)
     loads_contiguous = ep_peer.rank_loads(load, contiguous, world)
     mine = ep_peer.experts_of_rank(placement, rank, world).tolist()
-    gate_p, up_p, down_p = (_expert_bank(dev, QT, mine, I, H, 1000), _expert_bank(dev, QT, mine, I, H, 2000), _expert_bank(dev, QT, mine, H, I, 3000))
+    gate_p, up_p, down_p = (_expert_bank(dev, QT, mine, E, I, H, 1000), _expert_bank(dev, QT, mine, E, I, H, 2000), _expert_bank(dev, QT, mine, E, H, I, 3000))
     lora = _moe_factors(dev, mine, g, 4000)
     ids = torch.arange(E // world, device=dev, dtype=torch.int64)
     shared = None
