@@ -383,24 +383,26 @@ class _PeerMoe(torch.autograd.Function):
         x = xchg.recv[0]
         tiles = []
         xchg.gemm_margin(True)
-        for c, (lo, hi) in enumerate(xchg.groups):
-            cs.wait_event(ev["sent"][c])
-            first, end = xchg.group_first[c], xchg.group_end[c]
-            with _Span(xchg, "experts_forward", cs):
-                t = ops.grouped_schedule(xchg.local_ids[lo:hi], plan.local_offsets[lo:hi], cap, first)
-                if lora:
-                    ops.grouped_lora_down(x, None, gu_a_c, False, scaling, r, t, zero=False, out=(xa, xas))
-                ops.grouped_fwd(x, gate_p.reshape(-1), up_p.reshape(-1), quant_type, inter_dim, e_local, t, xas, gu_b16, out0=gate, out1=up)
-                ops.swiglu_fwd(gate, up, 0.0, first, end, out=z)
-                if lora:
-                    ops.grouped_lora_down(z, None, down_a_c, False, scaling, r, t, zero=False, out=(za, zas))
-                ops.grouped_fwd(z, down_p.reshape(-1), None, quant_type, xchg.hidden, e_local, t, zas, down_b16, out0=out_e)
-            ev["computed"][c].record(cs)
-            tiles.append(t)
-            if c + 2 < n:
-                send(c + 2)
-            bring_back(c)
-        xchg.gemm_margin(False)
+        try:
+            for c, (lo, hi) in enumerate(xchg.groups):
+                cs.wait_event(ev["sent"][c])
+                first, end = xchg.group_first[c], xchg.group_end[c]
+                with _Span(xchg, "experts_forward", cs):
+                    t = ops.grouped_schedule(xchg.local_ids[lo:hi], plan.local_offsets[lo:hi], cap, first)
+                    if lora:
+                        ops.grouped_lora_down(x, None, gu_a_c, False, scaling, r, t, zero=False, out=(xa, xas))
+                    ops.grouped_fwd(x, gate_p.reshape(-1), up_p.reshape(-1), quant_type, inter_dim, e_local, t, xas, gu_b16, out0=gate, out1=up)
+                    ops.swiglu_fwd(gate, up, 0.0, first, end, out=z)
+                    if lora:
+                        ops.grouped_lora_down(z, None, down_a_c, False, scaling, r, t, zero=False, out=(za, zas))
+                    ops.grouped_fwd(z, down_p.reshape(-1), None, quant_type, xchg.hidden, e_local, t, zas, down_b16, out0=out_e)
+                ev["computed"][c].record(cs)
+                tiles.append(t)
+                if c + 2 < n:
+                    send(c + 2)
+                bring_back(c)
+        finally:
+            xchg.gemm_margin(False)
 
         cs.wait_event(ev["returned"][-1])                 # the exchange stream is in order: the last group's return is the last
         returned = xchg.ret[0][:rows]
@@ -454,31 +456,33 @@ class _PeerMoe(torch.autograd.Function):
             send(1)
         x, d_out = xchg.recv[0], xchg.recv[1]
         xchg.gemm_margin(True)
-        for c, (lo, hi) in enumerate(xchg.groups):
-            cs.wait_event(ev["g_sent"][c])
-            first, end, t, offs = xchg.group_first[c], xchg.group_end[c], tiles[c], plan.local_offsets[lo:hi]
-            with _Span(xchg, "experts_backward", cs):
-                if lora:
-                    # down projection: dZ = dOut.deq(Wd) + s.(dOut.Bd).Ad ; dAd = s.(dOut.Bd)^T.Z ; dBd = s.dOut^T.(Z.Ad^T)
-                    ops.grouped_lora_down(d_out, None, down_bt, False, scaling, r, t, zero=False, out=(dob, dobs))
-                ops.grouped_dgrad(d_out, None, down_p.reshape(-1), None, quant_type, inter_dim, e_local, t, dobs, down_a16, out=dz)
-                if lora:
-                    ops.grouped_lora_wgrad(dob, z, scaling, r, offs, grads[2][lo:hi], False, 0, first)
-                    ops.grouped_lora_wgrad(za, d_out, scaling, r, offs, grads[3][lo:hi], True, 0, first)
-                ops.swiglu_bwd(gate, up, dz, 0.0, first, end, out=(d_gate, d_up))
-                if lora:
-                    # gate|up: dX = dG.deq(Wg) + dU.deq(Wu) + s.([dG|dU].Bgu).Agu
-                    ops.grouped_lora_down(d_gate, d_up, gu_bt, False, scaling, r, t, zero=False, out=(dgb, dgbs))
-                ops.grouped_dgrad(d_gate, d_up, gate_p.reshape(-1), up_p.reshape(-1), quant_type, hid, e_local, t, dgbs, gu_a16, out=d_sel)
-                if lora:
-                    ops.grouped_lora_wgrad(dgb, x, scaling, r, offs, grads[0][lo:hi], False, 0, first)
-                    ops.grouped_lora_wgrad(xa, d_gate, scaling, r, offs, grads[1][lo:hi], True, 0, first)
-                    ops.grouped_lora_wgrad(xa, d_up, scaling, r, offs, grads[1][lo:hi], True, inter_dim, first)
-            ev["g_computed"][c].record(cs)
-            if c + 2 < n:
-                send(c + 2)
-            bring_back(c)
-        xchg.gemm_margin(False)
+        try:
+            for c, (lo, hi) in enumerate(xchg.groups):
+                cs.wait_event(ev["g_sent"][c])
+                first, end, t, offs = xchg.group_first[c], xchg.group_end[c], tiles[c], plan.local_offsets[lo:hi]
+                with _Span(xchg, "experts_backward", cs):
+                    if lora:
+                        # down projection: dZ = dOut.deq(Wd) + s.(dOut.Bd).Ad ; dAd = s.(dOut.Bd)^T.Z ; dBd = s.dOut^T.(Z.Ad^T)
+                        ops.grouped_lora_down(d_out, None, down_bt, False, scaling, r, t, zero=False, out=(dob, dobs))
+                    ops.grouped_dgrad(d_out, None, down_p.reshape(-1), None, quant_type, inter_dim, e_local, t, dobs, down_a16, out=dz)
+                    if lora:
+                        ops.grouped_lora_wgrad(dob, z, scaling, r, offs, grads[2][lo:hi], False, 0, first)
+                        ops.grouped_lora_wgrad(za, d_out, scaling, r, offs, grads[3][lo:hi], True, 0, first)
+                    ops.swiglu_bwd(gate, up, dz, 0.0, first, end, out=(d_gate, d_up))
+                    if lora:
+                        # gate|up: dX = dG.deq(Wg) + dU.deq(Wu) + s.([dG|dU].Bgu).Agu
+                        ops.grouped_lora_down(d_gate, d_up, gu_bt, False, scaling, r, t, zero=False, out=(dgb, dgbs))
+                    ops.grouped_dgrad(d_gate, d_up, gate_p.reshape(-1), up_p.reshape(-1), quant_type, hid, e_local, t, dgbs, gu_a16, out=d_sel)
+                    if lora:
+                        ops.grouped_lora_wgrad(dgb, x, scaling, r, offs, grads[0][lo:hi], False, 0, first)
+                        ops.grouped_lora_wgrad(xa, d_gate, scaling, r, offs, grads[1][lo:hi], True, 0, first)
+                        ops.grouped_lora_wgrad(xa, d_up, scaling, r, offs, grads[1][lo:hi], True, inter_dim, first)
+                ev["g_computed"][c].record(cs)
+                if c + 2 < n:
+                    send(c + 2)
+                bring_back(c)
+        finally:
+            xchg.gemm_margin(False)
 
         cs.wait_event(ev["g_returned"][-1])
         with _Span(xchg, "gather_backward", cs):
