@@ -266,6 +266,8 @@ def measure_moe(kind: str, args, dev, dist, rank: int, world: int, steps: int, w
 
     g = DSK if kind == "deepseek" else MOE
     E, H, I, TOPK, QT = g["E"], g["H"], g["I"], g["K"], g["Q"]
+    if getattr(args, "qtype", None):
+        QT = int(args.qtype)                             # the same layer in another packed format (side measurement)
     scaling = 2.0
     limit = g.get("limit", 0.0)
     t_total = {"qwen16k": 16384, "skew64k": 65536, "deepseek": 8192}[kind]
@@ -414,7 +416,7 @@ def measure_moe(kind: str, args, dev, dist, rank: int, world: int, steps: int, w
     out = {"workload": {"qwen16k": "grouped MoE Q4_K LoRA, 256 experts top-8, hidden 2048, intermediate 512, r=16, 16384 tokens (configuration 2 of the benchmark specification)",
                         "skew64k": "the same experts, 65536 tokens in total, router logits N(0,1) + per-expert bias N(0,0.5) (configuration 4)",
                         "deepseek": "grouped MoE IQ2_XXS LoRA, 256 experts top-6, hidden 4096, intermediate 2048, r=8, clamped SwiGLU, plus the Q8_0 shared expert, 8192 tokens (configuration 3)"}[kind],
-           "n_gpus": world, "tokens_total": t_total, "scaling": "strong" if skew else "weak", "steps": steps,
+           "n_gpus": world, "tokens_total": t_total, "scaling": "strong" if skew else "weak", "steps": steps, "expert_quant_type": QT,
            "parallelism": "1 GPU" if world == 1 else f"ep{world}: {E // world} experts per GPU, peer-store dispatch / combine over NVLink, {args.chunks} expert groups pipelined on an exchange stream ({('%d TPCs of its own' % args.exchange_tpcs) if args.exchange_tpcs and args.chunks > 1 else 'sharing the SMs'}), {args.placement} placement",
            "ms_per_step": ms, "tokens_per_s": t_total / (ms * 1e-3), "step_tflops": flops / (ms * 1e-3) / 1e12,
            "frac_of_tensor_peak_all_gpus": flops / (ms * 1e-3) / 1e12 / (peak_tf * world), "peak_source": peak_src,
@@ -639,6 +641,7 @@ def main() -> int:
     ap.add_argument("--placement", default="balanced", choices=["balanced", "contiguous"],
                     help="expert-parallel MoE: experts placed over the ranks by measured load (default) or in contiguous blocks")
     ap.add_argument("--no-moe", action="store_true", help="dense workload: leave the `moe` object out")
+    ap.add_argument("--qtype", type=int, default=None, help="MoE workloads: GGML type id of the expert weights instead of the workload's own (8, 10-14, 16, 22)")
     ap.add_argument("--timeline", action="store_true", help="expert-parallel MoE: print rank 0's phase timeline of one step to stderr")
     args = ap.parse_args()
     if args.workload in ("moe", "moe64k", "moe3"):

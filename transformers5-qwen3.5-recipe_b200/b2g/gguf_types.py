@@ -71,8 +71,11 @@ except Exception:  # stock transformers, or none
             self.output_permutation = None
 
         def forward(self, x: torch.Tensor) -> torch.Tensor:
+            # a module takes strided activations like nn.Linear does (e.g. the kept positions ``hidden[:, -1:, :]``); the
+            # operator underneath does not, so the one copy is made here, where it is visible
             w = self.weight
-            y = ag.mmq(x.to(self.compute_dtype), w.as_subclass(torch.Tensor), int(w.quant_type), self.out_features)
+            x = x.to(self.compute_dtype)
+            y = ag.mmq(x if x.is_contiguous() else x.contiguous(), w.as_subclass(torch.Tensor), int(w.quant_type), self.out_features)
             return y if self.bias is None else y + self.bias.to(y.dtype)
 
     class GGUFGroupedLinear(torch.nn.Module):
