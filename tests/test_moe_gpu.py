@@ -171,3 +171,38 @@ def test_grouped_round_trip_at_config_size(cuda):
             assert torch.equal(ops.qlinear_fwd(rows, pu[ex].reshape(-1), 12, i), up[b:en])
     z0, z1 = ag.grouped_mmq_pair(torch.zeros_like(plan.selected_hidden_states), pg, pu, active, offs, 12, i)
     assert float(z0.abs().max()) == 0.0 and float(z1.abs().max()) == 0.0
+
+
+def test_tile_table_covers_every_row_once_two_row_block_tiles_first(cuda):
+    """The grouped tile table: every active expert's rows appear in exactly one tile, tiles hold at most 512 rows, all tiles of
+    more than 256 rows (both row blocks of a CTA pair) stand before all shorter ones (round-robin over the table then gives
+    every CTA pair the same mix), each class in expert order; idle experts and a first row other than 0 are honoured."""
+    from b2g import ops
+
+    rng = np.random.default_rng(31)
+    for first in (0, 37):
+        rows = rng.integers(0, 1400, size=300)
+        rows[[3, 17, 250]] = 0
+        rows[5], rows[6], rows[7] = 512, 256, 257
+        ends = first + np.cumsum(rows)
+        active = np.arange(300, dtype=np.int64) * 2 + 1          # expert ids need not be dense
+        tiles = ops.grouped_schedule(torch.from_numpy(active).to(cuda), torch.from_numpy(ends.astype(np.int32)).to(cuda), int(ends[-1]),
+                                     torch.tensor([first], dtype=torch.int32, device=cuda) if first else None)
+        ops.check_status(cuda)
+        t = tiles.cpu().numpy().reshape(-1, 4)
+        n = int(t[0, 0])
+        assert t[0, 1] == 512 and t[0, 2] == 300
+        body = t[1:1 + n]
+        assert n == int(np.sum((rows + 511) // 512))
+        tall = body[:, 2] > 256
+        n_tall = int(tall.sum())
+        assert tall[:n_tall].all() and not tall[n_tall:].any()
+        for part in (body[:n_tall], body[n_tall:]):
+            assert (np.diff(part[:, 3]) >= 0).all()                  # expert order inside a class
+        covered = np.zeros(int(ends[-1]), dtype=np.int32)
+        begins = np.concatenate(([first], ends[:-1]))
+        for e, r0, nr, g in body:
+            assert e == active[g] and 0 < nr <= 512
+            assert begins[g] <= r0 and r0 + nr <= ends[g]
+            covered[r0:r0 + nr] += 1
+        assert (covered[first:] == 1).all() and (covered[:first] == 0).all()

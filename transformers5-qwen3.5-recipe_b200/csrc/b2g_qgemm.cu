@@ -1102,51 +1102,85 @@ int check_common(const Launch& L, const char* what) {
 // Offsets are clamped to [0, total_rows] and kept monotone, and no more entries are written than the table holds, so that a
 // caller whose offsets overrun the activation matrix (an expert-parallel receive buffer that was too small) gets tiles that
 // stay inside it; status 904 reports the overrun.
+// Tiles that fill both row blocks come first, the ragged ends of at most one row block (half the MMAs, about half the time)
+// after them, each class in expert order: CTA pairs take table entries round-robin, so every pair gets the same number of
+// tiles of each class to within one, which an order by expert alone does not give (experts of about one tile of rows
+// alternate long and short entries, and the period of that pattern beats against the number of pairs).
 __global__ void __launch_bounds__(256) schedule_kernel(const int64_t* __restrict__ expert_indices, const int32_t* __restrict__ offsets,
                                                        const int32_t* __restrict__ first_row, int G, int rows_per_tile, int total_rows,
                                                        int max_tiles, int4* __restrict__ tiles, int* __restrict__ status) {
-  __shared__ int scan[256];
-  __shared__ int carry;
-  if (threadIdx.x == 0) carry = 0;
-  __syncthreads();
-  for (int g0 = 0; g0 < G; g0 += 256) {
-    const int g = g0 + threadIdx.x;
-    int begin = 0, rows = 0;
-    if (g < G) {
-      begin = g > 0 ? offsets[g - 1] : (first_row ? *first_row : 0);
-      int end = offsets[g];
-      if (end > total_rows || begin > total_rows) {
-        if (status) atomicCAS(status, 0, 904);
-        end = end > total_rows ? total_rows : end;
-        begin = begin > total_rows ? total_rows : begin;
-      }
-      if (begin < 0) begin = 0;
-      rows = end - begin;
-      if (rows < 0) rows = 0;
+  __shared__ int scan_tall[256], scan_short[256];
+  __shared__ int carry_tall, carry_short, total_tall;
+  const int half_tile = rows_per_tile / 2;
+  auto segment = [&](int g, int& begin, int& rows) {
+    begin = 0; rows = 0;
+    if (g >= G) return;
+    begin = g > 0 ? offsets[g - 1] : (first_row ? *first_row : 0);
+    int end = offsets[g];
+    if (end > total_rows || begin > total_rows) {
+      if (status) atomicCAS(status, 0, 904);
+      end = end > total_rows ? total_rows : end;
+      begin = begin > total_rows ? total_rows : begin;
     }
+    if (begin < 0) begin = 0;
+    rows = end - begin;
+    if (rows < 0) rows = 0;
+  };
+  // pass 1: how many tiles fill both row blocks
+  int mine = 0;
+  for (int g = threadIdx.x; g < G; g += 256) {
+    int begin, rows;
+    segment(g, begin, rows);
     const int nt = (rows + rows_per_tile - 1) / rows_per_tile;
-    scan[threadIdx.x] = nt;
-    __syncthreads();
-    for (int off = 1; off < 256; off <<= 1) {
-      const int add = threadIdx.x >= off ? scan[threadIdx.x - off] : 0;
-      __syncthreads();
-      scan[threadIdx.x] += add;
-      __syncthreads();
-    }
-    const int first = carry + scan[threadIdx.x] - nt;
-    if (g < G) {
-      const int e = static_cast<int>(expert_indices[g]);
-      for (int i = 0; i < nt && first + i < max_tiles; ++i) {
-        const int r0 = begin + i * rows_per_tile;
-        const int left = rows - i * rows_per_tile;
-        tiles[1 + first + i] = make_int4(e, r0, left < rows_per_tile ? left : rows_per_tile, g);
-      }
-    }
-    __syncthreads();
-    if (threadIdx.x == 255) carry += scan[255];
+    const int last = rows - (nt - 1) * rows_per_tile;
+    mine += nt - (nt > 0 && last <= half_tile ? 1 : 0);
+  }
+  scan_tall[threadIdx.x] = mine;
+  if (threadIdx.x == 0) { carry_tall = 0; carry_short = 0; }
+  __syncthreads();
+  for (int off = 128; off > 0; off >>= 1) {
+    if (threadIdx.x < off) scan_tall[threadIdx.x] += scan_tall[threadIdx.x + off];
     __syncthreads();
   }
-  if (threadIdx.x == 0) tiles[0] = make_int4(carry < max_tiles ? carry : max_tiles, rows_per_tile, G, 0);
+  if (threadIdx.x == 0) total_tall = scan_tall[0];
+  __syncthreads();
+  // pass 2: place them
+  for (int g0 = 0; g0 < G; g0 += 256) {
+    const int g = g0 + threadIdx.x;
+    int begin, rows;
+    segment(g, begin, rows);
+    const int nt = (rows + rows_per_tile - 1) / rows_per_tile;
+    const int last = rows - (nt - 1) * rows_per_tile;
+    const int n_short = nt > 0 && last <= half_tile ? 1 : 0, n_tall = nt - n_short;
+    scan_tall[threadIdx.x] = n_tall;
+    scan_short[threadIdx.x] = n_short;
+    __syncthreads();
+    for (int off = 1; off < 256; off <<= 1) {
+      const int add_t = threadIdx.x >= off ? scan_tall[threadIdx.x - off] : 0;
+      const int add_s = threadIdx.x >= off ? scan_short[threadIdx.x - off] : 0;
+      __syncthreads();
+      scan_tall[threadIdx.x] += add_t;
+      scan_short[threadIdx.x] += add_s;
+      __syncthreads();
+    }
+    if (g < G) {
+      const int e = static_cast<int>(expert_indices[g]);
+      const int first_tall = carry_tall + scan_tall[threadIdx.x] - n_tall;
+      for (int i = 0; i < n_tall && first_tall + i < max_tiles; ++i) {
+        const int left = rows - i * rows_per_tile;
+        tiles[1 + first_tall + i] = make_int4(e, begin + i * rows_per_tile, left < rows_per_tile ? left : rows_per_tile, g);
+      }
+      const int at = total_tall + carry_short + scan_short[threadIdx.x] - n_short;
+      if (n_short && at < max_tiles) tiles[1 + at] = make_int4(e, begin + (nt - 1) * rows_per_tile, last, g);
+    }
+    __syncthreads();
+    if (threadIdx.x == 255) { carry_tall += scan_tall[255]; carry_short += scan_short[255]; }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    const int total = total_tall + carry_short;
+    tiles[0] = make_int4(total < max_tiles ? total : max_tiles, rows_per_tile, G, 0);
+  }
 }
 
 }  // namespace qg
