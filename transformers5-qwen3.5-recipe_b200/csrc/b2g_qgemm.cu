@@ -904,17 +904,36 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
         const int pairsel = MODE == kFwd ? (it & 3) : (2 * static_cast<int>(rank) + sub);   // ... of the tile's 256
         RowData<QT> rd;
         load_row<QT, MODE>(sP + sp * C::kPStage, drow, pairsel, it, ct, rd);
-        ok = dev::mbar_wait(bar(kEmptyB + sb), pb ^ 1, abort_flag, p.status, 402);
-        if (!ok) break;
         const uint32_t dst = sB + sb * kBStage + static_cast<uint32_t>(sub) * 8192u + static_cast<uint32_t>(drow) * 128u;
         const uint32_t sw = static_cast<uint32_t>(drow & 7);
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t out[16];
-          decode_half<QT>(rd, pairsel, half, grid_s, out);
+        // Both halves are decoded before the wait for the B slot, so that only the eight stores follow it: when the MMAs set the
+        // pace, the slot comes free late and the decode is off the critical path.  IQ2_XXS forward keeps one half in registers
+        // at a time: its decode is a chain of table loads, and on the short tiles of a DeepSeek expert (where the unpack warps
+        // set the pace and the slot is free anyway) the second register set only costs loads in flight.
+        constexpr bool kDecodeEarly = !(QT == B2G_IQ2_XXS && MODE == kFwd);
+        if constexpr (kDecodeEarly) {
+          uint32_t out0[16], out1[16];
+          decode_half<QT>(rd, pairsel, 0, grid_s, out0);
+          decode_half<QT>(rd, pairsel, 1, grid_s, out1);
+          ok = dev::mbar_wait(bar(kEmptyB + sb), pb ^ 1, abort_flag, p.status, 402);
+          if (!ok) break;
 #pragma unroll
           for (int c = 0; c < 4; ++c)
-            dev::sts128(dst + ((static_cast<uint32_t>(4 * half + c) ^ sw) << 4), out[4 * c], out[4 * c + 1], out[4 * c + 2], out[4 * c + 3]);
+            dev::sts128(dst + ((static_cast<uint32_t>(c) ^ sw) << 4), out0[4 * c], out0[4 * c + 1], out0[4 * c + 2], out0[4 * c + 3]);
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            dev::sts128(dst + ((static_cast<uint32_t>(4 + c) ^ sw) << 4), out1[4 * c], out1[4 * c + 1], out1[4 * c + 2], out1[4 * c + 3]);
+        } else {
+          ok = dev::mbar_wait(bar(kEmptyB + sb), pb ^ 1, abort_flag, p.status, 402);
+          if (!ok) break;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            uint32_t out[16];
+            decode_half<QT>(rd, pairsel, half, grid_s, out);
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+              dev::sts128(dst + ((static_cast<uint32_t>(4 * half + c) ^ sw) << 4), out[4 * c], out[4 * c + 1], out[4 * c + 2], out[4 * c + 3]);
+          }
         }
         dev::fence_proxy_async_smem();
         __syncwarp();
