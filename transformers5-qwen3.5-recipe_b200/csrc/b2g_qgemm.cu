@@ -125,7 +125,12 @@ struct Cfg {
   static constexpr int kOffBar = kOffGrid + 8 * kGridRows;
   static constexpr int kNumBars = 2 * kAStages + 2 * kBStages + 2 * kPStages + 2 + 3;
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;                   // tmem slot, abort flag
-  static constexpr int kSmemBytes = kOffMisc + 16 + 1024;                   // + alignment slack
+  // forward only, where the budget allows: one [32 rows x 64 columns] bf16 staging tile (128B swizzle) per epilogue warp,
+  // from which finished accumulator chunks leave as bulk tensor stores
+  static constexpr int kOffStage = (kOffMisc + 16 + 1023) / 1024 * 1024;
+  static constexpr int kStageWarp = 32 * 128;
+  static constexpr bool kStaged = MODE == kFwd && kOffStage + 4 * kStageWarp + 1024 <= 232448;
+  static constexpr int kSmemBytes = kStaged ? kOffStage + 4 * kStageWarp + 1024 : kOffMisc + 16 + 1024;   // + alignment slack
   static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
 };
 
@@ -149,6 +154,7 @@ struct Params {
   const uint2* grid;  // IQ2_XXS table in global memory
   int* status;
   int wide_ok;        // output rows and row segments start on 32-byte boundaries
+  int tma_out;        // the output tensor maps are valid (forward, 16-byte aligned rows)
   uint32_t spin_limit;   // polls the unpack warps' wait for packed bytes (site 401) may take before the kernel gives up; every
                          // other wait keeps the library's limit and leaves as soon as it sees the CTA's abort flag
   int hold_weights;      // test hook: the packed-weight producer issues nothing, so the unpack warps' wait (site 401) must run out
@@ -558,8 +564,9 @@ __device__ __forceinline__ void st_global_v8(void* dst, const uint32_t (&w)[16],
 
 // Drain one TMEM lane quarter (32 rows per row block of this CTA) of a finished tile.  A TMEM load gives each lane 32
 // consecutive accumulators of ONE output row: (+ bias) -> bf16 -> two 32-byte stores, whole sectors, straight from
-// registers.  (Staging through shared memory for wider row segments, by hand or by bulk tensor stores, and keeping the
-// next chunk's TMEM load in flight in a second register set all measured slower here.)
+// registers.  This is the drain of input-gradient launches, of ragged row blocks and of short reductions; forward launches with
+// long reductions take drain_block_staged below.  (Keeping the next chunk's TMEM load in flight in a second register set, and
+// transposing in registers for 128-byte stores, both measured slower here.)
 template <int MODE>
 __device__ __forceinline__ void drain_block(const Params& p, const Tile& t, uint32_t tmem_base, int rank, int q, int lane, int m) {
   int seg = 0, col0;
@@ -602,11 +609,56 @@ __device__ __forceinline__ void drain_block(const Params& p, const Tile& t, uint
   }
 }
 
+// Forward drain through shared memory: a warp whose 32 rows all belong to the tile converts 64 accumulator columns per row,
+// writes them as one 128-byte row of its swizzled staging tile and lets one bulk tensor store carry the [32 x 64] box out.
+// The stores of the SM then move whole 128-byte lines through the copy engine instead of one 32-byte sector per lane
+// through the load/store pipe.  The staging tile is reused as soon as the previous store has READ it.
+template <int MODE>
+__device__ __forceinline__ void drain_block_staged(const Params& p, const Tile& t, uint32_t tmem_base, int rank, int q, int lane, int m,
+                                                    uint32_t stage, const CUtensorMap* tm_o0, const CUtensorMap* tm_o1) {
+  const int seg = t.ct / p.ct_per_seg, col0 = (t.ct - seg * p.ct_per_seg) * kBN;
+  const CUtensorMap* om = seg ? tm_o1 : tm_o0;
+  const uint32_t acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + m * kBN;
+  const int row_first = m * kPairRows + rank * kBM + q * 32;
+  const uint32_t srow = stage + lane * 128u, sw = static_cast<uint32_t>(lane & 7);
+#pragma unroll 1
+  for (int c = 0; c < kBN / 64; ++c) {
+    const int cbase = col0 + c * 64;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint32_t r[32];
+      dev::tmem_ld_32x32(acc + c * 64 + h * 32, r);
+      dev::tmem_ld_wait();
+      uint32_t w[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        float lo = __uint_as_float(r[2 * i]), hi = __uint_as_float(r[2 * i + 1]);
+        if (p.bias) { lo += __bfloat162float(p.bias[cbase + 32 * h + 2 * i]); hi += __bfloat162float(p.bias[cbase + 32 * h + 2 * i + 1]); }
+        w[i] = dev::pack_bf16(lo, hi);
+      }
+      if (h == 0) {                              // the previous box must have left the staging tile
+        if (lane == 0) dev::bulk_wait_read<0>();
+        __syncwarp();
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        dev::sts128(srow + ((static_cast<uint32_t>(4 * h + j) ^ sw) << 4), w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+    }
+    dev::fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      dev::tma_store_2d(om, stage, cbase, t.row0 + row_first);
+      dev::bulk_commit();
+    }
+  }
+}
+
 template <int QT, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_a1,
              const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1,
-             const __grid_constant__ CUtensorMap tm_la, const __grid_constant__ CUtensorMap tm_lb) {
+             const __grid_constant__ CUtensorMap tm_la, const __grid_constant__ CUtensorMap tm_lb,
+             const __grid_constant__ CUtensorMap tm_o0, const __grid_constant__ CUtensorMap tm_o1) {
   using C = Cfg<QT, MODE>;
   using P = Packed<QT, MODE>;
   extern __shared__ uint8_t smem_raw[];
@@ -790,13 +842,22 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
       if (!ok) break;
       dev::tc_fence_after();
       for (int m = 0; m < kMT; ++m) {            // a tile of one row block frees the second accumulator without reading it
-        drain_block<MODE>(p, t, tmem_base, static_cast<int>(rank), q, lane, m);
+        bool staged = false;
+        if constexpr (C::kStaged) {
+          // whole warps only: every one of the 32 rows inside the tile, every 64-column box inside the output
+          const int row_first = m * kPairRows + static_cast<int>(rank) * kBM + q * 32;
+          const int col_end = (t.ct % p.ct_per_seg) * kBN + kBN;
+          staged = p.tma_out && row_first + 32 <= t.rows && col_end <= p.n;
+          if (staged) drain_block_staged<MODE>(p, t, tmem_base, static_cast<int>(rank), q, lane, m, sbase + C::kOffStage + q * C::kStageWarp, &tm_o0, &tm_o1);
+        }
+        if (!staged) drain_block<MODE>(p, t, tmem_base, static_cast<int>(rank), q, lane, m);
         dev::tc_fence_before();
         __syncwarp();
         if (lane == 0) dev::mbar_arrive_cluster(lead_acc_empty + 8u * m);
       }
       pacc ^= 1;
     }
+    if (C::kStaged && lane == 0) dev::bulk_wait_all();   // the staging tile must outlive the last store's read
   } else if (warp == 6 + kUnpackWarps) {
     // ============================== packed-weight producer ==============================
     if (lane == 0 && !p.hold_weights) {
@@ -1066,6 +1127,21 @@ int launch_impl(const Launch& L) {
     }
   }
 
+  // Staged drain (forward, types whose packed slots leave 16 KB of shared memory): worth it when the reduction is long enough
+  // for the drain to run beside the next tile's MMAs and the unpack warps' shared-memory traffic (measured: +4 % at 32 steps
+  // per tile, -3 % at 8, where nothing else is in the load/store pipe and the wait for the staging tile shows).
+  CUtensorMap tm_o0 = tm_a0, tm_o1 = tm_a0;
+  p.tma_out = 0;
+  if (C::kStaged && p.wide_ok && L.n % 8 == 0 && p.num_iters >= 16) {
+    const uint64_t o_pitch = (uint64_t)p.ldc * 2;
+    if ((rc = make_tmap_2d(&tm_o0, L.out0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, L.n, L.m_total, o_pitch, 64, 32,
+                           CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+    tm_o1 = tm_o0;
+    if (L.out1 && (rc = make_tmap_2d(&tm_o1, L.out1, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, L.n, L.m_total, o_pitch, 64, 32,
+                                     CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+    p.tma_out = 1;
+  }
+
   int pairs = (sm_count() - gemm_sm_margin()) / 2;
   if (pairs < 1) pairs = 1;
   if (!L.tiles) {
@@ -1085,7 +1161,7 @@ int launch_impl(const Launch& L) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  B2G_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p, tm_a0, tm_a1, tm_w0, tm_w1, tm_la, tm_lb));
+  B2G_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p, tm_a0, tm_a1, tm_w0, tm_w1, tm_la, tm_lb, tm_o0, tm_o1));
   return 0;
 }
 
