@@ -795,6 +795,25 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
                dev::mbar_wait(bar(kFullB + sb), pb, abort_flag, p.status, 203);
           if (!ok) break;
           dev::tc_fence_after();
+          if (nmt > 1 && acc1 && pending == 0) {
+            // the common step: the two row blocks' MMAs alternate, so that consecutive instructions accumulate into
+            // different TMEM accumulators
+            const uint32_t a_base = sA + sa * C::kAStage, b_base = sB + sb * kBStage;
+#pragma unroll
+            for (int k16 = 0; k16 < 4; ++k16) {
+              const uint64_t bdesc = MODE == kFwd ? dev::make_smem_desc(b_base + k16 * 32, 16, 1024, 2)
+                                                  : dev::make_smem_desc(b_base + k16 * 2048, 8192, 1024, 2);
+#pragma unroll
+              for (int m = 0; m < 2; ++m)
+                dev::umma_bf16_pair(tmem_base + m * kBN, dev::make_smem_desc(a_base + m * kATile + k16 * 32, 16, 1024, 2), bdesc, idesc,
+                                    (it | k16) != 0 ? 1u : 0u);
+            }
+            dev::umma_commit_pair(bar(kRel + n % C::kRelBars));
+            ++n;
+            if (++sa == C::kAStages) { sa = 0; pa ^= 1; }
+            if (++sb == kBStages) { sb = 0; pb ^= 1; }
+            continue;
+          }
           issue(0, sa, sb, it);
           bool defer = false;
           if (!acc1) {
