@@ -39,7 +39,7 @@ SEED = 19260817 + 1
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum of one qgemm_kernel<Q4_K, forward> launch at N=4096, K=2048, keyed by M
 # (ncu captures summarised under profiles/)
-DRAM_TRAFFIC_BYTES = {16384: 156.9e6, 32768: 359.4e6}
+DRAM_TRAFFIC_BYTES = {16384: 157.8e6, 32768: 359.6e6}
 
 
 def flops_per_step(m: int) -> float:
