@@ -148,6 +148,12 @@ def test_swiglu_forward_backward(cuda):
         z = ops.swiglu_fwd(gate.to(cuda), up.to(cuda), limit)
         dg, du = ops.swiglu_bwd(gate.to(cuda), up.to(cuda), dz.to(cuda), limit)
         assert dense_ref.rel_l2(z, zr) < 2e-3 and dense_ref.rel_l2(du, ur.grad) < 4e-3 and dense_ref.rel_l2(dg, gr.grad) < 1e-2
+        # the pair-at-a-time form (a width that is no multiple of eight values) gives the same bits as the 16-byte form
+        narrow = slice(0, 6)
+        zn = ops.swiglu_fwd(gate[:, narrow].contiguous().to(cuda), up[:, narrow].contiguous().to(cuda), limit)
+        dgn, dun = ops.swiglu_bwd(gate[:, narrow].contiguous().to(cuda), up[:, narrow].contiguous().to(cuda),
+                                  dz[:, narrow].contiguous().to(cuda), limit)
+        assert torch.equal(zn, z[:, narrow]) and torch.equal(dgn, dg[:, narrow]) and torch.equal(dun, du[:, narrow])
 
 
 def test_an_expert_id_outside_the_expert_count_is_reported_and_contained(cuda):

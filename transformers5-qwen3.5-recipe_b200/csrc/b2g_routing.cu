@@ -325,25 +325,64 @@ __device__ __forceinline__ void live_pairs(int64_t npairs, const int32_t* row_be
   if (last > npairs) last = npairs;
 }
 
+__device__ __forceinline__ uint32_t swiglu_fwd_pair(uint32_t g2, uint32_t u2, float limit) {
+  float g[2] = {dev::bf16_lo(g2), dev::bf16_hi(g2)}, u[2] = {dev::bf16_lo(u2), dev::bf16_hi(u2)}, o[2];
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    if (limit > 0.f) { g[k] = fminf(g[k], limit); u[k] = fminf(fmaxf(u[k], -limit), limit); }
+    const float act = dev::round_bf16(g[k] * sigmoidf_(g[k]));
+    o[k] = act * u[k];
+  }
+  return dev::pack_bf16(o[0], o[1]);
+}
+
+__device__ __forceinline__ void swiglu_bwd_pair(uint32_t g2, uint32_t u2, uint32_t d2, float limit, uint32_t& dg2, uint32_t& du2) {
+  const float g[2] = {dev::bf16_lo(g2), dev::bf16_hi(g2)}, u[2] = {dev::bf16_lo(u2), dev::bf16_hi(u2)};
+  const float d[2] = {dev::bf16_lo(d2), dev::bf16_hi(d2)};
+  float og[2], ou[2];
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    float gc = g[k], uc = u[k];
+    bool g_pass = true, u_pass = true;
+    if (limit > 0.f) {
+      g_pass = g[k] <= limit; u_pass = (u[k] >= -limit) && (u[k] <= limit);
+      gc = fminf(gc, limit); uc = fminf(fmaxf(uc, -limit), limit);
+    }
+    const float sig = sigmoidf_(gc);
+    const float act = dev::round_bf16(gc * sig);
+    const float dact = dev::round_bf16(d[k] * uc);
+    ou[k] = u_pass ? d[k] * act : 0.f;
+    og[k] = g_pass ? dact * (sig * (1.0f + gc * (1.0f - sig))) : 0.f;
+  }
+  dg2 = dev::pack_bf16(og[0], og[1]);
+  du2 = dev::pack_bf16(ou[0], ou[1]);
+}
+
+// kVec: every thread moves 16 bytes (four bf16 pairs) per operand and step; the host picks it when the live range and the
+// pointers allow it (they do for every expert width in use), else the pair-at-a-time form.
+template <bool kVec>
 __global__ void __launch_bounds__(256) swiglu_fwd_kernel(const uint32_t* __restrict__ gate, const uint32_t* __restrict__ up,
                                                          uint32_t* __restrict__ z, int64_t npairs, float limit,
                                                          const int32_t* __restrict__ row_begin, const int32_t* __restrict__ row_end,
                                                          int64_t pairs_per_row) {
   int64_t first, last;
   live_pairs(npairs, row_begin, row_end, pairs_per_row, first, last);
-  for (int64_t i = first + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < last; i += (int64_t)gridDim.x * blockDim.x) {
-    const uint32_t g2 = gate[i], u2 = up[i];
-    float g[2] = {dev::bf16_lo(g2), dev::bf16_hi(g2)}, u[2] = {dev::bf16_lo(u2), dev::bf16_hi(u2)}, o[2];
-#pragma unroll
-    for (int k = 0; k < 2; ++k) {
-      if (limit > 0.f) { g[k] = fminf(g[k], limit); u[k] = fminf(fmaxf(u[k], -limit), limit); }
-      const float act = dev::round_bf16(g[k] * sigmoidf_(g[k]));
-      o[k] = act * u[k];
+  if (kVec) {
+    const uint4* g4 = reinterpret_cast<const uint4*>(gate);
+    const uint4* u4 = reinterpret_cast<const uint4*>(up);
+    uint4* z4 = reinterpret_cast<uint4*>(z);
+    for (int64_t i = first / 4 + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < last / 4; i += (int64_t)gridDim.x * blockDim.x) {
+      const uint4 g = g4[i], u = u4[i];
+      z4[i] = make_uint4(swiglu_fwd_pair(g.x, u.x, limit), swiglu_fwd_pair(g.y, u.y, limit), swiglu_fwd_pair(g.z, u.z, limit),
+                         swiglu_fwd_pair(g.w, u.w, limit));
     }
-    z[i] = dev::pack_bf16(o[0], o[1]);
+    return;
   }
+  for (int64_t i = first + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < last; i += (int64_t)gridDim.x * blockDim.x)
+    z[i] = swiglu_fwd_pair(gate[i], up[i], limit);
 }
 
+template <bool kVec>
 __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const uint32_t* __restrict__ gate, const uint32_t* __restrict__ up,
                                                          const uint32_t* __restrict__ dz, uint32_t* __restrict__ dgate,
                                                          uint32_t* __restrict__ dup, int64_t npairs, float limit,
@@ -351,27 +390,29 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const uint32_t* __restr
                                                          int64_t pairs_per_row) {
   int64_t first, last;
   live_pairs(npairs, row_begin, row_end, pairs_per_row, first, last);
-  for (int64_t i = first + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < last; i += (int64_t)gridDim.x * blockDim.x) {
-    const uint32_t g2 = gate[i], u2 = up[i], d2 = dz[i];
-    const float g[2] = {dev::bf16_lo(g2), dev::bf16_hi(g2)}, u[2] = {dev::bf16_lo(u2), dev::bf16_hi(u2)};
-    const float d[2] = {dev::bf16_lo(d2), dev::bf16_hi(d2)};
-    float og[2], ou[2];
-#pragma unroll
-    for (int k = 0; k < 2; ++k) {
-      float gc = g[k], uc = u[k];
-      bool g_pass = true, u_pass = true;
-      if (limit > 0.f) {
-        g_pass = g[k] <= limit; u_pass = (u[k] >= -limit) && (u[k] <= limit);
-        gc = fminf(gc, limit); uc = fminf(fmaxf(uc, -limit), limit);
-      }
-      const float sig = sigmoidf_(gc);
-      const float act = dev::round_bf16(gc * sig);
-      const float dact = dev::round_bf16(d[k] * uc);
-      ou[k] = u_pass ? d[k] * act : 0.f;
-      og[k] = g_pass ? dact * (sig * (1.0f + gc * (1.0f - sig))) : 0.f;
+  if (kVec) {
+    const uint4* g4 = reinterpret_cast<const uint4*>(gate);
+    const uint4* u4 = reinterpret_cast<const uint4*>(up);
+    const uint4* d4 = reinterpret_cast<const uint4*>(dz);
+    uint4* dg4 = reinterpret_cast<uint4*>(dgate);
+    uint4* du4 = reinterpret_cast<uint4*>(dup);
+    for (int64_t i = first / 4 + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < last / 4; i += (int64_t)gridDim.x * blockDim.x) {
+      const uint4 g = g4[i], u = u4[i], d = d4[i];
+      uint4 og, ou;
+      swiglu_bwd_pair(g.x, u.x, d.x, limit, og.x, ou.x);
+      swiglu_bwd_pair(g.y, u.y, d.y, limit, og.y, ou.y);
+      swiglu_bwd_pair(g.z, u.z, d.z, limit, og.z, ou.z);
+      swiglu_bwd_pair(g.w, u.w, d.w, limit, og.w, ou.w);
+      dg4[i] = og;
+      du4[i] = ou;
     }
-    dgate[i] = dev::pack_bf16(og[0], og[1]);
-    dup[i] = dev::pack_bf16(ou[0], ou[1]);
+    return;
+  }
+  for (int64_t i = first + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < last; i += (int64_t)gridDim.x * blockDim.x) {
+    uint32_t og, ou;
+    swiglu_bwd_pair(gate[i], up[i], dz[i], limit, og, ou);
+    dgate[i] = og;
+    dup[i] = ou;
   }
 }
 
@@ -516,10 +557,19 @@ extern "C" int b2g_swiglu_fwd(const void* gate, const void* up, void* z, int64_t
   if (n == 0) return 0;
   B2G_REQUIRE(gate && up && z, "null pointer");
   const int64_t pairs = n / 2;
-  const int64_t want = (pairs + 255) / 256, cap = (int64_t)sm_count() * 16;
-  B2G_KERNEL_MAX_SHARED(swiglu_fwd_kernel);
-  swiglu_fwd_kernel<<<(int)(want < cap ? want : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint32_t*>(gate), static_cast<const uint32_t*>(up), static_cast<uint32_t*>(z), pairs, limit, row_begin, row_end, cols / 2);
+  const bool vec = pairs % 4 == 0 && aligned16(gate) && aligned16(up) && aligned16(z) && (row_begin == nullptr && row_end == nullptr ? true : cols % 8 == 0);
+  const int64_t want = ((vec ? pairs / 4 : pairs) + 255) / 256, cap = (int64_t)sm_count() * 16;
+  const int grid = (int)(want < cap ? want : cap);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (vec) {
+    B2G_KERNEL_MAX_SHARED(swiglu_fwd_kernel<true>);
+    swiglu_fwd_kernel<true><<<grid, 256, 0, st>>>(static_cast<const uint32_t*>(gate), static_cast<const uint32_t*>(up), static_cast<uint32_t*>(z),
+                                                  pairs, limit, row_begin, row_end, cols / 2);
+  } else {
+    B2G_KERNEL_MAX_SHARED(swiglu_fwd_kernel<false>);
+    swiglu_fwd_kernel<false><<<grid, 256, 0, st>>>(static_cast<const uint32_t*>(gate), static_cast<const uint32_t*>(up), static_cast<uint32_t*>(z),
+                                                   pairs, limit, row_begin, row_end, cols / 2);
+  }
   B2G_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -532,11 +582,22 @@ extern "C" int b2g_swiglu_bwd(const void* gate, const void* up, const void* dz, 
   if (n == 0) return 0;
   B2G_REQUIRE(gate && up && dz && dgate && dup, "null pointer");
   const int64_t pairs = n / 2;
-  const int64_t want = (pairs + 255) / 256, cap = (int64_t)sm_count() * 16;
-  B2G_KERNEL_MAX_SHARED(swiglu_bwd_kernel);
-  swiglu_bwd_kernel<<<(int)(want < cap ? want : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint32_t*>(gate), static_cast<const uint32_t*>(up), static_cast<const uint32_t*>(dz),
-      static_cast<uint32_t*>(dgate), static_cast<uint32_t*>(dup), pairs, limit, row_begin, row_end, cols / 2);
+  const bool vec = pairs % 4 == 0 && aligned16(gate) && aligned16(up) && aligned16(dz) && aligned16(dgate) && aligned16(dup) &&
+                   (row_begin == nullptr && row_end == nullptr ? true : cols % 8 == 0);
+  const int64_t want = ((vec ? pairs / 4 : pairs) + 255) / 256, cap = (int64_t)sm_count() * 16;
+  const int grid = (int)(want < cap ? want : cap);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (vec) {
+    B2G_KERNEL_MAX_SHARED(swiglu_bwd_kernel<true>);
+    swiglu_bwd_kernel<true><<<grid, 256, 0, st>>>(static_cast<const uint32_t*>(gate), static_cast<const uint32_t*>(up),
+                                                  static_cast<const uint32_t*>(dz), static_cast<uint32_t*>(dgate),
+                                                  static_cast<uint32_t*>(dup), pairs, limit, row_begin, row_end, cols / 2);
+  } else {
+    B2G_KERNEL_MAX_SHARED(swiglu_bwd_kernel<false>);
+    swiglu_bwd_kernel<false><<<grid, 256, 0, st>>>(static_cast<const uint32_t*>(gate), static_cast<const uint32_t*>(up),
+                                                   static_cast<const uint32_t*>(dz), static_cast<uint32_t*>(dgate),
+                                                   static_cast<uint32_t*>(dup), pairs, limit, row_begin, row_end, cols / 2);
+  }
   B2G_CUDA_OK(cudaGetLastError());
   return 0;
 }
