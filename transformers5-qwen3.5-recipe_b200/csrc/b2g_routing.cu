@@ -199,13 +199,14 @@ __global__ void __launch_bounds__(256) gather_kernel(const uint4* __restrict__ h
   }
 }
 
-__device__ __forceinline__ void add_round8(float (&acc)[8], const uint4 g) {
-  const uint32_t w[4] = {g.x, g.y, g.z, g.w};
+// acc += g on eight bf16 values, each sum rounded to bf16 (round to nearest even): the packed bf16 add is the exactly rounded
+// sum, which is what adding in fp32 and rounding gives for bf16 operands (the fp32 sum is exact unless the exponents are more
+// than 16 apart, and then both forms return the larger operand).
+__device__ __forceinline__ void add_round8(uint4& acc, const uint4 g) {
+  const __nv_bfloat162* gv = reinterpret_cast<const __nv_bfloat162*>(&g);
+  __nv_bfloat162* av = reinterpret_cast<__nv_bfloat162*>(&acc);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    acc[2 * i] = dev::round_bf16(acc[2 * i] + dev::bf16_lo(w[i]));
-    acc[2 * i + 1] = dev::round_bf16(acc[2 * i + 1] + dev::bf16_hi(w[i]));
-  }
+  for (int i = 0; i < 4; ++i) av[i] = __hadd2(av[i], gv[i]);
 }
 
 __global__ void __launch_bounds__(256) gather_bwd_kernel(const uint4* __restrict__ grad_sel, const int64_t* __restrict__ inv,
@@ -221,14 +222,15 @@ __global__ void __launch_bounds__(256) gather_bwd_kernel(const uint4* __restrict
       for (int b = a; b > 0; --b)
         if (pos[b] < pos[b - 1]) { const int64_t x = pos[b]; pos[b] = pos[b - 1]; pos[b - 1] = x; }
     for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
-      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      uint4 rows[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j)
-        if (j < top_k) add_round8(acc, grad_sel[pos[j] * vec_per_row + v]);
-      uint4 o;
-      o.x = dev::pack_bf16(acc[0], acc[1]); o.y = dev::pack_bf16(acc[2], acc[3]);
-      o.z = dev::pack_bf16(acc[4], acc[5]); o.w = dev::pack_bf16(acc[6], acc[7]);
-      grad_hidden[t * vec_per_row + v] = o;
+        if (j < top_k) rows[j] = grad_sel[pos[j] * vec_per_row + v];
+      uint4 acc = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (j < top_k) add_round8(acc, rows[j]);
+      grad_hidden[t * vec_per_row + v] = acc;
     }
   }
 }
@@ -252,11 +254,15 @@ __global__ void __launch_bounds__(256) combine_kernel(const uint4* __restrict__ 
       w[j] = j < top_k ? load_weight_bf16<kW32>(weights, t * top_k + j) : 0.f;
     }
     for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
+      uint4 rows[8];                              // all of a token's rows in flight before the first FMA
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (j < top_k) rows[j] = expert_out[pos[j] * vec_per_row + v];
       float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         if (j < top_k) {
-          const uint4 g = expert_out[pos[j] * vec_per_row + v];
+          const uint4 g = rows[j];
           const uint32_t q[4] = {g.x, g.y, g.z, g.w};
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
