@@ -293,19 +293,28 @@ __global__ void __launch_bounds__(256) combine_bwd_kernel(const uint4* __restric
     const int64_t tok = route / top_k;
     const float w = load_weight_bf16<kW32>(weights, route);
     float dot = 0.f;
-    for (int v = lane; v < vec_per_row; v += 32) {
-      const uint4 g = grad_final[tok * vec_per_row + v];
-      const uint4 y = expert_out[s * vec_per_row + v];
-      const uint32_t gq[4] = {g.x, g.y, g.z, g.w}, yq[4] = {y.x, y.y, y.z, y.w};
-      uint32_t oq[4];
+    for (int v0 = lane; v0 < vec_per_row; v0 += 128) {   // four vectors of each operand in flight per lane
+      uint4 gs[4], ys[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float g0 = dev::bf16_lo(gq[i]), g1 = dev::bf16_hi(gq[i]);
-        oq[i] = dev::pack_bf16(__fmul_rn(g0, w), __fmul_rn(g1, w));
-        dot = fmaf(g0, dev::bf16_lo(yq[i]), dot);
-        dot = fmaf(g1, dev::bf16_hi(yq[i]), dot);
+      for (int u = 0; u < 4; ++u) {
+        const int v = v0 + 32 * u;
+        if (v < vec_per_row) { gs[u] = grad_final[tok * vec_per_row + v]; ys[u] = expert_out[s * vec_per_row + v]; }
       }
-      grad_out[s * vec_per_row + v] = make_uint4(oq[0], oq[1], oq[2], oq[3]);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int v = v0 + 32 * u;
+        if (v >= vec_per_row) break;
+        const uint32_t gq[4] = {gs[u].x, gs[u].y, gs[u].z, gs[u].w}, yq[4] = {ys[u].x, ys[u].y, ys[u].z, ys[u].w};
+        uint32_t oq[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float g0 = dev::bf16_lo(gq[i]), g1 = dev::bf16_hi(gq[i]);
+          oq[i] = dev::pack_bf16(__fmul_rn(g0, w), __fmul_rn(g1, w));
+          dot = fmaf(g0, dev::bf16_lo(yq[i]), dot);
+          dot = fmaf(g1, dev::bf16_hi(yq[i]), dot);
+        }
+        grad_out[s * vec_per_row + v] = make_uint4(oq[0], oq[1], oq[2], oq[3]);
+      }
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xFFFFFFFFu, dot, off);
