@@ -199,6 +199,106 @@ __global__ void __launch_bounds__(128) lora_down_kernel(const __nv_bfloat16* __r
 }
 
 // ------------------------------------------------------------------------------------------------
+// The same projection with the tiles brought in by TMA (weights given as [r, C], C a multiple of 64): one producer lane keeps
+// a ring of [64 rows x 128 columns] activation tiles and [16 x 128] weight slices full across slice and item boundaries, the
+// four MMA warps meet it only through mbarriers (no CTA-wide barrier anywhere), and nobody computes addresses or
+// predicates per 16 bytes.  Tiles are two 128B-swizzled boxes of 64 columns each; rows past the matrix and columns past C arrive
+// as zeros, rows past a ragged segment are computed and not stored, and rank rows >= r (another expert's, or zeros) are masked
+// at the store.
+// ------------------------------------------------------------------------------------------------
+constexpr int kDtStages = 4;
+constexpr int kDtXHalf = kDownRows * 128, kDtWHalf = kRankPad * 128;            // 8192, 2048 bytes
+constexpr int kDtStageBytes = 2 * kDtXHalf + 2 * kDtWHalf;                        // 20480
+constexpr int kDtSmemBytes = kDtStages * kDtStageBytes + 2 * kDtStages * 8 + 16 + 1024;
+
+__global__ void __launch_bounds__(160) lora_down_tma_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__ CUtensorMap tm_x1,
+                                                            const __grid_constant__ CUtensorMap tm_w, int nseg, float scale,
+                                                            const int4* __restrict__ tiles, __nv_bfloat16* __restrict__ out_plain,
+                                                            __nv_bfloat16* __restrict__ out_scaled, int64_t m_total, int C, int r,
+                                                            int dense_rows) {
+  extern __shared__ uint8_t sm_raw[];
+  uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(sm_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const uint32_t sbase = dev::smem_u32(sm);
+  const uint32_t bars = sbase + kDtStages * kDtStageBytes;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + kDtStages * kDtStageBytes + 2 * kDtStages * 8);
+  auto full = [&](int i) { return bars + 8u * i; };
+  auto empty = [&](int i) { return bars + 8u * (kDtStages + i); };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kDtStages; ++i) { dev::mbar_init(full(i), 1); dev::mbar_init(empty(i), 4); }
+    *abort_flag = 0;
+    dev::fence_barrier_init();
+    dev::fence_proxy_async_smem();
+  }
+  __syncthreads();
+  const int chunks = (C + kDownBK - 1) / kDownBK, total_chunks = nseg * chunks;
+  const int total_items = tiles ? tiles[0].x * (tiles[0].y / kDownRows) : (int)gridDim.x * ((dense_rows + kDownRows - 1) / kDownRows);
+  int st = 0, ph = 0;
+  if (warp == 4) {
+    if (lane == 0) {
+      for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+        const Seg s = down_segment(tiles, m_total, item, dense_rows);
+        if (s.rows <= 0) continue;
+        for (int ch = 0; ch < total_chunks; ++ch) {
+          const int seg = ch / chunks, c0 = (ch - seg * chunks) * kDownBK;
+          if (!dev::mbar_wait(empty(st), ph ^ 1, abort_flag, nullptr, 0)) return;
+          dev::mbar_arrive_expect_tx(full(st), kDtStageBytes);
+          const uint32_t dst = sbase + st * kDtStageBytes;
+          const CUtensorMap* xm = seg ? &tm_x1 : &tm_x0;
+          dev::tma_load_2d(dst, xm, full(st), c0, s.row0);
+          dev::tma_load_2d(dst + kDtXHalf, xm, full(st), c0 + 64, s.row0);
+          dev::tma_load_2d(dst + 2 * kDtXHalf, &tm_w, full(st), seg * C + c0, s.expert * r);
+          dev::tma_load_2d(dst + 2 * kDtXHalf + kDtWHalf, &tm_w, full(st), seg * C + c0 + 64, s.expert * r);
+          if (++st == kDtStages) { st = 0; ph ^= 1; }
+        }
+      }
+    }
+    return;
+  }
+  // ---- MMA warps: 16 rows each -------------------------------------------------------------------
+  const int arow = warp * 16 + (lane & 15);                       // this lane's row of the activation tile (ldmatrix address)
+  const uint32_t a_off = arow * 128u, a_sw = static_cast<uint32_t>(arow & 7), a_k = static_cast<uint32_t>(lane >> 4);
+  const int wrow = (lane & 7) + ((lane >> 4) << 3);               // rank row of the weight slice
+  const uint32_t w_off = wrow * 128u, w_sw = static_cast<uint32_t>(wrow & 7), w_k = static_cast<uint32_t>((lane >> 3) & 1);
+  for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+    const Seg s = down_segment(tiles, m_total, item, dense_rows);
+    if (s.rows <= 0) continue;
+    float acc[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+    for (int ch = 0; ch < total_chunks; ++ch) {
+      if (!dev::mbar_wait(full(st), ph, abort_flag, nullptr, 0)) return;
+      const uint32_t xt = sbase + st * kDtStageBytes, wt = xt + 2 * kDtXHalf;
+#pragma unroll
+      for (int kk = 0; kk < kDownBK / 16; ++kk) {
+        const uint32_t h = kk >> 2, j = 2u * (kk & 3);             // 64-column half, first 16-byte chunk of this k-slice in it
+        uint32_t a[4], b[4];
+        ldmatrix_x4(xt + h * kDtXHalf + a_off + (((j + a_k) ^ a_sw) << 4), a);
+        ldmatrix_x4(wt + h * kDtWHalf + w_off + (((j + w_k) ^ w_sw) << 4), b);
+        mma_bf16(acc[0], a, b[0], b[1]);
+        mma_bf16(acc[1], a, b[2], b[3]);
+      }
+      __syncwarp();
+      if (lane == 0) dev::mbar_arrive(empty(st));
+      if (++st == kDtStages) { st = 0; ph ^= 1; }
+    }
+    // store: thread holds rows g and g+8, columns nt*8 + 2*(lane%4) + {0,1}; rank columns >= r are zero by definition
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int row = warp * 16 + (lane >> 2) + half * 8;
+      if (row < s.rows) {
+        const int64_t o = (int64_t)(s.row0 + row) * kRankPad;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          const int col = nt * 8 + (lane & 3) * 2;
+          const float v0 = col < r ? acc[nt][half * 2] : 0.f, v1 = col + 1 < r ? acc[nt][half * 2 + 1] : 0.f;
+          if (out_plain) *reinterpret_cast<uint32_t*>(out_plain + o + col) = dev::pack_bf16(v0, v1);
+          if (out_scaled) *reinterpret_cast<uint32_t*>(out_scaled + o + col) = dev::pack_bf16(v0 * scale, v1 * scale);
+        }
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // Factor gradient: G[16, 128-column chunk] = S[rows,16]^T . T[rows, chunk] over one row segment.
 // CTA = 4 warps x 32 columns; rows stream in steps of 64 through a 4-stage cp.async ring.
 //   kPartial = true : dense path, segment = one split of M, fp32 partial to the workspace
@@ -378,7 +478,7 @@ inline int wgrad_splits(int64_t M, int64_t C) {
 using namespace b2g;
 
 static int lora_down_launch(const void* x, const void* x1, const void* w, int w_is_cr, float scale, const int32_t* tiles, void* out_plain,
-                            void* out_scaled, int64_t M, int64_t C, int r, void* stream, const char* what) {
+                            void* out_scaled, int64_t M, int64_t C, int r, int num_experts, void* stream, const char* what) {
   B2G_REQUIRE(r >= 1 && r <= lora::kRankPad, "%s: rank %d outside 1..16", what, r);
   B2G_REQUIRE(C > 0 && C % 8 == 0, "%s: reduction width %lld must be a multiple of 8", what, (long long)C);
   B2G_REQUIRE(M >= 0 && M < (1ll << 31), "%s: bad row count", what);
@@ -403,7 +503,21 @@ static int lora_down_launch(const void* x, const void* x1, const void* w, int w_
   auto* op = static_cast<__nv_bfloat16*>(out_plain);
   auto* os = static_cast<__nv_bfloat16*>(out_scaled);
   auto* tl = reinterpret_cast<const int4*>(tiles);
-  if (w_is_cr) {
+  if (!w_is_cr && C % 64 == 0) {
+    // TMA-fed form.  Tensor maps: activations [M, C], weights [experts * r, nseg * C].
+    const int nseg = x1 ? 2 : 1;
+    CUtensorMap tm_x0, tm_x1, tm_w;
+    int rc;
+    if ((rc = make_tmap_2d(&tm_x0, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)C, (uint64_t)M, (uint64_t)C * 2, 64, lora::kDownRows,
+                           CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+    tm_x1 = tm_x0;
+    if (x1 && (rc = make_tmap_2d(&tm_x1, x1, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)C, (uint64_t)M, (uint64_t)C * 2, 64,
+                                 lora::kDownRows, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+    if ((rc = make_tmap_2d(&tm_w, w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)nseg * C, (uint64_t)num_experts * r,
+                           (uint64_t)nseg * C * 2, 64, lora::kRankPad, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+    B2G_KERNEL_SMEM(lora::lora_down_tma_kernel, lora::kDtSmemBytes);
+    lora::lora_down_tma_kernel<<<grid, 160, lora::kDtSmemBytes, s>>>(tm_x0, tm_x1, tm_w, nseg, scale, tl, op, os, M, (int)C, r, dense_rows);
+  } else if (w_is_cr) {
     B2G_KERNEL_SMEM(lora::lora_down_kernel<true>, smem);
     lora::lora_down_kernel<true><<<grid, 128, smem, s>>>(xb, x1b, wb, scale, tl, op, os, M, (int)C, r, dense_rows);
   } else {
@@ -416,13 +530,13 @@ static int lora_down_launch(const void* x, const void* x1, const void* w, int w_
 
 extern "C" int b2g_lora_down(const void* x, const void* w, int w_is_cr, float scale, void* out_plain, void* out_scaled, int64_t M,
                              int64_t C, int r, void* stream) {
-  return lora_down_launch(x, nullptr, w, w_is_cr, scale, nullptr, out_plain, out_scaled, M, C, r, stream, "lora_down");
+  return lora_down_launch(x, nullptr, w, w_is_cr, scale, nullptr, out_plain, out_scaled, M, C, r, 1, stream, "lora_down");
 }
 
 extern "C" int b2g_grouped_lora_down(const void* x, const void* x1, const void* w, int w_is_cr, float scale, const int32_t* tiles,
                                      void* out_plain, void* out_scaled, int64_t R, int64_t C, int r, int num_experts, void* stream) {
   B2G_REQUIRE(tiles != nullptr && num_experts >= 1, "grouped_lora_down: tile table missing");
-  return lora_down_launch(x, x1, w, w_is_cr, scale, tiles, out_plain, out_scaled, R, C, r, stream, "grouped_lora_down");
+  return lora_down_launch(x, x1, w, w_is_cr, scale, tiles, out_plain, out_scaled, R, C, r, num_experts, stream, "grouped_lora_down");
 }
 
 extern "C" int64_t b2g_lora_wgrad_workspace_bytes(int64_t M, int64_t C) {
