@@ -409,6 +409,97 @@ __global__ void __launch_bounds__(128) lora_wgrad_kernel(const __nv_bfloat16* __
   }
 }
 
+// The dense factor gradient with the tiles brought in by TMA: a split is a whole number of 64-row steps (only the last one can
+// run past the matrix, and rows past it arrive as zeros in S and T alike, so they add nothing), one producer lane keeps a ring of
+// [64 x 128] T tiles (two 128B-swizzled boxes) and [64 x 16] S tiles (32B swizzle) full, and the four MMA warps meet it only
+// through mbarriers.  Same fragments, same order and same partials as lora_wgrad_kernel<true>.
+constexpr int kWtStages = 4;
+constexpr int kWtTHalf = kWgRows * 128, kWtS = kWgRows * 32;                    // 8192, 2048 bytes
+constexpr int kWtStageBytes = 2 * kWtTHalf + kWtS;                                // 18432
+constexpr int kWtSmemBytes = kWtStages * kWtStageBytes + 2 * kWtStages * 8 + 16 + 1024;
+
+__global__ void __launch_bounds__(160) lora_wgrad_tma_kernel(const __grid_constant__ CUtensorMap tm_s, const __grid_constant__ CUtensorMap tm_t,
+                                                             int64_t m_total, int rows_per_split, int C, float* __restrict__ partial) {
+  extern __shared__ uint8_t sm_raw[];
+  uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(sm_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const uint32_t sbase = dev::smem_u32(sm);
+  const uint32_t bars = sbase + kWtStages * kWtStageBytes;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + kWtStages * kWtStageBytes + 2 * kWtStages * 8);
+  auto full = [&](int i) { return bars + 8u * i; };
+  auto empty = [&](int i) { return bars + 8u * (kWtStages + i); };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kWtStages; ++i) { dev::mbar_init(full(i), 1); dev::mbar_init(empty(i), 4); }
+    *abort_flag = 0;
+    dev::fence_barrier_init();
+    dev::fence_proxy_async_smem();
+  }
+  __syncthreads();
+  const int chunk = blockIdx.x, segi = blockIdx.y;
+  const int c0 = chunk * kWgCols;
+  const int64_t row0 = (int64_t)segi * rows_per_split;
+  int64_t rows = m_total - row0 < rows_per_split ? m_total - row0 : rows_per_split;
+  if (rows < 0) rows = 0;
+  const int steps = (int)((rows + kWgRows - 1) / kWgRows);
+  if (warp == 4) {
+    if (lane == 0) {
+      int st = 0, ph = 0;
+      for (int i = 0; i < steps; ++i) {
+        if (!dev::mbar_wait(empty(st), ph ^ 1, abort_flag, nullptr, 0)) return;
+        dev::mbar_arrive_expect_tx(full(st), kWtStageBytes);
+        const uint32_t dst = sbase + st * kWtStageBytes;
+        const int y = (int)(row0 + (int64_t)i * kWgRows);
+        dev::tma_load_2d(dst, &tm_t, full(st), c0, y);
+        dev::tma_load_2d(dst + kWtTHalf, &tm_t, full(st), c0 + 64, y);
+        dev::tma_load_2d(dst + 2 * kWtTHalf, &tm_s, full(st), 0, y);
+        if (++st == kWtStages) { st = 0; ph ^= 1; }
+      }
+    }
+    return;
+  }
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  int st = 0, ph = 0;
+  for (int i = 0; i < steps; ++i) {
+    if (!dev::mbar_wait(full(st), ph, abort_flag, nullptr, 0)) return;
+    const uint32_t tt = sbase + st * kWtStageBytes, ss = tt + 2 * kWtTHalf;
+#pragma unroll
+    for (int kk = 0; kk < kWgRows / 16; ++kk) {
+      uint32_t a[4];  // S^T fragment: rows = rank index, k = token row
+      const uint32_t srow = kk * 16 + (lane >> 4) * 8 + (lane & 7), sch = (lane >> 3) & 1;
+      ldmatrix_x4_trans(ss + srow * 32u + ((sch ^ ((srow >> 2) & 1u)) << 4), a);
+      const uint32_t trow = kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+#pragma unroll
+      for (int np = 0; np < 2; ++np) {  // two pairs of 8-column tiles
+        uint32_t b[4];
+        const uint32_t idx = warp * 4 + np * 2 + (lane >> 4);         // 16-byte chunk of the 128-column row
+        ldmatrix_x4_trans(tt + (idx >> 3) * kWtTHalf + trow * 128u + (((idx & 7u) ^ (trow & 7u)) << 4), b);
+        mma_bf16(acc[np * 2], a, b[0], b[1]);
+        mma_bf16(acc[np * 2 + 1], a, b[2], b[3]);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) dev::mbar_arrive(empty(st));
+    if (++st == kWtStages) { st = 0; ph ^= 1; }
+  }
+  // acc[nt]: rank rows g, g+8; columns c0 + warp*32 + nt*8 + 2*(lane%4) + {0,1}
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int i = (lane >> 2) + half * 8;
+      const int col = c0 + warp * 32 + nt * 8 + (lane & 3) * 2;
+      if (col >= C) continue;
+      float* p = partial + ((int64_t)segi * kRankPad + i) * C + col;
+      p[0] = acc[nt][half * 2];
+      p[1] = acc[nt][half * 2 + 1];
+    }
+  }
+}
+
 // Sum the per-split partials in split order (deterministic), scale, round, store.
 __global__ void __launch_bounds__(64) lora_wgrad_reduce_kernel(const float* __restrict__ partial, int splits, int C, int r, float scale,
                                                                 __nv_bfloat16* __restrict__ out, int transpose_out) {
@@ -558,11 +649,20 @@ extern "C" int b2g_lora_wgrad(const void* s, const void* t, float scale, void* o
   const int chunks = (int)((C + lora::kWgCols - 1) / lora::kWgCols);
   const size_t smem = (size_t)lora::kWgStages * lora::kWgStageBytes;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  B2G_KERNEL_SMEM(lora::lora_wgrad_kernel<true>, smem);
   B2G_KERNEL_MAX_SHARED(lora::lora_wgrad_reduce_kernel);
-  lora::lora_wgrad_kernel<true><<<dim3(chunks, splits), 128, smem, st>>>(
-      static_cast<const __nv_bfloat16*>(s), static_cast<const __nv_bfloat16*>(t), scale, nullptr, M, rows_per_split, (int)C, r,
-      static_cast<float*>(workspace), nullptr, 0, 0, 0, nullptr);
+  {
+    // TMA-fed form.  Tensor maps: S [M, 16] (32-byte rows), T [M, C].
+    (void)smem;
+    CUtensorMap tm_s, tm_t;
+    int rc;
+    if ((rc = make_tmap_2d(&tm_s, s, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, lora::kRankPad, (uint64_t)M, lora::kRankPad * 2, lora::kRankPad,
+                           lora::kWgRows, CU_TENSOR_MAP_SWIZZLE_32B))) return rc;
+    if ((rc = make_tmap_2d(&tm_t, t, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)C, (uint64_t)M, (uint64_t)C * 2, 64, lora::kWgRows,
+                           CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+    B2G_KERNEL_SMEM(lora::lora_wgrad_tma_kernel, lora::kWtSmemBytes);
+    lora::lora_wgrad_tma_kernel<<<dim3(chunks, splits), 160, lora::kWtSmemBytes, st>>>(tm_s, tm_t, M, rows_per_split, (int)C,
+                                                                                       static_cast<float*>(workspace));
+  }
   B2G_CUDA_OK(cudaGetLastError());
   const int64_t n = (int64_t)r * C;
   lora::lora_wgrad_reduce_kernel<<<(int)((n + 63) / 64), 64, 0, st>>>(static_cast<const float*>(workspace), splits, (int)C, r, scale,
