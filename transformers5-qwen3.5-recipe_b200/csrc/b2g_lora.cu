@@ -1,7 +1,8 @@
 // LoRA rank-side products: the skinny projections (X.A^T, dY.B) and the factor gradients
 // (contractions over the token rows).  Output widths are <= 16, so these kernels are bound by
-// streaming X / dY once from HBM; tiles arrive through TMA (the projection with [r, C] weights) or a
-// cp.async pipeline (the rest) and the arithmetic is bf16 mma.sync with fp32 accumulation.  The same kernels serve the dense path (one weight) and the
+// streaming X / dY once from HBM; tiles arrive through TMA (the projection with [r, C] weights, the
+// dense factor gradient) or a cp.async pipeline (the rest) and the arithmetic is bf16 mma.sync with
+// fp32 accumulation.  The same kernels serve the dense path (one weight) and the
 // grouped path (one weight per expert segment).
 #include "b2g_common.cuh"
 
