@@ -984,7 +984,7 @@ qgemm_kernel(const Params p, const __grid_constant__ CUtensorMap tm_a0, const __
         if ((n % kUnpackGroups) != group) continue;
         const int ps = n / P::kSteps;                                // packed slots advance once per P::kSteps steps
         const int sp = ps % C::kPStages, pp = (ps / C::kPStages) & 1;
-        const int sb = n % kBStages, pb = (n / kBStages) & 1;
+        const int sb = n % kBStages;
         ok = dev::mbar_wait(bar(kFullP + sp), pp, abort_flag, p.status, 401, p.spin_limit);
         if (!ok) break;
         // one (row, column group) per thread: forward 128 rows, dgrad 64 rows x the two 64-column groups of this CTA

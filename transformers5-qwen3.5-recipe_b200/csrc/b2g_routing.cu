@@ -382,7 +382,7 @@ __global__ void __launch_bounds__(256) swiglu_fwd_kernel(const uint32_t* __restr
                                                          int64_t pairs_per_row) {
   int64_t first, last;
   live_pairs(npairs, row_begin, row_end, pairs_per_row, first, last);
-  if (kVec) {
+  if constexpr (kVec) {
     const uint4* g4 = reinterpret_cast<const uint4*>(gate);
     const uint4* u4 = reinterpret_cast<const uint4*>(up);
     uint4* z4 = reinterpret_cast<uint4*>(z);
@@ -391,10 +391,10 @@ __global__ void __launch_bounds__(256) swiglu_fwd_kernel(const uint32_t* __restr
       z4[i] = make_uint4(swiglu_fwd_pair(g.x, u.x, limit), swiglu_fwd_pair(g.y, u.y, limit), swiglu_fwd_pair(g.z, u.z, limit),
                          swiglu_fwd_pair(g.w, u.w, limit));
     }
-    return;
+  } else {
+    for (int64_t i = first + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < last; i += (int64_t)gridDim.x * blockDim.x)
+      z[i] = swiglu_fwd_pair(gate[i], up[i], limit);
   }
-  for (int64_t i = first + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < last; i += (int64_t)gridDim.x * blockDim.x)
-    z[i] = swiglu_fwd_pair(gate[i], up[i], limit);
 }
 
 template <bool kVec>
@@ -405,7 +405,7 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const uint32_t* __restr
                                                          int64_t pairs_per_row) {
   int64_t first, last;
   live_pairs(npairs, row_begin, row_end, pairs_per_row, first, last);
-  if (kVec) {
+  if constexpr (kVec) {
     const uint4* g4 = reinterpret_cast<const uint4*>(gate);
     const uint4* u4 = reinterpret_cast<const uint4*>(up);
     const uint4* d4 = reinterpret_cast<const uint4*>(dz);
@@ -421,13 +421,13 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const uint32_t* __restr
       dg4[i] = og;
       du4[i] = ou;
     }
-    return;
-  }
-  for (int64_t i = first + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < last; i += (int64_t)gridDim.x * blockDim.x) {
-    uint32_t og, ou;
-    swiglu_bwd_pair(gate[i], up[i], dz[i], limit, og, ou);
-    dgate[i] = og;
-    dup[i] = ou;
+  } else {
+    for (int64_t i = first + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < last; i += (int64_t)gridDim.x * blockDim.x) {
+      uint32_t og, ou;
+      swiglu_bwd_pair(gate[i], up[i], dz[i], limit, og, ou);
+      dgate[i] = og;
+      dup[i] = ou;
+    }
   }
 }
 
