@@ -138,7 +138,9 @@ B2G_API int b2g_lora_wgrad(const void* s, const void* t, float scale, void* out,
  * framework's memory plan, a host that was handed only input and output buffers, a process whose pool is
  * fully committed): the split partials live in a fixed 8 MiB array inside the library image, which every
  * GPU that loads the library holds until exit.  This entry has no counterpart in the reference.
- *   - allocates nothing: no cudaMalloc / cudaFree, no allocating library routine;
+ *   - allocates nothing on the device: no cudaMalloc / cudaFree, no allocating library routine (the two tensor maps of its
+ *     kernel are 128-byte host structures filled by cuTensorMapEncodeTiled, kept in a host-side table and passed as kernel
+ *     parameters);
  *   - shapes whose scratch need (b2g_lora_wgrad_workspace_bytes) exceeds b2g_lora_wgrad_static_max_bytes()
  *     are rejected with B2G_E_ARG; use b2g_lora_wgrad with your own workspace for those;
  *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress, with that
